@@ -1,0 +1,277 @@
+"""Headline benchmark: Qwen3-0.6B batch-1 greedy decode at long context.
+
+Workload (one "step"): reset, prefill a 2048-token uniform-random prompt, then
+256 greedy decode steps on seed-0 random-init bf16 weights of the Qwen3-0.6B
+architecture.  `value` is decode tokens/s with everything resident in HBM (the
+256-step device-resident chain timed with CUDA events); `e2e` is decode
+tokens/s through the public decoder API with host inputs and outputs
+(`decode_steps(first_token:int, n) -> cpu tensor`), and the prefill through
+`prefill_step(cpu ids)` is reported beside it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With --gpus N > 1 (under torchrun) every rank runs an independent replica on
+its own GPU with its own prompt; there is no data-path communication.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from megaqwen_b200.spec import QWEN3_0_6B  # noqa: E402
+from megaqwen_b200.synthetic import random_prompt, random_weights  # noqa: E402
+
+PROMPT_LEN = 2048
+NEW_TOKENS = 256
+MAX_SEQ = 2304
+METRIC = "decode_tokens_per_s_b1_ctx2048"
+WORKLOAD = "qwen3-0.6b random-init bf16, batch 1, 2048-token random prompt + 256 greedy decode steps"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().split(",")
+                self.samples.append(float(out[0]))
+                self.max_mhz = float(out[1])
+                for n, v in zip(names, out[2:]):
+                    if v.strip().lower() == "active":
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop_evt.wait(0.2)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=5)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def init_dist(world):
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # control plane only (start barrier, max of the timings): CPU tensors over gloo
+        dist.init_process_group("gloo")
+        return dist
+    return None
+
+
+def barrier_max(dist, values):
+    """Max over ranks of a list of floats (identity when single-process)."""
+    if dist is None:
+        return values
+    t = torch.tensor(values, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def cpu_reference(sample_new: int, threads: int | None = None):
+    """The reference's HF bf16 path on the host cores: decode tokens/s at context
+    2048 on a bounded sample (2048-token prompt, `sample_new` new tokens)."""
+    from oracle.hf_reference import build_hf_model, time_hf_decode
+    if threads:
+        torch.set_num_threads(threads)
+    w = random_weights(QWEN3_0_6B, MAX_SEQ)
+    model = build_hf_model(QWEN3_0_6B, w)
+    prompt = random_prompt(QWEN3_0_6B, PROMPT_LEN, 2, 0)
+    tps, prefill_s = time_hf_decode(model, prompt, sample_new)
+    return tps, prefill_s, torch.get_num_threads()
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    sample_new = 24
+    vals, pre = [], []
+    from oracle.hf_reference import build_hf_model, time_hf_decode
+    w = random_weights(QWEN3_0_6B, MAX_SEQ)
+    model = build_hf_model(QWEN3_0_6B, w)
+    prompt = random_prompt(QWEN3_0_6B, PROMPT_LEN, 2, 0)
+    for i in range(args.warmup + args.steps):
+        tps, prefill_s = time_hf_decode(model, prompt, sample_new)
+        if i >= args.warmup:
+            vals.append(tps)
+            pre.append(prefill_s)
+    v = sum(vals) / len(vals)
+    cores = torch.get_num_threads()
+    sample = f"{PROMPT_LEN}-token prompt + {sample_new} greedy tokens per step, HF Qwen3ForCausalLM bf16 on CPU"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sample_new / v,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "prefill_tokens_per_s": PROMPT_LEN / (sum(pre) / len(pre)),
+        "host_cpus": os.cpu_count(),
+    }))
+
+
+def run_ours(args):
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = init_dist(world)
+    from megaqwen_b200.decoder import MegakernelDecoder
+
+    w = random_weights(QWEN3_0_6B, MAX_SEQ)
+    lw = [t.to(dev) for t in w["layer_weights"]]
+    embed = w["embed_weight"].to(dev)
+    dec = MegakernelDecoder(embed, lw, w["final_norm_weight"].to(dev), embed, w["cos_table"].to(dev),
+                            w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, PROMPT_LEN)
+    prompt = random_prompt(QWEN3_0_6B, PROMPT_LEN, 2, rank).pin_memory()
+    chunk = args.chunk
+
+    def one_step(timed: bool):
+        """Returns (decode_ms_device, decode_ms_e2e, prefill_ms_e2e, launches)."""
+        dec.reset()
+        torch.cuda.synchronize(dev)
+        l0 = dec.launches
+        t0 = time.perf_counter()
+        first = dec.prefill_step(prompt)
+        torch.cuda.synchronize(dev)
+        t1 = time.perf_counter()
+        # (a) device-resident chain, CUDA events on the launching stream
+        pos0 = dec.position()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first_dev = torch.tensor([first], dtype=torch.int32, device=dev)
+        torch.cuda.synchronize(dev)
+        l1 = dec.launches
+        ev0.record()
+        done = 0
+        cur = first_dev
+        while done < NEW_TOKENS:
+            n = min(chunk, NEW_TOKENS - done)
+            out = dec._chain(cur, n, True)
+            cur = out[n - 1:n].clone()
+            done += n
+        ev1.record()
+        torch.cuda.synchronize(dev)
+        l2 = dec.launches
+        dev_ms = ev0.elapsed_time(ev1)
+        dec.check_status()
+        # (b) the same 256 steps through the public API with host in/out
+        dec.position_ = pos0
+        torch.cuda.synchronize(dev)
+        t2 = time.perf_counter()
+        toks = dec.decode_steps(first, NEW_TOKENS)
+        t3 = time.perf_counter()
+        assert toks.numel() == NEW_TOKENS and not toks.is_cuda
+        return dev_ms, (t3 - t2) * 1e3, (t1 - t0) * 1e3, l2 - l1
+
+    for _ in range(args.warmup):
+        one_step(False)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(local)
+    sampler.start()
+    dev_ms, e2e_ms, pre_ms, launches = [], [], [], 0
+    wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        a, b, c, l = one_step(True)
+        dev_ms.append(a); e2e_ms.append(b); pre_ms.append(c); launches += l
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop()
+    tot_dev, tot_e2e, tot_pre = barrier_max(dist, [sum(dev_ms), sum(e2e_ms), sum(pre_ms)])
+    if rank != 0:
+        return
+    n_tok = NEW_TOKENS * args.steps * world
+    value = n_tok / (tot_dev / 1e3)
+    e2e = n_tok / (tot_e2e / 1e3)
+    peak, peak_kind = load_peaks()
+    # algorithmic bytes of the decode steps of one pass: cache length after step i is 2048 + i + 1
+    bytes_pass = sum(QWEN3_0_6B.decode_bytes(PROMPT_LEN + i + 1) for i in range(NEW_TOKENS))
+    step_s = (tot_dev / 1e3) / (NEW_TOKENS * args.steps)
+    achieved = bytes_pass / NEW_TOKENS / step_s / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": tot_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": f"{world} independent replica(s), no communication",
+                   "l2": "inputs larger than L2 (1.19 GB of weights stream per token)", "graph_chunk": chunk},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * NEW_TOKENS + 4,
+                "prefill_tokens_per_s": PROMPT_LEN * args.steps * world / (tot_pre / 1e3),
+                "prefill_h2d_bytes_per_step": 4 * PROMPT_LEN},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "one decode step (141 chained kernels)",
+                     "frac_of_8TBps": achieved / 8000.0, "us_per_token": step_s * 1e6},
+        "clocks": clocks,
+        "wall_s": wall,
+    }
+    if not args.no_cpu and world == 1:
+        try:
+            tps, prefill_s, cores = cpu_reference(16)
+            line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference",
+                                    "sample": f"{PROMPT_LEN}-token prompt + 16 greedy tokens, HF Qwen3ForCausalLM bf16 on CPU",
+                                    "prefill_tokens_per_s": PROMPT_LEN / prefill_s}
+        except Exception as exc:  # the baseline is reported, never a gate
+            line["cpu_baseline"] = {"value": None, "error": repr(exc)[:200]}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunk", type=int, default=32, help="decode steps per CUDA graph")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,151 @@
+/*
+ * megaqwen_b200 — C ABI of the sm_100a Qwen3-0.6B greedy prefill + decode path.
+ *
+ * This is the boundary a non-Python caller links against.  It replaces the
+ * reference's `extern "C" launch_*` functions (csrc/megakernel/
+ * fused_decode_ldg_launch.inl, fused_prefill_launch.inl) and keeps their
+ * conventions: the caller owns every buffer (weights, KV cache, scratch, token
+ * and position scalars are device pointers), token in/out and the position are
+ * DEVICE scalars so that steps can be chained without a host round trip and
+ * captured in a CUDA graph, and every call is asynchronous on the given
+ * stream.  Unlike the reference (which returns void and drops errors) every
+ * entry point returns an int: 0 on success, a negative MQ_ERR_* code for a
+ * rejected argument, or a positive cudaError_t value.  Device-side waits are
+ * bounded; one that expires sets a bit in the caller's `status` word instead
+ * of hanging.
+ *
+ * Plain C types only: no torch, no C++ in the signatures.
+ */
+#ifndef MEGAQWEN_B200_H
+#define MEGAQWEN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Fixed block geometry the kernels are compiled for
+ * (reference: csrc/megakernel/config.cuh:64-73). */
+#define MQ_HIDDEN 1024
+#define MQ_INTERMEDIATE 3072
+#define MQ_NUM_Q_HEADS 16
+#define MQ_NUM_KV_HEADS 8
+#define MQ_HEAD_DIM 128
+#define MQ_Q_SIZE 2048
+#define MQ_KV_SIZE 1024
+
+#define MQ_OK 0
+#define MQ_ERR_BAD_ARG (-1)       /* null pointer, non-positive size */
+#define MQ_ERR_TOO_LONG (-2)      /* sequence / position exceeds max_seq_len or scratch capacity */
+#define MQ_ERR_UNSUPPORTED (-3)   /* device is not sm_100, or geometry not supported */
+#define MQ_ERR_ALIGNMENT (-4)     /* a pointer is not 16-byte aligned */
+
+/* Bits of the device status word (MqDecodeBuffers.status). */
+#define MQ_STATUS_WAIT_TIMEOUT 1u /* a bounded shared-memory barrier wait expired */
+#define MQ_STATUS_BAD_POSITION 2u /* position >= max_seq_len seen on the device; the step was skipped */
+#define MQ_STATUS_BAD_TOKEN 4u    /* token id outside [0, vocab) seen on the device; clamped */
+
+/* Launch flags. */
+#define MQ_FLAG_CHAINED 1   /* this step directly follows another decode step of the same
+                               buffers on the same stream (lets its first kernel overlap
+                               the previous step's LM head) */
+#define MQ_FLAG_NO_PDL 2    /* launch every kernel with full stream serialisation
+                               (no programmatic dependent launch); for A/B measurements */
+
+/* Per-layer weight table, bf16 row-major [out, in] exactly as HF nn.Linear.weight.
+ * Same member order as the reference's LDGLayerWeights
+ * (csrc/megakernel/fused_decode_ldg_common.inl:97-109, bindings_decode.cpp:32-44). */
+typedef struct MqLayerWeights {
+    const void* input_layernorm;     /* [1024]        */
+    const void* q_proj;              /* [2048, 1024]  */
+    const void* k_proj;              /* [1024, 1024]  */
+    const void* v_proj;              /* [1024, 1024]  */
+    const void* q_norm;              /* [128]         */
+    const void* k_norm;              /* [128]         */
+    const void* o_proj;              /* [1024, 2048]  */
+    const void* post_attn_layernorm; /* [1024]        */
+    const void* gate_proj;           /* [3072, 1024]  */
+    const void* up_proj;             /* [3072, 1024]  */
+    const void* down_proj;           /* [1024, 3072]  */
+} MqLayerWeights;
+
+/* Model description.  `layers` is a HOST array of num_layers entries holding
+ * device pointers (the reference passes a host table to launch_prefill_float,
+ * bindings_prefill.cpp:798, and a device table to launch_ldg_decode). */
+typedef struct MqModel {
+    const void* embed;        /* [vocab, 1024] bf16 */
+    const MqLayerWeights* layers;
+    const void* final_norm;   /* [1024] bf16 */
+    const void* lm_head;      /* [vocab, 1024] bf16 (tied: same pointer as embed) */
+    const void* cos_table;    /* [max_seq_len, 128] bf16 */
+    const void* sin_table;    /* [max_seq_len, 128] bf16 */
+    int num_layers;
+    int vocab_size;
+    int max_seq_len;
+} MqModel;
+
+/* Caller-owned state and scratch of one batch-1 decoder.  KV cache layout is
+ * the reference's: [num_layers, 8, max_seq_len, 128] bf16, K stored after
+ * QK-norm and RoPE, V raw (bindings_decode.cpp:127-130). */
+typedef struct MqDecodeBuffers {
+    void* k_cache;
+    void* v_cache;
+    void* hidden;             /* bf16 [1024]  residual stream                     */
+    void* qkv;                /* bf16 [4096]  raw q|k|v of the current layer      */
+    void* attn_out;           /* bf16 [2048]                                      */
+    void* mlp_act;            /* bf16 [3072]  silu(gate)*up                       */
+    float* attn_partials;     /* fp32 [16 * nsplit * 130] split-KV partials       */
+    unsigned int* counters;   /* u32 [16], zero-initialised by the caller once    */
+    unsigned long long* argmax_slot; /* u64 [1], zero-initialised by the caller once */
+    unsigned int* status;     /* u32 [1], sticky MQ_STATUS_* bits                 */
+    int attn_nsplit;          /* from mq_decode_attn_nsplit(max_seq_len)          */
+} MqDecodeBuffers;
+
+/* Number of KV splits the decode attention kernel uses for a cache of
+ * max_seq_len positions; sizes MqDecodeBuffers.attn_partials. */
+int mq_decode_attn_nsplit(int max_seq_len);
+
+/* Bytes of MqDecodeBuffers.attn_partials for a given max_seq_len. */
+size_t mq_decode_partials_bytes(int max_seq_len);
+
+/* Number of kernels one mq_launch_decode call launches (for launch counting). */
+int mq_decode_launch_count(int num_layers);
+
+/* One greedy decode step: reads *in_token and *position (device), writes K/V of
+ * that position, attends over position+1 entries and writes the arg-max token
+ * (lowest index among equal bf16 logits) to *out_token.  If logits != NULL the
+ * bf16-rounded logits are also written there as fp32 [vocab].
+ * Replaces launch_ldg_decode / launch_ldg_decode_with_logits
+ * (csrc/megakernel/fused_decode_ldg_launch.inl:55-212, 215-364). */
+int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf,
+                     const int* in_token, int* out_token, const int* position,
+                     float* logits, int flags, void* stream);
+
+/* dst[i] = start + i.  Replaces launch_ldg_fill_iota
+ * (csrc/megakernel/fused_decode_ldg_launch.inl:5-17). */
+int mq_launch_fill_iota(int* dst, int start, int n, void* stream);
+
+/* *out_index = min(*out_index, first i in [0,n) with tokens[i] in eos_ids[0..n_eos)).
+ * The caller initialises *out_index (e.g. to n).  Replaces
+ * launch_ldg_find_first_eos (csrc/megakernel/fused_decode_ldg_launch.inl:19-53). */
+int mq_launch_find_first_eos(const int* tokens, int n, const int* eos_ids, int n_eos,
+                             int* out_index, void* stream);
+
+/* Library / device facts: returns 0 and fills the outputs (any may be NULL). */
+int mq_device_info(int* sm_count, int* cc_major, int* cc_minor);
+
+/* One-time set-up of the current device (shared-memory opt-in of the kernels).
+ * Every launch entry point does this lazily on its first call; call it
+ * explicitly before capturing launches into a CUDA graph.  Returns
+ * MQ_ERR_UNSUPPORTED on anything but an sm_100 device. */
+int mq_init_device(void);
+
+/* ABI version of this header. */
+int mq_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MEGAQWEN_B200_H */

@@ -1,0 +1,790 @@
+// Batch-1 greedy decode step for sm_100a: six weight-streaming kernels per
+// token position chained with programmatic dependent launch (PDL).
+//
+// Design.  One decode step is HBM-bound (1.19 GB of bf16 weights + the KV
+// cache per token) but consists of ~140 dependent phases.  Instead of a
+// cooperative grid with a grid-wide barrier per phase (the reference:
+// csrc/megakernel/fused_decode_ldg_kernel.inl:43-137, 225 grid.sync() calls)
+// every phase is its own kernel of one CTA per SM, and every kernel starts with
+// a prologue that does not depend on the previous phase: it pulls the CTA's
+// whole slice of the weight matrix (contiguous rows, 28-96 KB) into shared
+// memory with 1-D TMA bulk copies, then executes griddepcontrol.wait.  Because
+// each kernel releases its dependents at once, the weight stream of phase n+1
+// (and n+2, shared memory permitting) overlaps the arithmetic and the drain of
+// phase n, and the hardware tracks the dependency: no flag spinning anywhere.
+//
+// Rounding points follow the HuggingFace bf16 model (bf16 out of every linear,
+// norm, RoPE product and sum, activation, product and residual add; fp32
+// accumulation inside dot products, norms and softmax).
+//
+// Phases per layer (reference stage each one replaces):
+//   k_qkv     RMSNorm + [Wq;Wk;Wv] GEMV        fused_decode_ldg_common.inl:131-262
+//   k_attn    QK-norm + RoPE + cache write + split-KV GQA attention
+//                                              fused_decode_ldg_common.inl:268-394, 417-794
+//   k_oproj   Wo GEMV + residual               fused_decode_ldg_mlp.inl:5-63
+//   k_gateup  RMSNorm + gate/up GEMV + SiLU*up fused_decode_ldg_mlp.inl:64-170
+//   k_down    Wd GEMV + residual               fused_decode_ldg_mlp.inl:171-218
+// then k_lmhead: final RMSNorm + tied LM head + arg-max
+//                                              fused_decode_ldg_kernel.inl:104-137, fused_decode_ldg_lm.inl:6-163
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mq_device.cuh"
+
+namespace mq {
+
+struct DecodeArgs {
+    const bf16* embed;
+    const bf16* final_norm;
+    const bf16* lm_head;
+    const bf16* cos;
+    const bf16* sin;
+    bf16* k_cache;
+    bf16* v_cache;
+    bf16* hidden;
+    bf16* qkv;
+    bf16* attn;
+    bf16* act;
+    float* partials;
+    unsigned int* counters;
+    unsigned long long* slot;
+    unsigned int* status;
+    const int* in_token;
+    int* out_token;
+    const int* pos;
+    float* logits;
+    int vocab;
+    int max_seq;
+    int nsplit;
+    int chunk_cap;
+};
+
+constexpr int GEMV_THREADS = 256;
+constexpr int DOWN_THREADS = 384;
+constexpr int MIN_GRID = 128;                 // row caps below assume at least this many CTAs
+constexpr int QKV_MAXROWS = QKV / MIN_GRID;   // 32 rows x 2 KB
+constexpr int O_MAXROWS = H / MIN_GRID;       // 8 rows x 4 KB
+constexpr int GU_MAXROWS = I / MIN_GRID;      // 24 rows x 2 KB, twice
+constexpr int DN_MAXROWS = H / MIN_GRID;      // 8 rows x 6 KB
+constexpr int MAX_BARS = 8;
+
+__device__ __forceinline__ void row_range(int total, int& r0, int& n) {
+    r0 = (int)(((long long)blockIdx.x * total) / gridDim.x);
+    const int r1 = (int)(((long long)(blockIdx.x + 1) * total) / gridDim.x);
+    n = r1 - r0;
+}
+
+// ---------------------------------------------------------------- k_qkv
+// qkv[r] = bf16( [Wq;Wk;Wv][r,:] . rmsnorm(hidden) ), r in this CTA's rows.
+// For layer 0 the residual stream is first gathered from the embedding table.
+__global__ void __launch_bounds__(GEMV_THREADS) k_qkv(DecodeArgs a, MqLayerWeights w, int layer) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)QKV_MAXROWS * H * 2);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int r0, n;
+    row_range(QKV, r0, n);
+    constexpr int CH = 8;  // rows per barrier
+    if (tid == 0) {
+        const int nch = (n + CH - 1) / CH;
+        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
+        mbar_fence_init();
+        for (int c = 0; c < nch; ++c) {
+            const int a0 = r0 + c * CH, a1 = min(r0 + n, a0 + CH);
+            mbar_expect_tx(&bars[c], (uint32_t)(a1 - a0) * H * 2);
+            // a chunk may straddle the q|k|v matrix boundaries
+            int r = a0;
+            while (r < a1) {
+                const bf16* base;
+                int local, lim;
+                if (r < QSZ) { base = (const bf16*)w.q_proj; local = r; lim = QSZ; }
+                else if (r < QSZ + KVSZ) { base = (const bf16*)w.k_proj; local = r - QSZ; lim = QSZ + KVSZ; }
+                else { base = (const bf16*)w.v_proj; local = r - QSZ - KVSZ; lim = QKV; }
+                const int e = min(a1, lim);
+                bulk_g2s(wbuf + (size_t)(r - r0) * H, base + (size_t)local * H, (uint32_t)(e - r) * H * 2, &bars[c]);
+                r = e;
+            }
+        }
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+
+    float x[32];
+    if (layer == 0) {
+        int tok = ld_cg_i32(a.in_token);
+        const int p = ld_cg_i32(a.pos);
+        if (blockIdx.x == 0 && tid == 0) {
+            if (tok < 0 || tok >= a.vocab) atomicOr(a.status, MQ_STATUS_BAD_TOKEN);
+            if (p < 0 || p >= a.max_seq) atomicOr(a.status, MQ_STATUS_BAD_POSITION);
+        }
+        tok = min(max(tok, 0), a.vocab - 1);
+        const bf16* src = a.embed + (size_t)tok * H;
+        if (blockIdx.x == 0 && warp == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4*>(a.hidden + j * 256 + lane * 8) = ld_cg_u4(src + j * 256 + lane * 8);
+        }
+        load_x_slice(x, src, lane);
+    } else {
+        load_x_slice(x, a.hidden, lane);
+    }
+    rmsnorm_slice(x, (const bf16*)w.input_layernorm, lane);
+
+    for (int i = warp; i < n; i += 16) {
+        const int i2 = i + 8;
+        mbar_wait(&bars[i / CH], 0, a.status);
+        float d0 = dot_slice(wbuf + (size_t)i * H, x, lane);
+        float d1 = 0.f;
+        if (i2 < n) {
+            mbar_wait(&bars[i2 / CH], 0, a.status);
+            d1 = dot_slice(wbuf + (size_t)i2 * H, x, lane);
+        }
+        d0 = warp_sum(d0);
+        d1 = warp_sum(d1);
+        if (lane == 0) {
+            a.qkv[r0 + i] = __float2bfloat16_rn(d0);
+            if (i2 < n) a.qkv[r0 + i2] = __float2bfloat16_rn(d1);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- k_attn
+// One CTA per (kv head g, split s).  The two query heads 2g and 2g+1 share the
+// K/V stream.  The CTA's chunk of cached K and V rows is copied into shared
+// memory before the dependency wait (those rows were written by earlier decode
+// steps or by prefill); the new position's K/V come from this layer's qkv.
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_MIN_CHUNK = 64;
+constexpr int PART_STRIDE = D + 2;  // m, l, acc[128]
+
+__device__ __forceinline__ void norm_rope_head(const bf16* raw, const bf16* wn, const bf16* cosr, const bf16* sinr,
+                                               int lane, float (&lo)[2], float (&hi)[2]) {
+    // lane owns elements 2*lane, 2*lane+1 (first half) and 64+2*lane, 64+2*lane+1 (second half)
+    const uint32_t ulo = ld_cg_u32(raw + 2 * lane), uhi = ld_cg_u32(raw + 64 + 2 * lane);
+    float xl[2] = {bf_lo(ulo), bf_hi(ulo)}, xh[2] = {bf_lo(uhi), bf_hi(uhi)};
+    float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+    const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
+    const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
+    const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
+    const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
+    const float clo[2] = {bf_lo(cl), bf_hi(cl)}, chi[2] = {bf_lo(chh), bf_hi(chh)};
+    const float slo[2] = {bf_lo(sl), bf_hi(sl)}, shi[2] = {bf_lo(sh), bf_hi(sh)};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const float nl = rbf(wlo[e] * rbf(xl[e] * r));
+        const float nh = rbf(whi[e] * rbf(xh[e] * r));
+        // x*cos + rotate_half(x)*sin, rotate_half = (-second half, first half)
+        lo[e] = rbf(rbf(nl * clo[e]) + rbf(-nh * slo[e]));
+        hi[e] = rbf(rbf(nh * chi[e]) + rbf(nl * shi[e]));
+    }
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeights w, int layer) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    const int cap = a.chunk_cap;
+    bf16* kt = reinterpret_cast<bf16*>(smem_raw);                     // [cap][128]
+    bf16* vt = kt + (size_t)cap * D;                                  // [cap][128]
+    float* sc = reinterpret_cast<float*>(vt + (size_t)cap * D);       // [2][cap]
+    float* qh = sc + 2 * cap;                                         // [2][128]
+    float* accb = qh + 2 * D;                                         // [2][2][128]
+    float* ml = accb + 4 * D;                                         // [2][2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ml + 4);             // [2]
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = blockIdx.x, s = blockIdx.y;
+    const int pos = ld_cg_i32(a.pos);
+    const bool valid = pos >= 0 && pos < a.max_seq;
+    const int len = pos + 1;
+    int chunk = (len + a.nsplit - 1) / a.nsplit;
+    chunk = max(ATT_MIN_CHUNK, (chunk + 15) & ~15);
+    const int n_act = valid ? (len + chunk - 1) / chunk : 0;
+    const bool active = s < n_act && chunk <= cap;
+    if (valid && chunk > cap && tid == 0) atomicOr(a.status, MQ_STATUS_BAD_POSITION);
+    const int c0 = s * chunk;
+    const int n = active ? min(len, c0 + chunk) - c0 : 0;  // positions handled here
+    const bool is_last = active && (s == n_act - 1);       // owns the new position
+    const int n_cached = is_last ? n - 1 : n;
+    const size_t head_off = ((size_t)(layer * NKV + g) * a.max_seq) * D;
+
+    if (tid == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+        if (n_cached > 0) {
+            mbar_expect_tx(&bars[0], (uint32_t)n_cached * D * 2);
+            bulk_g2s(kt, a.k_cache + head_off + (size_t)c0 * D, (uint32_t)n_cached * D * 2, &bars[0]);
+            mbar_expect_tx(&bars[1], (uint32_t)n_cached * D * 2);
+            bulk_g2s(vt, a.v_cache + head_off + (size_t)c0 * D, (uint32_t)n_cached * D * 2, &bars[1]);
+        }
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+    if (!active) return;
+
+    // ---- per-head norm + RoPE of q (both heads), and of the new k; v raw
+    if (warp < 2) {
+        float lo[2], hi[2];
+        norm_rope_head(a.qkv + (2 * g + warp) * D, (const bf16*)w.q_norm, a.cos + (size_t)pos * D, a.sin + (size_t)pos * D, lane, lo, hi);
+        qh[warp * D + 2 * lane] = lo[0]; qh[warp * D + 2 * lane + 1] = lo[1];
+        qh[warp * D + 64 + 2 * lane] = hi[0]; qh[warp * D + 64 + 2 * lane + 1] = hi[1];
+    } else if (warp == 2 && is_last) {
+        float lo[2], hi[2];
+        norm_rope_head(a.qkv + QSZ + g * D, (const bf16*)w.k_norm, a.cos + (size_t)pos * D, a.sin + (size_t)pos * D, lane, lo, hi);
+        const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
+        bf16* krow = kt + (size_t)(n - 1) * D;
+        *reinterpret_cast<uint32_t*>(krow + 2 * lane) = plo;
+        *reinterpret_cast<uint32_t*>(krow + 64 + 2 * lane) = phi;
+        bf16* gk = a.k_cache + head_off + (size_t)pos * D;
+        *reinterpret_cast<uint32_t*>(gk + 2 * lane) = plo;
+        *reinterpret_cast<uint32_t*>(gk + 64 + 2 * lane) = phi;
+    } else if (warp == 3 && is_last) {
+        const uint2 u = ld_cg_u2(a.qkv + QSZ + KVSZ + g * D + 4 * lane);
+        *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * D + 4 * lane) = u;
+        *reinterpret_cast<uint2*>(a.v_cache + head_off + (size_t)pos * D + 4 * lane) = u;
+    }
+    __syncthreads();
+    if (n_cached > 0) mbar_wait(&bars[0], 0, a.status);
+
+    // ---- scores: 8 lanes per position, 4 positions per warp pass
+    {
+        const int psub = lane >> 3, part = lane & 7;
+        float q0[16], q1[16];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            q0[e] = qh[part * 8 + e]; q0[8 + e] = qh[64 + part * 8 + e];
+            q1[e] = qh[D + part * 8 + e]; q1[8 + e] = qh[D + 64 + part * 8 + e];
+        }
+        const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+        for (int p4 = warp * 4; p4 < n; p4 += (ATT_THREADS / 32) * 4) {
+            const int p = p4 + psub;
+            float s0 = 0.f, s1 = 0.f;
+            if (p < n) {
+                const uint4 ua = *reinterpret_cast<const uint4*>(kt + (size_t)p * D + part * 8);
+                const uint4 ub = *reinterpret_cast<const uint4*>(kt + (size_t)p * D + 64 + part * 8);
+                const float kv[16] = {bf_lo(ua.x), bf_hi(ua.x), bf_lo(ua.y), bf_hi(ua.y), bf_lo(ua.z), bf_hi(ua.z), bf_lo(ua.w), bf_hi(ua.w),
+                                      bf_lo(ub.x), bf_hi(ub.x), bf_lo(ub.y), bf_hi(ub.y), bf_lo(ub.z), bf_hi(ub.z), bf_lo(ub.w), bf_hi(ub.w)};
+#pragma unroll
+                for (int e = 0; e < 16; ++e) { s0 = fmaf(kv[e], q0[e], s0); s1 = fmaf(kv[e], q1[e], s1); }
+            }
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            }
+            if (part == 0 && p < n) { sc[p] = s0 * scale; sc[cap + p] = s1 * scale; }
+        }
+    }
+    __syncthreads();
+
+    // ---- chunk-local softmax statistics; probabilities rounded to bf16 for the PV product
+    if (warp < 2) {
+        float* srow = sc + warp * cap;
+        float m = -INFINITY;
+        for (int p = lane; p < n; p += 32) m = fmaxf(m, srow[p]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int p = lane; p < n; p += 32) {
+            const float e = expf(srow[p] - m);
+            l += e;
+            srow[p] = rbf(e);
+        }
+        l = warp_sum(l);
+        if (lane == 0) { ml[warp * 2] = m; ml[warp * 2 + 1] = l; }
+    }
+    __syncthreads();
+    if (n_cached > 0) mbar_wait(&bars[1], 0, a.status);
+
+    // ---- PV: thread = (head, half of the positions, pair of dims)
+    {
+        const int hh = tid >> 7, half = (tid >> 6) & 1, dp = tid & 63;
+        const int nh = (n + 1) >> 1;
+        const int pb = half * nh, pe = min(n, pb + nh);
+        const float* prow = sc + hh * cap;
+        float a0 = 0.f, a1 = 0.f;
+        for (int p = pb; p < pe; ++p) {
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(vt + (size_t)p * D + 2 * dp);
+            const float pv = prow[p];
+            a0 = fmaf(pv, bf_lo(u), a0);
+            a1 = fmaf(pv, bf_hi(u), a1);
+        }
+        accb[(hh * 2 + half) * D + 2 * dp] = a0;
+        accb[(hh * 2 + half) * D + 2 * dp + 1] = a1;
+    }
+    __syncthreads();
+    const int hh = tid >> 7, d = tid & 127;
+    const float acc = accb[(hh * 2) * D + d] + accb[(hh * 2 + 1) * D + d];
+    const int qhead = 2 * g + hh;
+    if (n_act == 1) {
+        a.attn[qhead * D + d] = __float2bfloat16_rn(acc / ml[hh * 2 + 1]);
+        return;
+    }
+    // ---- split-KV: publish the partial, the last CTA of this kv head merges
+    float* part = a.partials + ((size_t)qhead * a.nsplit + s) * PART_STRIDE;
+    part[2 + d] = acc;
+    if (d == 0) { part[0] = ml[hh * 2]; part[1] = ml[hh * 2 + 1]; }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int t = atomicAdd(&a.counters[g], 1u);
+        s_last = (t == (unsigned int)(n_act - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float M = -INFINITY;
+    for (int j = 0; j < n_act; ++j) M = fmaxf(M, ld_cg_f32(a.partials + ((size_t)qhead * a.nsplit + j) * PART_STRIDE));
+    float num = 0.f, den = 0.f;
+    for (int j = 0; j < n_act; ++j) {
+        const float* pj = a.partials + ((size_t)qhead * a.nsplit + j) * PART_STRIDE;
+        const float f = expf(ld_cg_f32(pj) - M);
+        den = fmaf(ld_cg_f32(pj + 1), f, den);
+        num = fmaf(ld_cg_f32(pj + 2 + d), f, num);
+    }
+    a.attn[qhead * D + d] = __float2bfloat16_rn(num / den);
+    if (tid == 0) a.counters[g] = 0u;
+}
+
+// ---------------------------------------------------------------- k_oproj
+// hidden[r] = bf16( hidden[r] + bf16( Wo[r,:] . attn ) )
+__global__ void __launch_bounds__(GEMV_THREADS) k_oproj(DecodeArgs a, MqLayerWeights w) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)O_MAXROWS * QSZ * 2);
+    float* part = reinterpret_cast<float*>(bars + MAX_BARS);  // [rows][2]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int r0, n;
+    row_range(H, r0, n);
+    constexpr int CH = 4;
+    if (tid == 0) {
+        const int nch = (n + CH - 1) / CH;
+        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
+        mbar_fence_init();
+        for (int c = 0; c < nch; ++c) {
+            const int a0 = c * CH, a1 = min(n, a0 + CH);
+            const uint32_t bytes = (uint32_t)(a1 - a0) * QSZ * 2;
+            mbar_expect_tx(&bars[c], bytes);
+            bulk_g2s(wbuf + (size_t)a0 * QSZ, (const bf16*)w.o_proj + (size_t)(r0 + a0) * QSZ, bytes, &bars[c]);
+        }
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+
+    const int slice = warp & 1, rg = warp >> 1;
+    float x[32];
+    load_x_slice(x, a.attn + slice * 1024, lane);
+    for (int i = rg; i < n; i += 4) {
+        mbar_wait(&bars[i / CH], 0, a.status);
+        const float dsum = warp_sum(dot_slice(wbuf + (size_t)i * QSZ + slice * 1024, x, lane));
+        if (lane == 0) part[i * 2 + slice] = dsum;
+    }
+    __syncthreads();
+    if (tid < n) {
+        const float o = rbf(part[tid * 2] + part[tid * 2 + 1]);
+        const unsigned short hb = __ldcg(reinterpret_cast<const unsigned short*>(a.hidden + r0 + tid));
+        const float hres = __uint_as_float((uint32_t)hb << 16);
+        a.hidden[r0 + tid] = __float2bfloat16_rn(hres + o);
+    }
+}
+
+// ---------------------------------------------------------------- k_gateup
+// act[i] = bf16( bf16(silu(bf16(Wg[i,:].x))) * bf16(Wu[i,:].x) ), x = rmsnorm(hidden)
+__global__ void __launch_bounds__(GEMV_THREADS) k_gateup(DecodeArgs a, MqLayerWeights w) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    bf16* gbuf = reinterpret_cast<bf16*>(smem_raw);
+    bf16* ubuf = gbuf + (size_t)GU_MAXROWS * H;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)2 * GU_MAXROWS * H * 2);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int r0, n;
+    row_range(I, r0, n);
+    constexpr int CH = 8;
+    if (tid == 0) {
+        const int nch = (n + CH - 1) / CH;
+        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
+        mbar_fence_init();
+        for (int c = 0; c < nch; ++c) {
+            const int a0 = c * CH, a1 = min(n, a0 + CH);
+            const uint32_t bytes = (uint32_t)(a1 - a0) * H * 2;
+            mbar_expect_tx(&bars[c], 2 * bytes);
+            bulk_g2s(gbuf + (size_t)a0 * H, (const bf16*)w.gate_proj + (size_t)(r0 + a0) * H, bytes, &bars[c]);
+            bulk_g2s(ubuf + (size_t)a0 * H, (const bf16*)w.up_proj + (size_t)(r0 + a0) * H, bytes, &bars[c]);
+        }
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+
+    float x[32];
+    load_x_slice(x, a.hidden, lane);
+    rmsnorm_slice(x, (const bf16*)w.post_attn_layernorm, lane);
+    for (int i = warp; i < n; i += 8) {
+        mbar_wait(&bars[i / CH], 0, a.status);
+        float gsum = dot_slice(gbuf + (size_t)i * H, x, lane);
+        float usum = dot_slice(ubuf + (size_t)i * H, x, lane);
+        gsum = warp_sum(gsum);
+        usum = warp_sum(usum);
+        if (lane == 0) {
+            const float act = rbf(silu_f32(rbf(gsum)));
+            a.act[r0 + i] = __float2bfloat16_rn(act * rbf(usum));
+        }
+    }
+}
+
+// ---------------------------------------------------------------- k_down
+// hidden[r] = bf16( hidden[r] + bf16( Wd[r,:] . act ) )
+__global__ void __launch_bounds__(DOWN_THREADS) k_down(DecodeArgs a, MqLayerWeights w) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)DN_MAXROWS * I * 2);
+    float* part = reinterpret_cast<float*>(bars + MAX_BARS);  // [rows][3]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int r0, n;
+    row_range(H, r0, n);
+    constexpr int CH = 4;
+    if (tid == 0) {
+        const int nch = (n + CH - 1) / CH;
+        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
+        mbar_fence_init();
+        for (int c = 0; c < nch; ++c) {
+            const int a0 = c * CH, a1 = min(n, a0 + CH);
+            const uint32_t bytes = (uint32_t)(a1 - a0) * I * 2;
+            mbar_expect_tx(&bars[c], bytes);
+            bulk_g2s(wbuf + (size_t)a0 * I, (const bf16*)w.down_proj + (size_t)(r0 + a0) * I, bytes, &bars[c]);
+        }
+    }
+    __syncthreads();
+    pdl_trigger();
+    pdl_wait();
+
+    const int slice = warp % 3, rg = warp / 3;
+    float x[32];
+    load_x_slice(x, a.act + slice * 1024, lane);
+    for (int i = rg; i < n; i += 4) {
+        mbar_wait(&bars[i / CH], 0, a.status);
+        const float dsum = warp_sum(dot_slice(wbuf + (size_t)i * I + slice * 1024, x, lane));
+        if (lane == 0) part[i * 3 + slice] = dsum;
+    }
+    __syncthreads();
+    if (tid < n) {
+        const float dn = rbf(part[tid * 3] + part[tid * 3 + 1] + part[tid * 3 + 2]);
+        const unsigned short hb = __ldcg(reinterpret_cast<const unsigned short*>(a.hidden + r0 + tid));
+        const float hres = __uint_as_float((uint32_t)hb << 16);
+        a.hidden[r0 + tid] = __float2bfloat16_rn(hres + dn);
+    }
+}
+
+// ---------------------------------------------------------------- k_lmhead
+// logits[r] = bf16( E[r,:] . rmsnorm(hidden) ); token = lowest index of the maximum.
+// The 311 MB embedding matrix streams through a 4-stage shared-memory ring fed
+// by one producer thread; eight consumer warps take two rows each per stage.
+constexpr int LM_ROWS = 16;
+constexpr int LM_STAGES = 4;
+constexpr int LM_CONSUMERS = 8;
+constexpr int LM_THREADS = (LM_CONSUMERS + 1) * 32;
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+    uint32_t u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (uint32_t)idx);
+}
+
+__global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // [LM_STAGES][LM_ROWS][H]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)LM_STAGES * LM_ROWS * H * 2);
+    uint64_t* empty = full + LM_STAGES;
+    unsigned long long* wbest = reinterpret_cast<unsigned long long*>(empty + LM_STAGES);  // [LM_CONSUMERS]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r0 = (int)(((long long)blockIdx.x * a.vocab) / gridDim.x);
+    const int r1 = (int)(((long long)(blockIdx.x + 1) * a.vocab) / gridDim.x);
+    const int n = r1 - r0;
+    const int nst = (n + LM_ROWS - 1) / LM_ROWS;
+
+    auto issue = [&](int it) {
+        const int s = it % LM_STAGES;
+        const int rows = min(LM_ROWS, n - it * LM_ROWS);
+        const uint32_t bytes = (uint32_t)rows * H * 2;
+        mbar_expect_tx(&full[s], bytes);
+        bulk_g2s(ring + (size_t)s * LM_ROWS * H, a.lm_head + (size_t)(r0 + it * LM_ROWS) * H, bytes, &full[s]);
+    };
+    if (tid == LM_CONSUMERS * 32) {
+        for (int s = 0; s < LM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], LM_CONSUMERS); }
+        mbar_fence_init();
+        for (int it = 0; it < min(nst, LM_STAGES); ++it) issue(it);
+    }
+    __syncthreads();
+    // The trigger comes AFTER the wait: the next decode step may only begin once
+    // every kernel of this step has completed, which makes the KV rows written by
+    // this step safe to prefetch in the next step's attention prologues.
+    pdl_wait();
+    pdl_trigger();
+
+    if (warp == LM_CONSUMERS) {
+        if (lane == 0) {
+            for (int it = LM_STAGES; it < nst; ++it) {
+                const int s = it % LM_STAGES;
+                mbar_wait(&empty[s], (uint32_t)((it / LM_STAGES) - 1) & 1u, a.status);
+                issue(it);
+            }
+        }
+    } else {
+        float x[32];
+        load_x_slice(x, a.hidden, lane);
+        rmsnorm_slice(x, a.final_norm, lane);
+        float bestv = -INFINITY;
+        int besti = 0x7fffffff;
+        for (int it = 0; it < nst; ++it) {
+            const int s = it % LM_STAGES;
+            const int rows = min(LM_ROWS, n - it * LM_ROWS);
+            mbar_wait(&full[s], (uint32_t)(it / LM_STAGES) & 1u, a.status);
+            const bf16* st = ring + (size_t)s * LM_ROWS * H;
+            const int ra = warp, rb = warp + LM_CONSUMERS;
+            float d0 = 0.f, d1 = 0.f;
+            if (ra < rows) d0 = dot_slice(st + (size_t)ra * H, x, lane);
+            if (rb < rows) d1 = dot_slice(st + (size_t)rb * H, x, lane);
+            d0 = rbf(warp_sum(d0));
+            d1 = rbf(warp_sum(d1));
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&empty[s]);
+                const int ga = r0 + it * LM_ROWS + ra, gb = r0 + it * LM_ROWS + rb;
+                if (ra < rows) {
+                    if (a.logits) a.logits[ga] = d0;
+                    if (d0 > bestv) { bestv = d0; besti = ga; }
+                }
+                if (rb < rows) {
+                    if (a.logits) a.logits[gb] = d1;
+                    if (d1 > bestv) { bestv = d1; besti = gb; }
+                }
+            }
+        }
+        if (lane == 0) wbest[warp] = (besti == 0x7fffffff) ? 0ull : argmax_key(bestv, besti);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long k = 0ull;
+        for (int i = 0; i < LM_CONSUMERS; ++i) k = wbest[i] > k ? wbest[i] : k;
+        atomicMax(a.slot, k);
+        __threadfence();
+        const unsigned int t = atomicAdd(&a.counters[NKV], 1u);
+        if (t == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long best = atomicExch(a.slot, 0ull);
+            *a.out_token = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+            a.counters[NKV] = 0u;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- small helpers
+__global__ void k_fill_iota(int* dst, int start, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = start + i;
+}
+
+__global__ void k_find_first_eos(const int* tokens, int n, const int* eos, int n_eos, int* out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int t = tokens[i];
+    for (int j = 0; j < n_eos; ++j)
+        if (t == eos[j]) { atomicMin(out, i); return; }
+}
+
+// ---------------------------------------------------------------- host side
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+};
+static DeviceState g_dev[64];
+
+static size_t smem_qkv() { return (size_t)QKV_MAXROWS * H * 2 + MAX_BARS * 8; }
+static size_t smem_oproj() { return (size_t)O_MAXROWS * QSZ * 2 + MAX_BARS * 8 + O_MAXROWS * 2 * 4; }
+static size_t smem_gateup() { return (size_t)2 * GU_MAXROWS * H * 2 + MAX_BARS * 8; }
+static size_t smem_down() { return (size_t)DN_MAXROWS * I * 2 + MAX_BARS * 8 + DN_MAXROWS * 3 * 4; }
+static size_t smem_lmhead() { return (size_t)LM_STAGES * LM_ROWS * H * 2 + 2 * LM_STAGES * 8 + LM_CONSUMERS * 8; }
+static size_t smem_attn(int cap) { return (size_t)cap * D * 2 * 2 + (size_t)2 * cap * 4 + 2 * D * 4 + 4 * D * 4 + 4 * 4 + 2 * 8; }
+
+constexpr int ATT_MAX_CAP = 384;    // positions per CTA: 384 * 520 B + 3 KB of shared memory
+constexpr int ATT_MAX_SPLIT = 64;
+
+static int attn_nsplit(int max_seq) {
+    int ns = (max_seq + 127) / 128;
+    if (ns < 1) ns = 1;
+    if (ns > ATT_MAX_SPLIT) ns = ATT_MAX_SPLIT;
+    return ns;
+}
+static int attn_cap(int max_seq) {
+    const int ns = attn_nsplit(max_seq);
+    int cap = ((max_seq + ns - 1) / ns + 15) & ~15;
+    if (cap < ATT_MIN_CHUNK) cap = ATT_MIN_CHUNK;
+    return cap;
+}
+
+static int ensure_device(DeviceState** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return MQ_ERR_UNSUPPORTED;
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        cudaDeviceProp p;
+        e = cudaGetDeviceProperties(&p, dev);
+        if (e != cudaSuccess) return (int)e;
+        st.sm_count = p.multiProcessorCount;
+        st.cc_major = p.major;
+        st.cc_minor = p.minor;
+        if (p.major != 10 || st.sm_count < MIN_GRID) return MQ_ERR_UNSUPPORTED;
+#define MQ_SET_SMEM(k, bytes)                                                                   \
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes));     \
+    if (e != cudaSuccess) return (int)e;
+        MQ_SET_SMEM(k_qkv, smem_qkv());
+        MQ_SET_SMEM(k_oproj, smem_oproj());
+        MQ_SET_SMEM(k_gateup, smem_gateup());
+        MQ_SET_SMEM(k_down, smem_down());
+        MQ_SET_SMEM(k_lmhead, smem_lmhead());
+        MQ_SET_SMEM(k_attn, smem_attn(ATT_MAX_CAP));
+#undef MQ_SET_SMEM
+        st.ready = true;
+    }
+    *out = &st;
+    return MQ_OK;
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace mq
+
+using namespace mq;
+
+extern "C" int mq_abi_version(void) { return 1; }
+
+extern "C" int mq_device_info(int* sm_count, int* cc_major, int* cc_minor) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    cudaDeviceProp p;
+    e = cudaGetDeviceProperties(&p, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (sm_count) *sm_count = p.multiProcessorCount;
+    if (cc_major) *cc_major = p.major;
+    if (cc_minor) *cc_minor = p.minor;
+    return MQ_OK;
+}
+
+extern "C" int mq_init_device(void) {
+    DeviceState* st = nullptr;
+    return ensure_device(&st);
+}
+
+extern "C" int mq_decode_attn_nsplit(int max_seq_len) { return attn_nsplit(max_seq_len); }
+
+extern "C" size_t mq_decode_partials_bytes(int max_seq_len) {
+    return (size_t)NQ * attn_nsplit(max_seq_len) * PART_STRIDE * sizeof(float);
+}
+
+extern "C" int mq_decode_launch_count(int num_layers) { return 5 * num_layers + 1; }
+
+extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf, const int* in_token, int* out_token,
+                                const int* position, float* logits, int flags, void* stream_v) {
+    if (!model || !buf || !in_token || !out_token || !position) return MQ_ERR_BAD_ARG;
+    if (!model->embed || !model->layers || !model->final_norm || !model->lm_head || !model->cos_table || !model->sin_table)
+        return MQ_ERR_BAD_ARG;
+    if (model->num_layers <= 0 || model->vocab_size <= 0 || model->max_seq_len <= 0) return MQ_ERR_BAD_ARG;
+    if (!buf->k_cache || !buf->v_cache || !buf->hidden || !buf->qkv || !buf->attn_out || !buf->mlp_act || !buf->attn_partials ||
+        !buf->counters || !buf->argmax_slot || !buf->status)
+        return MQ_ERR_BAD_ARG;
+    const int cap = attn_cap(model->max_seq_len);
+    const int nsplit = attn_nsplit(model->max_seq_len);
+    if (buf->attn_nsplit != nsplit) return MQ_ERR_BAD_ARG;
+    if (cap > ATT_MAX_CAP) return MQ_ERR_TOO_LONG;
+    const void* al[] = {model->embed, model->lm_head, model->final_norm, model->cos_table, model->sin_table, buf->k_cache,
+                        buf->v_cache, buf->hidden, buf->qkv, buf->attn_out, buf->mlp_act};
+    for (const void* p : al)
+        if (!aligned16(p)) return MQ_ERR_ALIGNMENT;
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != MQ_OK) return rc;
+
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    DecodeArgs a;
+    a.embed = (const bf16*)model->embed;
+    a.final_norm = (const bf16*)model->final_norm;
+    a.lm_head = (const bf16*)model->lm_head;
+    a.cos = (const bf16*)model->cos_table;
+    a.sin = (const bf16*)model->sin_table;
+    a.k_cache = (bf16*)buf->k_cache;
+    a.v_cache = (bf16*)buf->v_cache;
+    a.hidden = (bf16*)buf->hidden;
+    a.qkv = (bf16*)buf->qkv;
+    a.attn = (bf16*)buf->attn_out;
+    a.act = (bf16*)buf->mlp_act;
+    a.partials = buf->attn_partials;
+    a.counters = buf->counters;
+    a.slot = buf->argmax_slot;
+    a.status = buf->status;
+    a.in_token = in_token;
+    a.out_token = out_token;
+    a.pos = position;
+    a.logits = logits;
+    a.vocab = model->vocab_size;
+    a.max_seq = model->max_seq_len;
+    a.nsplit = nsplit;
+    a.chunk_cap = cap;
+
+    const bool pdl = !(flags & MQ_FLAG_NO_PDL);
+    const int G = st->sm_count;
+    cudaError_t e;
+    for (int l = 0; l < model->num_layers; ++l) {
+        const MqLayerWeights& w = model->layers[l];
+        const bool first = (l == 0);
+        e = launch(k_qkv, dim3(G), dim3(GEMV_THREADS), smem_qkv(), stream, pdl && (!first || (flags & MQ_FLAG_CHAINED)), a, w, l);
+        if (e != cudaSuccess) return (int)e;
+        e = launch(k_attn, dim3(NKV, nsplit), dim3(ATT_THREADS), smem_attn(cap), stream, pdl, a, w, l);
+        if (e != cudaSuccess) return (int)e;
+        e = launch(k_oproj, dim3(G), dim3(GEMV_THREADS), smem_oproj(), stream, pdl, a, w);
+        if (e != cudaSuccess) return (int)e;
+        e = launch(k_gateup, dim3(G), dim3(GEMV_THREADS), smem_gateup(), stream, pdl, a, w);
+        if (e != cudaSuccess) return (int)e;
+        e = launch(k_down, dim3(G), dim3(DOWN_THREADS), smem_down(), stream, pdl, a, w);
+        if (e != cudaSuccess) return (int)e;
+    }
+    e = launch(k_lmhead, dim3(G), dim3(LM_THREADS), smem_lmhead(), stream, pdl, a);
+    if (e != cudaSuccess) return (int)e;
+    return MQ_OK;
+}
+
+extern "C" int mq_launch_fill_iota(int* dst, int start, int n, void* stream) {
+    if (!dst || n < 0) return MQ_ERR_BAD_ARG;
+    if (n == 0) return MQ_OK;
+    k_fill_iota<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(dst, start, n);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int mq_launch_find_first_eos(const int* tokens, int n, const int* eos_ids, int n_eos, int* out_index, void* stream) {
+    if (!tokens || !out_index || n < 0 || n_eos < 0 || (n_eos > 0 && !eos_ids)) return MQ_ERR_BAD_ARG;
+    if (n == 0 || n_eos == 0) return MQ_OK;
+    k_find_first_eos<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(tokens, n, eos_ids, n_eos, out_index);
+    return (int)cudaGetLastError();
+}

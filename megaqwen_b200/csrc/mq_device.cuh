@@ -1,0 +1,174 @@
+// Device-side building blocks shared by the decode and prefill kernels:
+// bf16 rounding helpers, warp reductions, bounded mbarrier waits, 1-D bulk
+// async copies (TMA, non-multicast) and programmatic-dependent-launch control.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/megaqwen_b200.h"
+
+namespace mq {
+
+constexpr int H = MQ_HIDDEN;
+constexpr int I = MQ_INTERMEDIATE;
+constexpr int NQ = MQ_NUM_Q_HEADS;
+constexpr int NKV = MQ_NUM_KV_HEADS;
+constexpr int D = MQ_HEAD_DIM;
+constexpr int QSZ = MQ_Q_SIZE;
+constexpr int KVSZ = MQ_KV_SIZE;
+constexpr int QKV = QSZ + 2 * KVSZ;
+constexpr float RMS_EPS = 1e-6f;
+
+typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------- rounding
+// Every value that the HuggingFace bf16 model materialises as a tensor is
+// rounded to bf16 here too; these helpers make the rounding points explicit.
+__device__ __forceinline__ float rbf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+__device__ __forceinline__ float bf2f(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&p);
+}
+// silu evaluated in fp32 as x / (1 + exp(-x)), rounded to bf16 by the caller.
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+// ---------------------------------------------------------------- reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---------------------------------------------------------------- loads
+// Activations are rewritten by every kernel of the chain while kernels overlap
+// under programmatic dependent launch, so they are always read through L2
+// (ld.global.cg), never through a possibly stale L1 line.
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint2 ld_cg_u2(const void* p) { return __ldcg(reinterpret_cast<const uint2*>(p)); }
+__device__ __forceinline__ uint32_t ld_cg_u32(const void* p) { return __ldcg(reinterpret_cast<const uint32_t*>(p)); }
+__device__ __forceinline__ int ld_cg_i32(const int* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_cg_f32(const float* p) { return __ldcg(p); }
+
+// ---------------------------------------------------------------- PDL
+// griddepcontrol.wait: block until every grid this one depends on has
+// completed and its memory is visible.  launch_dependents: allow the next
+// kernel of the stream to start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------- mbarrier + bulk copy
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait (about 0.2 s of SM clock).  On expiry the sticky status bit is
+// set and the caller carries on with whatever the buffer holds: the kernel
+// finishes, the host sees the bit at its next status check, and the GPU stays
+// usable.  Once the bit is set every later wait gives up at once, so a broken
+// chain drains in microseconds instead of one timeout per wait.  Returns false
+// if the wait was abandoned.
+constexpr long long WAIT_LIMIT_CYCLES = 400000000LL;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (status && (__ldcg(status) & MQ_STATUS_WAIT_TIMEOUT)) return false;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (status) atomicOr(status, MQ_STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+
+// 1-D bulk async copy global -> this CTA's shared memory, completing `bytes`
+// on `bar`.  Both addresses 16-byte aligned, bytes a multiple of 16.  No
+// cluster multicast.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// ---------------------------------------------------------------- dot products
+// A warp multiplies one 1024-wide slice of a bf16 weight row held in shared
+// memory with a slice of the activation vector held in registers.  Lane l owns
+// columns j*256 + l*8 + e (j < 4, e < 8): each lane reads 16 contiguous bytes,
+// a warp 512 contiguous bytes, so the loads are bank-conflict free.
+__device__ __forceinline__ void load_x_slice(float (&x)[32], const bf16* src, int lane) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint4 u = ld_cg_u4(src + j * 256 + lane * 8);
+        x[j * 8 + 0] = bf_lo(u.x); x[j * 8 + 1] = bf_hi(u.x);
+        x[j * 8 + 2] = bf_lo(u.y); x[j * 8 + 3] = bf_hi(u.y);
+        x[j * 8 + 4] = bf_lo(u.z); x[j * 8 + 5] = bf_hi(u.z);
+        x[j * 8 + 6] = bf_lo(u.w); x[j * 8 + 7] = bf_hi(u.w);
+    }
+}
+
+__device__ __forceinline__ float dot_slice(const bf16* wrow_smem, const float (&x)[32], int lane) {
+    const uint4* w4 = reinterpret_cast<const uint4*>(wrow_smem);
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint4 u = w4[j * 32 + lane];
+        a0 = fmaf(bf_lo(u.x), x[j * 8 + 0], a0); a1 = fmaf(bf_hi(u.x), x[j * 8 + 1], a1);
+        a0 = fmaf(bf_lo(u.y), x[j * 8 + 2], a0); a1 = fmaf(bf_hi(u.y), x[j * 8 + 3], a1);
+        a0 = fmaf(bf_lo(u.z), x[j * 8 + 4], a0); a1 = fmaf(bf_hi(u.z), x[j * 8 + 5], a1);
+        a0 = fmaf(bf_lo(u.w), x[j * 8 + 6], a0); a1 = fmaf(bf_hi(u.w), x[j * 8 + 7], a1);
+    }
+    return a0 + a1;
+}
+
+// RMSNorm of a 1024-wide bf16 vector held as a register slice per lane (every
+// warp holds the whole vector): x <- bf16(w * bf16(x * rsqrt(mean(x^2) + eps))).
+__device__ __forceinline__ void rmsnorm_slice(float (&x)[32], const bf16* w, int lane) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint4 u = *reinterpret_cast<const uint4*>(w + j * 256 + lane * 8);
+        const float wv[8] = {bf_lo(u.x), bf_hi(u.x), bf_lo(u.y), bf_hi(u.y), bf_lo(u.z), bf_hi(u.z), bf_lo(u.w), bf_hi(u.w)};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[j * 8 + e] = rbf(wv[e] * rbf(x[j * 8 + e] * r));
+    }
+}
+
+}  // namespace mq

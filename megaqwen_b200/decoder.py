@@ -1,0 +1,309 @@
+"""Host-side decoder object: the Python mirror of the reference's pybind
+classes ``MegakernelDecoder`` (csrc/megakernel/bindings_decode.cpp:80-280) and
+``MegakernelPrefillDecoder`` (csrc/megakernel/bindings_prefill.cpp:1637-1701),
+with the same constructor arguments, method names, state semantics and error
+texts.  It owns the KV cache, scratch and the position counter as torch CUDA
+tensors (torch is used for device memory, streams and graph capture only) and
+calls the C ABI of libmegaqwen_b200.so for every piece of arithmetic.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import MqDecodeBuffers, MqLayerWeights, MqModel
+
+_HIDDEN, _INTER, _NQ, _NKV, _D = 1024, 3072, 16, 8, 128
+_LAYER_SHAPES = [(_HIDDEN,), (_NQ * _D, _HIDDEN), (_NKV * _D, _HIDDEN), (_NKV * _D, _HIDDEN), (_D,), (_D,),
+                 (_HIDDEN, _NQ * _D), (_HIDDEN,), (_INTER, _HIDDEN), (_INTER, _HIDDEN), (_HIDDEN, _INTER)]
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return t.data_ptr()
+
+
+class MegakernelDecoder:
+    """Batch-1 greedy decoder.
+
+    ``position()`` is the number of tokens consumed.  ``decode_step(t)`` writes
+    K/V at ``position``, attends over ``position + 1`` entries, returns the
+    arg-max next token and increments the position.  ``prefill_step(ids)`` sets
+    ``position = len(ids)`` and returns the token following the prompt.
+    ``reset()`` zeroes the KV cache and the position.
+    """
+
+    def __init__(self, embed_weight, layer_weights, final_norm_weight, lm_head_weight, cos_table, sin_table,
+                 num_layers, max_seq_len, max_prefill_len=512, *w4_args, **w4_kwargs):
+        if not torch.cuda.is_available():
+            raise RuntimeError("megaqwen_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+        self._lib = _lib.lib()
+        for extra in list(w4_args) + list(w4_kwargs.values()):
+            if extra is not None and hasattr(extra, "__len__") and len(extra) > 0:
+                raise RuntimeError("W4 / FP8-KV / paged-KV options are not supported by this engine")
+        if len(layer_weights) != 11 * num_layers:
+            raise RuntimeError(f"layer_weights must hold 11 tensors per layer, got {len(layer_weights)} for {num_layers} layers")
+        self.device = embed_weight.device
+        if self.device.type != "cuda":
+            raise RuntimeError("weights must live on a CUDA device")
+        self.num_layers_ = int(num_layers)
+        self.max_seq_len_ = int(max_seq_len)
+        self.max_prefill_len_ = int(max_prefill_len)
+        self.vocab_size_ = int(embed_weight.shape[0])
+
+        def chk(t, shape, name):
+            if t.dtype != torch.bfloat16 or not t.is_contiguous() or t.device != self.device or tuple(t.shape) != tuple(shape):
+                raise RuntimeError(f"{name}: expected contiguous bf16 {tuple(shape)} on {self.device}, got {t.dtype} {tuple(t.shape)}")
+
+        chk(embed_weight, (self.vocab_size_, _HIDDEN), "embed_weight")
+        chk(lm_head_weight, (self.vocab_size_, _HIDDEN), "lm_head_weight")
+        chk(final_norm_weight, (_HIDDEN,), "final_norm_weight")
+        chk(cos_table, (self.max_seq_len_, _D), "cos_table")
+        chk(sin_table, (self.max_seq_len_, _D), "sin_table")
+        for i, t in enumerate(layer_weights):
+            chk(t, _LAYER_SHAPES[i % 11], f"layer_weights[{i}]")
+        # keep references: the C side only holds raw pointers
+        self._weights = (embed_weight, list(layer_weights), final_norm_weight, lm_head_weight, cos_table, sin_table)
+
+        self._layers = (MqLayerWeights * self.num_layers_)()
+        for l in range(self.num_layers_):
+            for j, (name, _) in enumerate(MqLayerWeights._fields_):
+                setattr(self._layers[l], name, _ptr(layer_weights[11 * l + j]))
+        self._model = MqModel(_ptr(embed_weight), self._layers, _ptr(final_norm_weight), _ptr(lm_head_weight),
+                              _ptr(cos_table), _ptr(sin_table), self.num_layers_, self.vocab_size_, self.max_seq_len_)
+
+        dev = self.device
+        with torch.cuda.device(dev):
+            _lib.check(self._lib.mq_init_device(), "mq_init_device")
+            bf, i32 = torch.bfloat16, torch.int32
+            self.k_cache_ = torch.zeros((self.num_layers_, _NKV, self.max_seq_len_, _D), dtype=bf, device=dev)
+            self.v_cache_ = torch.zeros_like(self.k_cache_)
+            self._hidden = torch.zeros(_HIDDEN, dtype=bf, device=dev)
+            self._qkv = torch.zeros(_NQ * _D + 2 * _NKV * _D, dtype=bf, device=dev)
+            self._attn = torch.zeros(_NQ * _D, dtype=bf, device=dev)
+            self._act = torch.zeros(_INTER, dtype=bf, device=dev)
+            nsplit = self._lib.mq_decode_attn_nsplit(self.max_seq_len_)
+            self._partials = torch.zeros(self._lib.mq_decode_partials_bytes(self.max_seq_len_) // 4, dtype=torch.float32, device=dev)
+            self._counters = torch.zeros(16, dtype=i32, device=dev)
+            self._slot = torch.zeros(1, dtype=torch.int64, device=dev)
+            # [0] = output token of single steps, [1] = sticky status word
+            self._scalars = torch.zeros(4, dtype=i32, device=dev)
+            self._in_token = torch.zeros(1, dtype=i32, device=dev)
+            self._pos_dev = torch.zeros(1, dtype=i32, device=dev)
+            self._logits = None
+            self._chain_cap = 0
+            self._chain_tokens = None
+            self._chain_pos = None
+            self._graphs = {}
+        self._buf = MqDecodeBuffers(_ptr(self.k_cache_), _ptr(self.v_cache_), _ptr(self._hidden), _ptr(self._qkv),
+                                    _ptr(self._attn), _ptr(self._act), _ptr(self._partials), _ptr(self._counters),
+                                    _ptr(self._slot), _ptr(self._scalars) + 4, nsplit)
+        self._pin = torch.zeros(2, dtype=i32).pin_memory()
+        self.position_ = 0
+        self.use_pdl = True
+        self.launches = 0          # kernels launched through the C ABI by this object
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self) -> int:
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _launch(self, in_ptr: int, out_ptr: int, pos_ptr: int, logits_ptr, chained: bool) -> None:
+        flags = (_lib.MQ_FLAG_CHAINED if chained else 0) | (0 if self.use_pdl else _lib.MQ_FLAG_NO_PDL)
+        rc = self._lib.mq_launch_decode(C.byref(self._model), C.byref(self._buf), in_ptr, out_ptr, pos_ptr,
+                                        logits_ptr, flags, self._stream())
+        _lib.check(rc, "mq_launch_decode")
+        self.launches += 5 * self.num_layers_ + 1
+
+    def _check_status(self, status: int) -> None:
+        if status:
+            self._scalars[1] = 0
+            what = []
+            if status & _lib.MQ_STATUS_WAIT_TIMEOUT:
+                what.append("a bounded device-side wait expired")
+            if status & _lib.MQ_STATUS_BAD_POSITION:
+                what.append("position outside the KV cache")
+            if status & _lib.MQ_STATUS_BAD_TOKEN:
+                what.append("token id outside the vocabulary")
+            raise RuntimeError("megaqwen_b200 device status: " + ", ".join(what))
+
+    def check_status(self) -> None:
+        """Read the sticky device status word (one 4-byte copy) and raise if set."""
+        self._check_status(int(self._scalars[1].item()))
+
+    def _ensure_chain(self, n: int) -> None:
+        if n > self._chain_cap:
+            cap = max(n, 64)
+            self._chain_tokens = torch.zeros(cap + 1, dtype=torch.int32, device=self.device)
+            self._chain_pos = torch.zeros(cap, dtype=torch.int32, device=self.device)
+            self._chain_cap = cap
+            self._graphs = {}
+
+    # ------------------------------------------------------------------ reference API
+    def position(self) -> int:
+        return self.position_
+
+    def max_prefill_len(self) -> int:
+        return self.max_prefill_len_
+
+    def get_k_cache(self) -> torch.Tensor:
+        return self.k_cache_
+
+    def get_v_cache(self) -> torch.Tensor:
+        return self.v_cache_
+
+    def reset(self) -> None:
+        self.position_ = 0
+        self.k_cache_.zero_()
+        self.v_cache_.zero_()
+
+    def _single(self, input_token_id: int, logits_ptr) -> int:
+        if self.position_ >= self.max_seq_len_:
+            raise RuntimeError("decode_step would exceed max_seq_len")
+        with torch.cuda.device(self.device):
+            self._pin[0] = int(input_token_id)
+            self._pin[1] = self.position_
+            self._in_token.copy_(self._pin[0:1], non_blocking=True)
+            self._pos_dev.copy_(self._pin[1:2], non_blocking=True)
+            self._launch(_ptr(self._in_token), _ptr(self._scalars), _ptr(self._pos_dev), logits_ptr, False)
+            self.position_ += 1
+            tok, status = self._scalars[:2].tolist()
+        self._check_status(status)
+        return tok
+
+    def decode_step(self, input_token_id: int) -> int:
+        return self._single(input_token_id, None)
+
+    def decode_step_logits(self, input_token_id: int):
+        """One step that also returns the bf16-rounded logits as fp32 [vocab]
+        (reference: launch_ldg_decode_with_logits, chat.py:241-314)."""
+        if self._logits is None:
+            self._logits = torch.empty(self.vocab_size_, dtype=torch.float32, device=self.device)
+        tok = self._single(input_token_id, _ptr(self._logits))
+        return tok, self._logits.clone()
+
+    def _chain(self, first_token, num_steps: int, use_graph: bool) -> torch.Tensor:
+        """Device-resident chain token[i] -> token[i+1]; returns the view of the
+        num_steps generated tokens (cuda int32).  No host synchronisation."""
+        if num_steps <= 0:
+            return torch.empty(0, dtype=torch.int32, device=self.device)
+        if self.position_ + num_steps > self.max_seq_len_:
+            raise RuntimeError("decode_steps would exceed max_seq_len")
+        with torch.cuda.device(self.device):
+            self._ensure_chain(num_steps)
+            tk, ps = self._chain_tokens, self._chain_pos
+            if torch.is_tensor(first_token):
+                tk[0:1].copy_(first_token.reshape(1).to(torch.int32), non_blocking=True)
+            else:
+                self._pin[0] = int(first_token)
+                tk[0:1].copy_(self._pin[0:1], non_blocking=True)
+            _lib.check(self._lib.mq_launch_fill_iota(_ptr(ps), self.position_, num_steps, self._stream()), "mq_launch_fill_iota")
+            self.launches += 1
+            if use_graph:
+                self._replay_graph(num_steps)
+            else:
+                for i in range(num_steps):
+                    self._launch(_ptr(tk) + 4 * i, _ptr(tk) + 4 * (i + 1), _ptr(ps) + 4 * i, None, i > 0)
+            self.position_ += num_steps
+            return tk[1:num_steps + 1]
+
+    def _replay_graph(self, num_steps: int) -> None:
+        g = self._graphs.get(num_steps)
+        tk, ps = self._chain_tokens, self._chain_pos
+        if g is None:
+            g = torch.cuda.CUDAGraph()
+            launches0 = self.launches
+            # capture on a side stream as torch requires; the chain reads tokens[0]
+            # and positions[] which are refreshed before every replay
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                with torch.cuda.graph(g, stream=s):
+                    for i in range(num_steps):
+                        self._launch(_ptr(tk) + 4 * i, _ptr(tk) + 4 * (i + 1), _ptr(ps) + 4 * i, None, i > 0)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            self.launches = launches0
+            self._graphs[num_steps] = g
+        g.replay()
+        self.launches += num_steps * (5 * self.num_layers_ + 1)
+
+    def decode_steps_cuda(self, first_token, num_steps: int) -> torch.Tensor:
+        return self._chain(first_token, num_steps, False).clone()
+
+    def decode_steps_cuda_graph(self, first_token, num_steps: int) -> torch.Tensor:
+        return self._chain(first_token, num_steps, True).clone()
+
+    def decode_steps(self, first_token_id: int, num_steps: int) -> torch.Tensor:
+        out = self._chain(first_token_id, num_steps, True)
+        host = torch.cat([out, self._scalars[1:2]]).cpu()
+        self._check_status(int(host[-1]))
+        return host[:-1]
+
+    def decode_greedy_cuda(self, first_token, max_new_tokens: int, eos_ids=None, chunk: int = 32):
+        """Greedy loop with tokens kept on the device; the EOS scan and one 4-byte
+        read happen once per chunk (reference: bindings_prefill.cpp:1159-1349).
+        Returns (tokens cuda int32[len], len, stop_reason) with stop_reason 0 =
+        max_new_tokens reached, 1 = EOS found (the EOS token is not included)."""
+        eos = None
+        if eos_ids is not None and len(eos_ids) > 0:
+            eos = torch.as_tensor(eos_ids, dtype=torch.int32).to(self.device)
+        outs, total, cur = [], 0, first_token
+        hit = torch.empty(1, dtype=torch.int32, device=self.device)
+        while total < max_new_tokens:
+            n = min(chunk, max_new_tokens - total, self.max_seq_len_ - self.position_)
+            if n <= 0:
+                break
+            toks = self._chain(cur, n, n == chunk).clone()
+            if eos is not None:
+                hit.fill_(n)
+                _lib.check(self._lib.mq_launch_find_first_eos(_ptr(toks), n, _ptr(eos), eos.numel(), _ptr(hit), self._stream()),
+                           "mq_launch_find_first_eos")
+                self.launches += 1
+                idx = int(hit.item())
+                if idx < n:
+                    outs.append(toks[:idx])
+                    total += idx
+                    self.position_ -= n - (idx + 1)
+                    self.check_status()
+                    return torch.cat(outs), total, 1
+            outs.append(toks)
+            total += n
+            cur = toks[-1:]
+        self.check_status()
+        res = torch.cat(outs) if outs else torch.empty(0, dtype=torch.int32, device=self.device)
+        return res, total, 0
+
+    def prefill_step(self, input_ids) -> int:
+        ids = torch.as_tensor(input_ids, dtype=torch.int32).reshape(-1)
+        n = int(ids.numel())
+        if n <= 0:
+            raise RuntimeError("prefill_step: empty input")
+        if n > self.max_prefill_len_:
+            raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
+        if self.position_ + n > self.max_seq_len_:
+            raise RuntimeError("prefill_step would exceed max_seq_len")
+        return self._prefill_by_decode(ids)
+
+    def _prefill_by_decode(self, ids: torch.Tensor) -> int:
+        """Feed the prompt one position at a time through the decode chain, as
+        the reference's decode-only generator does
+        (csrc/megakernel/megakernel_generators.py:29-33)."""
+        n = int(ids.numel())
+        with torch.cuda.device(self.device):
+            self._ensure_chain(n)
+            dev_ids = ids.to(self.device, non_blocking=True)
+            tk, ps = self._chain_tokens, self._chain_pos
+            _lib.check(self._lib.mq_launch_fill_iota(_ptr(ps), self.position_, n, self._stream()), "mq_launch_fill_iota")
+            self.launches += 1
+            for i in range(n):
+                self._launch(_ptr(dev_ids) + 4 * i, _ptr(self._scalars), _ptr(ps) + 4 * i, None, i > 0)
+            self.position_ += n
+            tok, status = self._scalars[:2].tolist()
+        self._check_status(status)
+        return tok
+
+
+# The reference exports the prefill-capable decoder under a second name with the
+# same methods (bindings_prefill.cpp:1637-1701, bindings_fused_prefill.cpp:511-538).
+MegakernelPrefillDecoder = MegakernelDecoder
+MegakernelFusedPrefillDecoder = MegakernelDecoder
