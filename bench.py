@@ -258,6 +258,25 @@ def run_ours(args):
     print(json.dumps(line))
 
 
+def run_ncu_case(args):
+    """Small case for profiler captures: a few eager decode steps at context 2048
+    over a cache filled with random values (no 2048-step prompt before them)."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    from megaqwen_b200.decoder import MegakernelDecoder
+    w = random_weights(QWEN3_0_6B, MAX_SEQ)
+    embed = w["embed_weight"].to(dev)
+    dec = MegakernelDecoder(embed, [t.to(dev) for t in w["layer_weights"]], w["final_norm_weight"].to(dev), embed,
+                            w["cos_table"].to(dev), w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, PROMPT_LEN)
+    dec.k_cache_.normal_(0, 1)
+    dec.v_cache_.normal_(0, 1)
+    dec.position_ = args.ncu_pos
+    toks = dec.decode_steps_cuda(17, args.ncu_case)
+    torch.cuda.synchronize(dev)
+    dec.check_status()
+    print(json.dumps({"ncu_case_steps": args.ncu_case, "position": dec.position(), "tokens": toks.tolist()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -266,8 +285,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunk", type=int, default=32, help="decode steps per CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--ncu-case", type=int, default=0, help="run N eager decode steps at --ncu-pos and exit (profiler case)")
+    ap.add_argument("--ncu-pos", type=int, default=PROMPT_LEN)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.ncu_case > 0:
+        run_ncu_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
