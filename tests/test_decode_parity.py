@@ -70,8 +70,8 @@ def test_tiny_decode_matches_restatement_state(tiny):
     # layer 0 sees identical inputs: at most isolated one-ulp flips
     assert (kd[0] - kr[0]).abs().max() <= 2 ** -6 and ((kd[0] != kr[0]).float().mean() < 2e-2)
     assert (vd[0] - vr[0]).abs().max() <= 2 ** -6 and ((vd[0] != vr[0]).float().mean() < 2e-2)
-    assert (kd - kr).abs().max() <= 6.25e-2 and (kd - kr).abs().mean() <= 2e-3
-    assert (vd - vr).abs().max() <= 6.25e-2 and (vd - vr).abs().mean() <= 2e-3
+    assert (kd - kr).abs().max() <= 6.25e-2 and (kd - kr).abs().mean() <= 4e-3
+    assert (vd - vr).abs().max() <= 6.25e-2 and (vd - vr).abs().mean() <= 4e-3
     # positions never written stay zero
     assert float(dec.get_k_cache()[:, :, n:].abs().max()) == 0.0
 

@@ -42,5 +42,8 @@ def test_restatement_matches_hf_golden_full_cfg1():
 def test_golden_files_are_self_consistent():
     for name in ("tiny_p16_n32", "tiny_p300_n24", "full_cfg1_p16_n64", "full_cfg2_p2048_n256", "full_cfg3_p1024_n32"):
         g = load_golden(name)
-        assert g["top_idx"][:, 0].tolist() == g["tokens"], name
+        # the greedy token carries the maximum logit (ties: any index holding it)
+        for i, t in enumerate(g["tokens"]):
+            holders = g["top_idx"][i][g["top_vals"][i] == g["top_vals"][i, 0]].tolist()
+            assert t in holders, (name, i)
         assert (g["top_vals"][:, 0] >= g["top_vals"][:, 1]).all()
