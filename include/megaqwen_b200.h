@@ -123,6 +123,37 @@ int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf,
                      const int* in_token, int* out_token, const int* position,
                      float* logits, int flags, void* stream);
 
+/* The same decode step for callers that must not allocate device memory.
+ * It has no counterpart in the reference.  Who needs it: a host process that
+ * receives one fixed arena at start-up and may never call cudaMalloc again
+ * (plug-ins of a serving runtime, real-time loops where cudaMalloc's implicit
+ * device-wide synchronisation is not acceptable, processes whose pool belongs
+ * to another component).  Such a caller passes only inputs and outputs - the
+ * model, its KV cache (state, read and written), the token / position scalars,
+ * the optional logits and the status word, all device pointers it already
+ * owns.  The step's scratch (residual stream, q|k|v, attention output, MLP
+ * activation, split-KV partials, tickets, arg-max slot) lives in a static
+ * device array of MQ_NOALLOC_SCRATCH_BYTES inside the library; every GPU that
+ * loads the library holds it until the process exits.
+ *
+ * - model->max_seq_len must not exceed MQ_NOALLOC_MAX_SEQ_LEN, else
+ *   MQ_ERR_TOO_LONG is returned and nothing is launched.
+ * - The call allocates nothing: no cudaMalloc / cudaFree and no allocating
+ *   library routine.  Its first call on each device resolves the array's
+ *   device address (cudaGetSymbolAddress); make that first call, and
+ *   mq_init_device(), before any stream capture.
+ * - All calls on a device share the one array, which keeps the previous call's
+ *   contents; the entry point clears the words that must start at zero on the
+ *   given stream.  Two calls that overlap on the GPU (different streams, or two
+ *   decoders driven concurrently) race on it: serialise them.
+ * - MQ_FLAG_CHAINED is ignored (each step is fully stream-ordered after the
+ *   previous one).  Results are identical to mq_launch_decode. */
+#define MQ_NOALLOC_MAX_SEQ_LEN 8192
+#define MQ_NOALLOC_SCRATCH_BYTES (576 * 1024)
+int mq_launch_decode_noalloc(const MqModel* model, void* k_cache, void* v_cache,
+                             const int* in_token, int* out_token, const int* position,
+                             float* logits, unsigned int* status, int flags, void* stream);
+
 /* dst[i] = start + i.  Replaces launch_ldg_fill_iota
  * (csrc/megakernel/fused_decode_ldg_launch.inl:5-17). */
 int mq_launch_fill_iota(int* dst, int start, int n, void* stream);

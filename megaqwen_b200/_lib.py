@@ -50,6 +50,8 @@ SIGNATURES = {
     "mq_decode_launch_count": (C.c_int, [C.c_int]),
     "mq_launch_decode": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "mq_launch_decode_noalloc": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "mq_launch_fill_iota": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "mq_launch_find_first_eos": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
 }

@@ -788,3 +788,73 @@ extern "C" int mq_launch_find_first_eos(const int* tokens, int n, const int* eos
     k_find_first_eos<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(tokens, n, eos_ids, n_eos, out_index);
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- decode step without allocations
+// Some hosts of this library may not allocate device memory while they serve:
+// a runtime that hands each plug-in a fixed arena at start-up, a real-time loop
+// in which cudaMalloc's implicit device synchronisation is forbidden, or a
+// process whose memory pool is owned by another component.  For them the
+// scratch of one decode step (residual stream, q|k|v, attention output, MLP
+// activation, split-KV partials, tickets and the arg-max slot) lives in this
+// file-scope device array instead of caller-provided buffers.  Every GPU that
+// loads the library holds these bytes until the process exits.
+constexpr size_t NA_HIDDEN_OFF = 0;                                   // bf16 [1024]
+constexpr size_t NA_QKV_OFF = NA_HIDDEN_OFF + (size_t)H * 2;          // bf16 [4096]
+constexpr size_t NA_ATTN_OFF = NA_QKV_OFF + (size_t)QKV * 2;          // bf16 [2048]
+constexpr size_t NA_ACT_OFF = NA_ATTN_OFF + (size_t)QSZ * 2;          // bf16 [3072]
+constexpr size_t NA_PART_OFF = NA_ACT_OFF + (size_t)I * 2;            // fp32 [16 * 64 * 130]
+constexpr size_t NA_PART_BYTES = (size_t)NQ * mq::ATT_MAX_SPLIT * mq::PART_STRIDE * 4;
+constexpr size_t NA_CNT_OFF = NA_PART_OFF + NA_PART_BYTES;            // u32 [16]
+constexpr size_t NA_SLOT_OFF = NA_CNT_OFF + 64;                       // u64 [1]
+constexpr size_t NA_BYTES = NA_SLOT_OFF + 64;
+static_assert(NA_BYTES <= MQ_NOALLOC_SCRATCH_BYTES, "static scratch too small");
+static_assert(NA_QKV_OFF % 16 == 0 && NA_ATTN_OFF % 16 == 0 && NA_ACT_OFF % 16 == 0 && NA_PART_OFF % 16 == 0 &&
+              NA_CNT_OFF % 16 == 0 && NA_SLOT_OFF % 16 == 0, "scratch members must stay 16-byte aligned");
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MQ_NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a
+// device address; the address is looked up once per device, with that device
+// current, and cached here.
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+extern "C" int mq_launch_decode_noalloc(const MqModel* model, void* k_cache, void* v_cache, const int* in_token,
+                                        int* out_token, const int* position, float* logits, unsigned int* status,
+                                        int flags, void* stream_v) {
+    if (!model || !k_cache || !v_cache || !in_token || !out_token || !position || !status) return MQ_ERR_BAD_ARG;
+    if (model->max_seq_len <= 0) return MQ_ERR_BAD_ARG;
+    if (model->max_seq_len > MQ_NOALLOC_MAX_SEQ_LEN) return MQ_ERR_TOO_LONG;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return MQ_ERR_UNSUPPORTED;
+    if (!g_noalloc_ptr[dev]) {
+        // first call on this device: resolve the symbol's device address
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return MQ_ERR_UNSUPPORTED;
+        g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = g_noalloc_ptr[dev];
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    // The tickets and the arg-max slot must start at zero; everything else is
+    // fully rewritten by the step before it is read.
+    e = cudaMemsetAsync(base + NA_CNT_OFF, 0, 128, stream);
+    if (e != cudaSuccess) return (int)e;
+    MqDecodeBuffers buf;
+    buf.k_cache = k_cache;
+    buf.v_cache = v_cache;
+    buf.hidden = base + NA_HIDDEN_OFF;
+    buf.qkv = base + NA_QKV_OFF;
+    buf.attn_out = base + NA_ATTN_OFF;
+    buf.mlp_act = base + NA_ACT_OFF;
+    buf.attn_partials = reinterpret_cast<float*>(base + NA_PART_OFF);
+    buf.counters = reinterpret_cast<unsigned int*>(base + NA_CNT_OFF);
+    buf.argmax_slot = reinterpret_cast<unsigned long long*>(base + NA_SLOT_OFF);
+    buf.status = status;
+    buf.attn_nsplit = mq::attn_nsplit(model->max_seq_len);
+    // The memset above sits between this step and the previous one, so the first
+    // kernel must not be launched as a programmatic dependent of an earlier step.
+    return mq_launch_decode(model, &buf, in_token, out_token, position, logits, flags & ~MQ_FLAG_CHAINED, stream_v);
+}
