@@ -271,7 +271,10 @@ def run_ncu_case(args):
     dec.k_cache_.normal_(0, 1)
     dec.v_cache_.normal_(0, 1)
     dec.position_ = args.ncu_pos
-    toks = dec.decode_steps_cuda(17, args.ncu_case)
+    if args.ncu_persistent:
+        toks = dec.decode_steps_cuda_persistent(17, args.ncu_case)
+    else:
+        toks = dec.decode_steps_cuda(17, args.ncu_case)
     torch.cuda.synchronize(dev)
     dec.check_status()
     print(json.dumps({"ncu_case_steps": args.ncu_case, "position": dec.position(), "tokens": toks.tolist()}))
@@ -287,6 +290,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--ncu-case", type=int, default=0, help="run N eager decode steps at --ncu-pos and exit (profiler case)")
     ap.add_argument("--ncu-pos", type=int, default=PROMPT_LEN)
+    ap.add_argument("--ncu-persistent", action="store_true", help="profiler case runs the persistent chain kernel")
     args = ap.parse_args()
     if args.ncu_case > 0:
         run_ncu_case(args)

@@ -123,6 +123,41 @@ int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf,
                      const int* in_token, int* out_token, const int* position,
                      float* logits, int flags, void* stream);
 
+/* n_steps greedy decode steps in ONE persistent cooperative launch (one CTA per
+ * SM): step i consumes the token produced by step i-1 (step 0: *first_token) at
+ * position *position0 + i and writes its arg-max token to tokens_out[i].  The
+ * device-resident equivalent of the reference's decode_steps_cuda /
+ * decode_greedy_cuda chains (csrc/megakernel/bindings_prefill.cpp:1045-1349),
+ * which launch one cooperative kernel plus two LM-head kernels per token.
+ *   layers_dev  DEVICE copy of the num_layers MqLayerWeights entries
+ *   scratch     mq_chain_scratch_bytes() bytes, 256-byte aligned, zeroed ONCE by
+ *               the caller before the first call and never touched afterwards
+ *               (it carries a phase counter from launch to launch)
+ *   status      sticky MQ_STATUS_* word
+ *   last_logits optional fp32 [vocab]: bf16-rounded logits of the LAST step
+ * model->max_seq_len must not exceed mq_chain_max_seq_len().  Results are
+ * identical to n_steps calls of mq_launch_decode. */
+int mq_launch_decode_chain(const MqModel* model, const MqLayerWeights* layers_dev,
+                           void* k_cache, void* v_cache, void* scratch, unsigned int* status,
+                           const int* first_token, const int* position0, int* tokens_out,
+                           int n_steps, float* last_logits, void* stream);
+size_t mq_chain_scratch_bytes(void);
+int mq_chain_max_seq_len(void);
+/* Instrumentation of mq_launch_decode_chain, the counterpart of the reference's
+ * per-stage clock64 counters (csrc/megakernel/fused_decode_ldg_common.inl:24-69,
+ * debug_ldg_decode_cycles in bindings_prefill.cpp:980-1043).  stage_cycles_dev:
+ * NULL (off) or a device array of 16 u64 per CTA that thread 0 of every CTA fills
+ * with SM cycles spent waiting for: [0] the hidden vector (QKV phase), [1] q|k|v
+ * (attention), [2] attention output, [3] post-attention hidden, [4] MLP
+ * activation, [5] weight pieces from the shared-memory ring; [6] the LM-head
+ * phase; [7] the whole launch; and computing: [8] QKV rows, [9] attention,
+ * [10] O rows, [11] gate/up rows, [12] down rows, [13] the input RMSNorm.  l2_prefetch_ahead: 0/1, whether the producer
+ * prefetches the next layer's weight slices into L2 (default 1). */
+int mq_chain_set_debug(unsigned long long* stage_cycles_dev, int l2_prefetch_ahead);
+/* One-time set-up of the current device for mq_launch_decode_chain (done lazily
+ * by the first launch otherwise). */
+int mq_chain_init_device(void);
+
 /* The same decode step for callers that must not allocate device memory.
  * It has no counterpart in the reference.  Who needs it: a host process that
  * receives one fixed arena at start-up and may never call cudaMalloc again

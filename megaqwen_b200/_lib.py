@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmegaqwen_b200.so")
+LIB_PATH = os.environ.get("MQ_LIB_PATH") or os.path.join(_HERE, "libmegaqwen_b200.so")
 
 MQ_OK = 0
 MQ_ERR = {-1: "bad argument", -2: "sequence too long for the cache or scratch", -3: "unsupported device or geometry",
@@ -52,6 +52,12 @@ SIGNATURES = {
                                    C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "mq_launch_decode_noalloc": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "mq_launch_decode_chain": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "mq_chain_scratch_bytes": (C.c_size_t, []),
+    "mq_chain_max_seq_len": (C.c_int, []),
+    "mq_chain_init_device": (C.c_int, []),
+    "mq_chain_set_debug": (C.c_int, [C.c_void_p, C.c_int]),
     "mq_launch_fill_iota": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "mq_launch_find_first_eos": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
 }

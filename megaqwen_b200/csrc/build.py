@@ -12,8 +12,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-SOURCES = ["decode.cu"]
-OUT = os.path.join(PKG, "libmegaqwen_b200.so")
+SOURCES = ["decode.cu", "decode_chain.cu"]
+OUT = os.environ.get("MQ_LIB_OUT") or os.path.join(PKG, "libmegaqwen_b200.so")
 
 
 def _stale() -> bool:
@@ -33,6 +33,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-shared", "-Xcompiler", "-fPIC", "-o", OUT]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("MQ_NVCC_FLAGS", "").split()
     cmd += [os.path.join(HERE, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:

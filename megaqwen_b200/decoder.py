@@ -92,6 +92,16 @@ class MegakernelDecoder:
             self._in_token = torch.zeros(1, dtype=i32, device=dev)
             self._pos_dev = torch.zeros(1, dtype=i32, device=dev)
             self._logits = None
+            # persistent decode chain: device copy of the layer table + its scratch
+            raw = bytes(self._layers)
+            self._layers_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
+            self._chain_scratch = torch.zeros(self._lib.mq_chain_scratch_bytes(), dtype=torch.uint8, device=dev)
+            # The persistent chain is opt-in: at present the PDL-chained kernels replayed
+            # from a CUDA graph are faster (see profiles/).
+            self.persistent_available = self.max_seq_len_ <= self._lib.mq_chain_max_seq_len()
+            self.use_persistent = False
+            if self.persistent_available:
+                _lib.check(self._lib.mq_chain_init_device(), "mq_chain_init_device")
             self._chain_cap = 0
             self._chain_tokens = None
             self._chain_pos = None
@@ -99,7 +109,6 @@ class MegakernelDecoder:
         self._buf = MqDecodeBuffers(_ptr(self.k_cache_), _ptr(self.v_cache_), _ptr(self._hidden), _ptr(self._qkv),
                                     _ptr(self._attn), _ptr(self._act), _ptr(self._partials), _ptr(self._counters),
                                     _ptr(self._slot), _ptr(self._scalars) + 4, nsplit)
-        self._pin = torch.zeros(2, dtype=i32).pin_memory()
         self.position_ = 0
         self.use_pdl = True
         self.launches = 0          # kernels launched through the C ABI by this object
@@ -161,10 +170,9 @@ class MegakernelDecoder:
         if self.position_ >= self.max_seq_len_:
             raise RuntimeError("decode_step would exceed max_seq_len")
         with torch.cuda.device(self.device):
-            self._pin[0] = int(input_token_id)
-            self._pin[1] = self.position_
-            self._in_token.copy_(self._pin[0:1], non_blocking=True)
-            self._pos_dev.copy_(self._pin[1:2], non_blocking=True)
+            # scalar fills carry the value as a kernel argument: no host buffer to race on
+            self._in_token.fill_(int(input_token_id))
+            self._pos_dev.fill_(self.position_)
             self._launch(_ptr(self._in_token), _ptr(self._scalars), _ptr(self._pos_dev), logits_ptr, False)
             self.position_ += 1
             tok, status = self._scalars[:2].tolist()
@@ -195,8 +203,17 @@ class MegakernelDecoder:
             if torch.is_tensor(first_token):
                 tk[0:1].copy_(first_token.reshape(1).to(torch.int32), non_blocking=True)
             else:
-                self._pin[0] = int(first_token)
-                tk[0:1].copy_(self._pin[0:1], non_blocking=True)
+                tk[0:1].fill_(int(first_token))
+            if self.use_persistent and use_graph is not False:
+                self._pos_dev.fill_(self.position_)
+                rc = self._lib.mq_launch_decode_chain(
+                    C.byref(self._model), _ptr(self._layers_dev), _ptr(self.k_cache_), _ptr(self.v_cache_),
+                    _ptr(self._chain_scratch), _ptr(self._scalars) + 4, _ptr(tk), _ptr(self._pos_dev), _ptr(tk) + 4,
+                    num_steps, None, self._stream())
+                _lib.check(rc, "mq_launch_decode_chain")
+                self.launches += 1
+                self.position_ += num_steps
+                return tk[1:num_steps + 1]
             _lib.check(self._lib.mq_launch_fill_iota(_ptr(ps), self.position_, num_steps, self._stream()), "mq_launch_fill_iota")
             self.launches += 1
             if use_graph:
@@ -231,7 +248,23 @@ class MegakernelDecoder:
         return self._chain(first_token, num_steps, False).clone()
 
     def decode_steps_cuda_graph(self, first_token, num_steps: int) -> torch.Tensor:
-        return self._chain(first_token, num_steps, True).clone()
+        """Per-phase kernels replayed from a CUDA graph (reference:
+        decode_steps_cuda_graph, bindings_prefill.cpp:1082-1150)."""
+        keep, self.use_persistent = self.use_persistent, False
+        try:
+            return self._chain(first_token, num_steps, True).clone()
+        finally:
+            self.use_persistent = keep
+
+    def decode_steps_cuda_persistent(self, first_token, num_steps: int) -> torch.Tensor:
+        """All steps in one persistent cooperative launch."""
+        if not self.persistent_available:
+            raise RuntimeError("persistent decode chain unavailable for this max_seq_len")
+        keep, self.use_persistent = self.use_persistent, True
+        try:
+            return self._chain(first_token, num_steps, True).clone()
+        finally:
+            self.use_persistent = keep
 
     def decode_steps(self, first_token_id: int, num_steps: int) -> torch.Tensor:
         out = self._chain(first_token_id, num_steps, True)
