@@ -189,6 +189,37 @@ int mq_launch_decode_noalloc(const MqModel* model, void* k_cache, void* v_cache,
                              const int* in_token, int* out_token, const int* position,
                              float* logits, unsigned int* status, int flags, void* stream);
 
+/* Caller-owned activation buffers of the prefill path, all bf16, max_tokens rows. */
+typedef struct MqPrefillBuffers {
+    void* h;      /* [max_tokens, 1024] residual stream                    */
+    void* x;      /* [max_tokens, 1024] normalised input of the linears    */
+    void* qkv;    /* [max_tokens, 4096] q | k | v                          */
+    void* attn;   /* [max_tokens, 2048] attention output                   */
+    void* act;    /* [max_tokens, 3072] silu(gate) * up                    */
+    int max_tokens;
+} MqPrefillBuffers;
+
+/* Full-sequence forward of seq_len tokens (device ids) placed at positions
+ * pos0 .. pos0 + seq_len - 1: writes their K/V into dbuf's cache, attends
+ * causally over everything cached so far, and writes the arg-max token that
+ * follows the last one to *out_token (logits: optional fp32 [vocab] of that
+ * row).  bf16 tensors between all ops; the seven linears per layer run on
+ * tcgen05 tensor cores.  Replaces launch_prefill_float
+ * (csrc/megakernel/fused_prefill_launch.inl:71-731). */
+int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pbuf,
+                      const int* ids, int seq_len, int pos0, int* out_token, float* logits, void* stream);
+
+/* Number of kernels one mq_launch_prefill call launches. */
+int mq_prefill_launch_count(int num_layers);
+
+/* C[M,N] = A[M,K] * B[N,K]^T (+ R), bf16 row-major, fp32 accumulation, on the
+ * tcgen05 path; N a multiple of 128, K a multiple of 64, lda/ldc multiples of
+ * 8.  R (optional) has C's shape and leading dimension and may alias C.  The
+ * building block of mq_launch_prefill, exposed for unit tests; the reference
+ * calls cublasGemmEx here (fused_prefill_launch.inl:290-323). */
+int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* C, const void* R,
+                        int M, int N, int K, int ldc, unsigned int* status, void* stream);
+
 /* dst[i] = start + i.  Replaces launch_ldg_fill_iota
  * (csrc/megakernel/fused_decode_ldg_launch.inl:5-17). */
 int mq_launch_fill_iota(int* dst, int start, int n, void* stream);

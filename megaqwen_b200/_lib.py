@@ -40,6 +40,11 @@ class MqDecodeBuffers(C.Structure):
                 ("attn_nsplit", C.c_int)]
 
 
+class MqPrefillBuffers(C.Structure):
+    _fields_ = [("h", C.c_void_p), ("x", C.c_void_p), ("qkv", C.c_void_p), ("attn", C.c_void_p), ("act", C.c_void_p),
+                ("max_tokens", C.c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/megaqwen_b200.h declares.
 SIGNATURES = {
     "mq_abi_version": (C.c_int, []),
@@ -58,6 +63,11 @@ SIGNATURES = {
     "mq_chain_max_seq_len": (C.c_int, []),
     "mq_chain_init_device": (C.c_int, []),
     "mq_chain_set_debug": (C.c_int, [C.c_void_p, C.c_int]),
+    "mq_launch_prefill": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.POINTER(MqPrefillBuffers), C.c_void_p,
+                                    C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mq_prefill_launch_count": (C.c_int, [C.c_int]),
+    "mq_launch_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                      C.c_int, C.c_void_p, C.c_void_p]),
     "mq_launch_fill_iota": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "mq_launch_find_first_eos": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
 }

@@ -672,11 +672,32 @@ static cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Final RMSNorm + LM head + arg-max on buf->hidden (used by the prefill path).
+int launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream);
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace mq
 
 using namespace mq;
+
+int mq::launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream) {
+    DeviceState* st = nullptr;
+    int rc = ensure_device(&st);
+    if (rc != MQ_OK) return rc;
+    DecodeArgs a = {};
+    a.final_norm = (const bf16*)model->final_norm;
+    a.lm_head = (const bf16*)model->lm_head;
+    a.hidden = (bf16*)buf->hidden;
+    a.counters = buf->counters;
+    a.slot = buf->argmax_slot;
+    a.status = buf->status;
+    a.out_token = out_token;
+    a.logits = logits;
+    a.vocab = model->vocab_size;
+    a.max_seq = model->max_seq_len;
+    return (int)launch(k_lmhead, dim3(st->sm_count), dim3(LM_THREADS), smem_lmhead(), stream, false, a);
+}
 
 extern "C" int mq_abi_version(void) { return 1; }
 

@@ -1,0 +1,596 @@
+// Prefill (full-sequence forward) for sm_100a.
+//
+// The reference runs prefill as 7 cuBLAS GEMMs per layer plus ~14 small kernels
+// and a serial-per-warp O(S^2) attention (csrc/megakernel/fused_prefill_launch.inl:71-731,
+// fused_prefill_kernels.inl:3-824).  Here the dense contractions run on the
+// 5th-generation tensor cores directly: one kernel per GEMM that stages both
+// operands with TMA (128-byte swizzle) into a multi-stage shared-memory ring,
+// issues tcgen05.mma from a single elected thread into a TMEM accumulator and
+// drains it with tcgen05.ld in four epilogue warps, with the residual add and
+// the SwiGLU product fused into the epilogue.  Activations are bf16 between
+// all ops (the rounding points of the HF bf16 model, as in the reference's
+// launch_prefill_float).
+//
+// Every mbarrier wait is bounded (mq_device.cuh) and TMEM is always freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "mq_device.cuh"
+
+namespace mq {
+
+// ---------------------------------------------------------------- tcgen05 / TMA primitives
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on `bar` once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes
+// (64 elements) under the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
+    uint64_t d = (uint64_t)((smem_u32(tile) >> 4) & 0x3fffu);
+    d |= 1ull << 16;                 // leading byte offset (unused for swizzled K-major), 16 B units
+    d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+    d |= 1ull << 46;                 // descriptor version (sm_100)
+    d |= 2ull << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+// ---------------------------------------------------------------- GEMM  C[M,N] = A[M,K] * B[N,K]^T
+constexpr int GM_BM = 128;
+constexpr int GM_BK = 64;
+constexpr int GM_THREADS = 192;    // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..5 epilogue
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+
+template <int BN, int EPI>
+struct GemmCfg {
+    static constexpr int NB = (EPI == EPI_SWIGLU) ? 2 : 1;                       // B operands per stage
+    static constexpr int STAGE_BYTES = GM_BM * GM_BK * 2 + NB * BN * GM_BK * 2;
+    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
+    static constexpr int TMEM_COLS = NB * BN;                                    // power of two >= 32
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GM_THREADS, 1)
+k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
+       bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
+    using Cfg = GemmCfg<BN, EPI>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t* empty = full + Cfg::STAGES;
+    uint64_t* accum = empty + Cfg::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int m0 = blockIdx.y * GM_BM, n0 = blockIdx.x * BN;
+    const int nk = K / GM_BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nk; ++kb) {
+                const int s = kb % Cfg::STAGES;
+                if (kb >= Cfg::STAGES) mbar_wait(&empty[s], (uint32_t)((kb / Cfg::STAGES) - 1) & 1u, status);
+                uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
+                mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
+                tma_load_2d(st, &tmA, kb * GM_BK, m0, &full[s]);
+                tma_load_2d(st + GM_BM * GM_BK * 2, &tmB, kb * GM_BK, n0, &full[s]);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + GM_BM * GM_BK * 2 + BN * GM_BK * 2, &tmB2, kb * GM_BK, n0, &full[s]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+            for (int kb = 0; kb < nk; ++kb) {
+                const int s = kb % Cfg::STAGES;
+                mbar_wait(&full[s], (uint32_t)(kb / Cfg::STAGES) & 1u, status);
+                tc_fence_after();
+                uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
+                const uint64_t da = smem_desc_sw128(st);
+                const uint64_t db = smem_desc_sw128(st + GM_BM * GM_BK * 2);
+                const uint64_t db2 = smem_desc_sw128(st + GM_BM * GM_BK * 2 + BN * GM_BK * 2);
+#pragma unroll
+                for (int k = 0; k < GM_BK / 16; ++k) {
+                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);              // +32 bytes per K=16 step
+                    if (EPI == EPI_SWIGLU) umma_bf16(tmem_base + BN, da + 2 * k, db2 + 2 * k, idesc, acc);
+                }
+                umma_commit(&empty[s]);     // frees this stage once the MMAs above have read it
+            }
+            umma_commit(accum);             // accumulator complete
+        }
+        __syncwarp();
+    } else {
+        // epilogue: warp (2..5) owns TMEM lanes 32*(warp%4) .. +31 = tile rows
+        mbar_wait(accum, 0, status);
+        tc_fence_after();
+        const int quarter = warp & 3;
+        const int row = m0 + quarter * 32 + lane;
+        const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(trow + c0, v);
+            uint32_t out[16];
+            if (EPI == EPI_SWIGLU) {
+                uint32_t u[32];
+                tmem_ld32(trow + BN + c0, u);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float g0 = rbf(__uint_as_float(v[2 * j])), g1 = rbf(__uint_as_float(v[2 * j + 1]));
+                    const float u0 = rbf(__uint_as_float(u[2 * j])), u1 = rbf(__uint_as_float(u[2 * j + 1]));
+                    out[j] = pack_bf16x2(rbf(silu_f32(g0)) * u0, rbf(silu_f32(g1)) * u1);
+                }
+            } else if (EPI == EPI_RESID) {
+                if (row < M) {
+                    const uint4* rp = reinterpret_cast<const uint4*>(R + (size_t)row * ldc + n0 + c0);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint4 rr = rp[q];
+                        const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = q * 4 + e;
+                            out[j] = pack_bf16x2(bf_lo(rw[e]) + rbf(__uint_as_float(v[2 * j])), bf_hi(rw[e]) + rbf(__uint_as_float(v[2 * j + 1])));
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) out[j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+            }
+            if (row < M) {
+                uint4* cp = reinterpret_cast<uint4*>(C + (size_t)row * ldc + n0 + c0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) cp[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------- row-wise kernels
+// h[s,:] = embed[ids[s],:]      (reference: prefill_embed_kernel, fused_prefill_kernels.inl:3-20)
+__global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, const bf16* __restrict__ embed, bf16* __restrict__ h,
+                                                  int vocab, unsigned int* status) {
+    const int s = blockIdx.x;
+    int tok = ids[s];
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, MQ_STATUS_BAD_TOKEN);
+        tok = min(max(tok, 0), vocab - 1);
+    }
+    reinterpret_cast<uint4*>(h + (size_t)s * H)[threadIdx.x] = __ldg(reinterpret_cast<const uint4*>(embed + (size_t)tok * H) + threadIdx.x);
+}
+
+// x[s,:] = bf16( w * bf16( h[s,:] * rsqrt(mean(h^2) + eps) ) )   one warp per row
+// (reference: prefill_rmsnorm_kernel, fused_prefill_kernels.inl:52-105)
+__global__ void __launch_bounds__(256) k_pf_rmsnorm(const bf16* __restrict__ h, const bf16* __restrict__ w, bf16* __restrict__ x, int rows) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float v[32];
+    const bf16* src = h + (size_t)row * H;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 u = *reinterpret_cast<const uint4*>(src + j * 256 + lane * 8);
+        v[j * 8 + 0] = bf_lo(u.x); v[j * 8 + 1] = bf_hi(u.x); v[j * 8 + 2] = bf_lo(u.y); v[j * 8 + 3] = bf_hi(u.y);
+        v[j * 8 + 4] = bf_lo(u.z); v[j * 8 + 5] = bf_hi(u.z); v[j * 8 + 6] = bf_lo(u.w); v[j * 8 + 7] = bf_hi(u.w);
+    }
+    rmsnorm_slice(v, w, lane);
+    bf16* dst = x + (size_t)row * H;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint4 o;
+        o.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]); o.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+        o.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]); o.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+        *reinterpret_cast<uint4*>(dst + j * 256 + lane * 8) = o;
+    }
+}
+
+// Per (position, head): q/k heads get RMSNorm(128) * w and split-half RoPE evaluated in
+// bf16; q stays in the qkv buffer, k and v go to the cache at position pos0 + s
+// (reference: prefill_qk_norm_rope_kernel, fused_prefill_kernels.inl:112-258).
+// One warp per head: 16 q + 8 k + 8 v = 32 warps per position.
+__global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, const bf16* __restrict__ wq, const bf16* __restrict__ wk,
+                                                        const bf16* __restrict__ cos, const bf16* __restrict__ sin, bf16* __restrict__ k_cache,
+                                                        bf16* __restrict__ v_cache, int layer, int pos0, int max_seq) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.y * 8 + (threadIdx.x >> 5);   // 0..31
+    const int s = blockIdx.x, pos = pos0 + s;
+    bf16* row = qkv + (size_t)s * QKV;
+    if (unit >= NQ + NKV) {   // V head: raw copy into the cache
+        const int g = unit - NQ - NKV;
+        const uint2 u = *reinterpret_cast<const uint2*>(row + QSZ + KVSZ + g * D + 4 * lane);
+        *reinterpret_cast<uint2*>(v_cache + ((size_t)(layer * NKV + g) * max_seq + pos) * D + 4 * lane) = u;
+        return;
+    }
+    const bool is_q = unit < NQ;
+    bf16* head = is_q ? row + unit * D : row + QSZ + (unit - NQ) * D;
+    const bf16* wn = is_q ? wq : wk;
+    const bf16* cosr = cos + (size_t)pos * D;
+    const bf16* sinr = sin + (size_t)pos * D;
+    const uint32_t ulo = *reinterpret_cast<const uint32_t*>(head + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
+    const float xl[2] = {bf_lo(ulo), bf_hi(ulo)}, xh[2] = {bf_lo(uhi), bf_hi(uhi)};
+    float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+    const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
+    const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
+    const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
+    const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
+    const float clo[2] = {bf_lo(cl), bf_hi(cl)}, chi[2] = {bf_lo(chh), bf_hi(chh)};
+    const float slo[2] = {bf_lo(sl), bf_hi(sl)}, shi[2] = {bf_lo(sh), bf_hi(sh)};
+    float lo[2], hi[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const float nl = rbf(wlo[e] * rbf(xl[e] * r));
+        const float nh = rbf(whi[e] * rbf(xh[e] * r));
+        lo[e] = rbf(rbf(nl * clo[e]) + rbf(-nh * slo[e]));
+        hi[e] = rbf(rbf(nh * chi[e]) + rbf(nl * shi[e]));
+    }
+    const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
+    bf16* dst = is_q ? head : k_cache + ((size_t)(layer * NKV + (unit - NQ)) * max_seq + pos) * D;
+    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = plo;
+    *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = phi;
+}
+
+// ---------------------------------------------------------------- causal GQA attention (prefill)
+// One CTA per (64-query tile, query head); 4 warps x 16 query rows; K/V tiles of 64
+// cached positions.  QK^T and PV run on mma.sync m16n8k16 (bf16 in, fp32 accumulate)
+// with an online softmax in registers; probabilities are rounded to bf16 before
+// the PV product and the row sum uses the unrounded fp32 values.
+// (Reference: prefill_causal_attention_kernel, fused_prefill_kernels.inl:265-342,
+// one warp per (query, head) walking the keys serially.)
+constexpr int FA_BQ = 64, FA_BK = 64, FA_LD = D + 8, FA_THREADS = 128;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const bf16* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                                                            const bf16* __restrict__ v_cache, bf16* __restrict__ out, int S, int pos0,
+                                                            int layer, int max_seq) {
+    extern __shared__ __align__(16) uint8_t fa_smem[];
+    bf16* sq = reinterpret_cast<bf16*>(fa_smem);        // [64][FA_LD]
+    bf16* sk = sq + FA_BQ * FA_LD;                      // [64][FA_LD]
+    bf16* sv = sk + FA_BK * FA_LD;                      // [64][FA_LD]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q0 = blockIdx.x * FA_BQ, head = blockIdx.y, g = head / (NQ / NKV);
+    const bf16* kbase = k_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
+    const bf16* vbase = v_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
+
+    // Q tile -> shared (rows past S are zero)
+    for (int c = tid; c < FA_BQ * (D / 8); c += FA_THREADS) {
+        const int r = c / (D / 8), cc = c % (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (q0 + r < S) v = *reinterpret_cast<const uint4*>(qkv + (size_t)(q0 + r) * QKV + head * D + cc * 8);
+        *reinterpret_cast<uint4*>(sq + r * FA_LD + cc * 8) = v;
+    }
+    __syncthreads();
+    uint32_t qf[8][4];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)
+        ldsm_x4(qf[kk], sq + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * FA_LD + kk * 16 + (lane >> 4) * 8);
+
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
+    const float scale = 0.08838834764831845f;
+    const int row_a = pos0 + q0 + warp * 16 + (lane >> 2);   // absolute position of this thread's first row; second is +8
+    const int kv_end = min(pos0 + S, pos0 + q0 + FA_BQ);     // exclusive bound of keys any row of the tile may see
+    const int ntiles = (kv_end + FA_BK - 1) / FA_BK;
+
+    for (int t = 0; t < ntiles; ++t) {
+        const int p0 = t * FA_BK;
+        __syncthreads();   // previous tile fully consumed
+        for (int c = tid; c < FA_BK * (D / 8); c += FA_THREADS) {
+            const int r = c / (D / 8), cc = c % (D / 8);
+            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+            if (p0 + r < kv_end) {
+                kv4 = *reinterpret_cast<const uint4*>(kbase + (size_t)(p0 + r) * D + cc * 8);
+                vv4 = *reinterpret_cast<const uint4*>(vbase + (size_t)(p0 + r) * D + cc * 8);
+            }
+            *reinterpret_cast<uint4*>(sk + r * FA_LD + cc * 8) = kv4;
+            *reinterpret_cast<uint4*>(sv + r * FA_LD + cc * 8) = vv4;
+        }
+        __syncthreads();
+
+        float sacc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {   // pairs of 8-key tiles
+                uint32_t kf[4];
+                ldsm_x4(kf, sk + (np * 16 + (lane & 7) + (lane >> 4) * 8) * FA_LD + kk * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(sacc[2 * np], qf[kk], kf[0], kf[1]);
+                mma_bf16_16816(sacc[2 * np + 1], qf[kk], kf[2], kf[3]);
+            }
+        }
+        // scale, causal mask, online softmax
+        float mx[2] = {-1e30f, -1e30f};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = p0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const int rowp = row_a + (e >> 1) * 8;
+                const float sv_ = (key <= rowp) ? sacc[nt][e] * scale : -1e30f;
+                sacc[nt][e] = sv_;
+                mx[e >> 1] = fmaxf(mx[e >> 1], sv_);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
+            mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
+            const float m_new = fmaxf(m_run[h2], mx[h2]);
+            corr[h2] = expf(m_run[h2] - m_new);
+            m_run[h2] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+        uint32_t pf[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float pe[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                pe[e] = (sacc[nt][e] <= -1e29f) ? 0.f : expf(sacc[nt][e] - m_run[e >> 1]);
+                rs[e >> 1] += pe[e];
+            }
+            pf[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(pe[0], pe[1]);
+            pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(pe[2], pe[3]);
+        }
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            rs[h2] += __shfl_xor_sync(0xffffffffu, rs[h2], 1);
+            rs[h2] += __shfl_xor_sync(0xffffffffu, rs[h2], 2);
+            l_run[h2] = l_run[h2] * corr[h2] + rs[h2];
+        }
+#pragma unroll
+        for (int dt = 0; dt < 16; ++dt) { o[dt][0] *= corr[0]; o[dt][1] *= corr[0]; o[dt][2] *= corr[1]; o[dt][3] *= corr[1]; }
+        // O += P V
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {          // 16 keys per step
+#pragma unroll
+            for (int dp = 0; dp < 8; ++dp) {   // pairs of 8-wide output tiles
+                uint32_t vf[4];
+                ldsm_x4_t(vf, sv + (j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * FA_LD + dp * 16 + (lane >> 4) * 8);
+                mma_bf16_16816(o[2 * dp], pf[j], vf[0], vf[1]);
+                mma_bf16_16816(o[2 * dp + 1], pf[j], vf[2], vf[3]);
+            }
+        }
+    }
+    // normalise and store
+    const int r_lo = q0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+#pragma unroll
+    for (int dt = 0; dt < 16; ++dt) {
+        const int col = head * D + dt * 8 + (lane & 3) * 2;
+        if (r_lo < S) *reinterpret_cast<uint32_t*>(out + (size_t)r_lo * QSZ + col) = pack_bf16x2(o[dt][0] * inv0, o[dt][1] * inv0);
+        if (r_hi < S) *reinterpret_cast<uint32_t*>(out + (size_t)r_hi * QSZ + col) = pack_bf16x2(o[dt][2] * inv1, o[dt][3] * inv1);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct MapKey {
+    const void* ptr; uint64_t rows, cols, ld; uint32_t box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        h ^= k.rows * 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h ^= k.cols * 0xc2b2ae3d27d4eb4full + (h << 6) + (h >> 2);
+        h ^= (k.ld * 31 + k.box_rows) + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+static std::mutex g_map_mu;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static EncodeTiledFn g_encode = nullptr;
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with leading dimension ld
+// (elements); box = 64 columns x box_rows rows, 128-byte swizzle, zero fill
+// outside the matrix.  Maps are cached: weight matrices never move.
+static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return (int)e;
+        if (!fn || qres != cudaDriverEntryPointSuccess) return MQ_ERR_UNSUPPORTED;
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const MapKey key{ptr, rows, cols, ld, box_rows};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return MQ_OK; }
+    if (g_maps.size() > 4096) g_maps.clear();
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {GM_BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return MQ_ERR_BAD_ARG;
+    g_maps.emplace(key, m);
+    *out = m;
+    return MQ_OK;
+}
+
+template <int BN, int EPI>
+static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf16* C, const bf16* R, int M, int N, int K, int ldc,
+                       unsigned int* status, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN, EPI>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_set[dev] = true;
+    }
+    if (N % BN != 0 || K % GM_BK != 0) return MQ_ERR_BAD_ARG;
+    CUtensorMap ma, mb, mb2;
+    int rc = get_map(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GM_BM, &ma);
+    if (rc != MQ_OK) return rc;
+    rc = get_map(B, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, &mb);
+    if (rc != MQ_OK) return rc;
+    mb2 = mb;
+    if (EPI == EPI_SWIGLU) {
+        rc = get_map(B2, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, &mb2);
+        if (rc != MQ_OK) return rc;
+    }
+    dim3 grid(N / BN, (M + GM_BM - 1) / GM_BM);
+    k_gemm<BN, EPI><<<grid, GM_THREADS, Cfg::SMEM, stream>>>(ma, mb, mb2, C, R, M, N, K, ldc, status);
+    return (int)cudaGetLastError();
+}
+
+// defined in decode.cu: final RMSNorm + LM head + arg-max on buf->hidden
+int launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream);
+
+__global__ void k_pf_copy_row(const bf16* __restrict__ src, bf16* __restrict__ dst) {
+    reinterpret_cast<uint4*>(dst)[threadIdx.x] = reinterpret_cast<const uint4*>(src)[threadIdx.x];
+}
+
+}  // namespace mq
+
+using namespace mq;
+
+extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 10 + 2; }
+
+// C[M,N] = A[M,K] * B[N,K]^T on the tcgen05 path (bf16 in/out, fp32 accumulate);
+// optional residual R (same shape and leading dimension as C, may alias C).
+extern "C" int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* C, const void* R, int M, int N, int K, int ldc,
+                                   unsigned int* status, void* stream) {
+    if (!A || !B || !C || !status || M <= 0 || N <= 0 || K <= 0) return MQ_ERR_BAD_ARG;
+    if (lda % 8 != 0 || ldc % 8 != 0) return MQ_ERR_ALIGNMENT;
+    if (R) return launch_gemm<128, EPI_RESID>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, (const bf16*)R, M, N, K, ldc, status, (cudaStream_t)stream);
+    return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream);
+}
+
+extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,
+                                 int seq_len, int pos0, int* out_token, float* logits, void* stream_v) {
+    if (!model || !dbuf || !pb || !ids || !out_token) return MQ_ERR_BAD_ARG;
+    if (!pb->h || !pb->x || !pb->qkv || !pb->attn || !pb->act) return MQ_ERR_BAD_ARG;
+    if (seq_len <= 0 || pos0 < 0) return MQ_ERR_BAD_ARG;
+    if (seq_len > pb->max_tokens || pos0 + seq_len > model->max_seq_len) return MQ_ERR_TOO_LONG;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    const int S = seq_len;
+    bf16* h = (bf16*)pb->h; bf16* x = (bf16*)pb->x; bf16* qkv = (bf16*)pb->qkv; bf16* attn = (bf16*)pb->attn; bf16* act = (bf16*)pb->act;
+    unsigned int* status = dbuf->status;
+    static bool fa_attr[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const size_t fa_smem = (size_t)(FA_BQ + 2 * FA_BK) * FA_LD * 2;
+    if (dev >= 0 && dev < 64 && !fa_attr[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_pf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem);
+        if (e != cudaSuccess) return (int)e;
+        fa_attr[dev] = true;
+    }
+    k_pf_embed<<<S, 128, 0, stream>>>(ids, (const bf16*)model->embed, h, model->vocab_size, status);
+    int rc;
+    for (int l = 0; l < model->num_layers; ++l) {
+        const MqLayerWeights& w = model->layers[l];
+        k_pf_rmsnorm<<<(S + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.input_layernorm, x, S);
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, nullptr, qkv, nullptr, S, QSZ, H, QKV, status, stream);
+        if (rc) return rc;
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.k_proj, nullptr, qkv + QSZ, nullptr, S, KVSZ, H, QKV, status, stream);
+        if (rc) return rc;
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.v_proj, nullptr, qkv + QSZ + KVSZ, nullptr, S, KVSZ, H, QKV, status, stream);
+        if (rc) return rc;
+        k_pf_qknorm_rope<<<dim3(S, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+                                                         (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
+                                                         model->max_seq_len);
+        k_pf_attention<<<dim3((S + FA_BQ - 1) / FA_BQ, NQ), FA_THREADS, fa_smem, stream>>>(qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
+                                                                                          attn, S, pos0, l, model->max_seq_len);
+        rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
+        if (rc) return rc;
+        k_pf_rmsnorm<<<(S + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.post_attn_layernorm, x, S);
+        rc = launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
+        if (rc) return rc;
+        rc = launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream);
+        if (rc) return rc;
+    }
+    // last row -> decode hidden buffer, then the decode path's LM head + arg-max
+    k_pf_copy_row<<<1, H / 8, 0, stream>>>(h + (size_t)(S - 1) * H, (bf16*)dbuf->hidden);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    return launch_lmhead_only(model, dbuf, out_token, logits, stream);
+}

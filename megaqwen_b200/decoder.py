@@ -13,7 +13,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import MqDecodeBuffers, MqLayerWeights, MqModel
+from ._lib import MqDecodeBuffers, MqLayerWeights, MqModel, MqPrefillBuffers
 
 _HIDDEN, _INTER, _NQ, _NKV, _D = 1024, 3072, 16, 8, 128
 _LAYER_SHAPES = [(_HIDDEN,), (_NQ * _D, _HIDDEN), (_NKV * _D, _HIDDEN), (_NKV * _D, _HIDDEN), (_D,), (_D,),
@@ -92,6 +92,9 @@ class MegakernelDecoder:
             self._in_token = torch.zeros(1, dtype=i32, device=dev)
             self._pos_dev = torch.zeros(1, dtype=i32, device=dev)
             self._logits = None
+            self._pf = None            # prefill activation buffers, allocated at the first prefill
+            self._pf_tensors = None
+            self.use_gemm_prefill = True
             # persistent decode chain: device copy of the layer table + its scratch
             raw = bytes(self._layers)
             self._layers_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
@@ -315,7 +318,48 @@ class MegakernelDecoder:
             raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
         if self.position_ + n > self.max_seq_len_:
             raise RuntimeError("prefill_step would exceed max_seq_len")
+        if self.use_gemm_prefill:
+            return self._prefill_gemm(ids)
         return self._prefill_by_decode(ids)
+
+    def _prefill_gemm(self, ids: torch.Tensor, want_logits: bool = False):
+        """Full-sequence forward on the tcgen05 GEMM path (mq_launch_prefill)."""
+        n = int(ids.numel())
+        with torch.cuda.device(self.device):
+            if self._pf is None or self._pf.max_tokens < n:
+                cap = max(n, self.max_prefill_len_)
+                bf = torch.bfloat16
+                t = [torch.empty((cap, w), dtype=bf, device=self.device) for w in (_HIDDEN, _HIDDEN, _NQ * _D + 2 * _NKV * _D, _NQ * _D, _INTER)]
+                self._pf_tensors = t
+                self._pf = MqPrefillBuffers(_ptr(t[0]), _ptr(t[1]), _ptr(t[2]), _ptr(t[3]), _ptr(t[4]), cap)
+            dev_ids = ids.to(self.device, non_blocking=True)
+            logits_ptr = None
+            if want_logits:
+                if self._logits is None:
+                    self._logits = torch.empty(self.vocab_size_, dtype=torch.float32, device=self.device)
+                logits_ptr = _ptr(self._logits)
+            rc = self._lib.mq_launch_prefill(C.byref(self._model), C.byref(self._buf), C.byref(self._pf), _ptr(dev_ids), n,
+                                             self.position_, _ptr(self._scalars), logits_ptr, self._stream())
+            _lib.check(rc, "mq_launch_prefill")
+            self.launches += self._lib.mq_prefill_launch_count(self.num_layers_)
+            self.position_ += n
+            tok, status = self._scalars[:2].tolist()
+        self._check_status(status)
+        if want_logits:
+            return tok, self._logits.clone()
+        return tok
+
+    def prefill_step_logits(self, input_ids):
+        """prefill_step that also returns the fp32 logits of the last prompt position."""
+        ids = torch.as_tensor(input_ids, dtype=torch.int32).reshape(-1)
+        n = int(ids.numel())
+        if n <= 0:
+            raise RuntimeError("prefill_step: empty input")
+        if n > self.max_prefill_len_:
+            raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
+        if self.position_ + n > self.max_seq_len_:
+            raise RuntimeError("prefill_step would exceed max_seq_len")
+        return self._prefill_gemm(ids, want_logits=True)
 
     def _prefill_by_decode(self, ids: torch.Tensor) -> int:
         """Feed the prompt one position at a time through the decode chain, as
