@@ -268,6 +268,15 @@ def run_ncu_case(args):
     embed = w["embed_weight"].to(dev)
     dec = MegakernelDecoder(embed, [t.to(dev) for t in w["layer_weights"]], w["final_norm_weight"].to(dev), embed,
                             w["cos_table"].to(dev), w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, PROMPT_LEN)
+    if args.ncu_prefill > 0:
+        prompt = random_prompt(QWEN3_0_6B, args.ncu_prefill, 3, 0)
+        tok = None
+        for _ in range(args.ncu_case):
+            dec.reset()
+            tok = dec.prefill_step(prompt)
+        torch.cuda.synchronize(dev)
+        print(json.dumps({"ncu_prefill_tokens": args.ncu_prefill, "repeats": args.ncu_case, "next_token": tok}))
+        return
     dec.k_cache_.normal_(0, 1)
     dec.v_cache_.normal_(0, 1)
     dec.position_ = args.ncu_pos
@@ -290,6 +299,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--ncu-case", type=int, default=0, help="run N eager decode steps at --ncu-pos and exit (profiler case)")
     ap.add_argument("--ncu-pos", type=int, default=PROMPT_LEN)
+    ap.add_argument("--ncu-prefill", type=int, default=0, help="profiler case: N prefills of this many tokens instead of decode steps")
     ap.add_argument("--ncu-persistent", action="store_true", help="profiler case runs the persistent chain kernel")
     args = ap.parse_args()
     if args.ncu_case > 0:
