@@ -209,6 +209,31 @@ typedef struct MqPrefillBuffers {
 int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pbuf,
                       const int* ids, int seq_len, int pos0, int* out_token, float* logits, void* stream);
 
+/* State and scratch of a batch of independent sequences (no counterpart in the
+ * reference, which is batch-1 only).  Sequence b owns the cache slice
+ * [b][num_layers, 8, max_seq_len, 128]; a prefill of sequence b is an
+ * mq_launch_prefill call whose MqDecodeBuffers point at that slice. */
+typedef struct MqBatchBuffers {
+    void* k_cache;            /* bf16 [batch, num_layers, 8, max_seq_len, 128] */
+    void* v_cache;
+    int* positions;           /* device int32 [batch]: tokens consumed per sequence */
+    void* logits;             /* bf16 [batch, vocab] scratch                    */
+    MqPrefillBuffers act;     /* activation buffers, max_tokens >= batch        */
+    unsigned int* status;
+    int batch;
+} MqBatchBuffers;
+
+/* One greedy decode step for every sequence of the batch: sequence b consumes
+ * in_tokens[b] at position positions[b] (its K/V are written there), attends
+ * over its own positions[b] + 1 cached entries and out_tokens[b] receives the
+ * arg-max token; positions[b] is incremented on the device, so steps chain
+ * without host work.  The linears run as M = batch GEMMs on tcgen05 (weights
+ * are read once per step for the whole batch).  logits_f32: optional fp32
+ * [batch, vocab].  vocab must be a multiple of 128. */
+int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens,
+                           int* out_tokens, float* logits_f32, void* stream);
+int mq_decode_batch_launch_count(int num_layers);
+
 /* Number of kernels one mq_launch_prefill call launches. */
 int mq_prefill_launch_count(int num_layers);
 

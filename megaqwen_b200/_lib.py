@@ -45,6 +45,11 @@ class MqPrefillBuffers(C.Structure):
                 ("max_tokens", C.c_int)]
 
 
+class MqBatchBuffers(C.Structure):
+    _fields_ = [("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("positions", C.c_void_p), ("logits", C.c_void_p),
+                ("act", MqPrefillBuffers), ("status", C.c_void_p), ("batch", C.c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/megaqwen_b200.h declares.
 SIGNATURES = {
     "mq_abi_version": (C.c_int, []),
@@ -65,6 +70,9 @@ SIGNATURES = {
     "mq_chain_set_debug": (C.c_int, [C.c_void_p, C.c_int]),
     "mq_launch_prefill": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.POINTER(MqPrefillBuffers), C.c_void_p,
                                     C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mq_launch_decode_batch": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers), C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_void_p]),
+    "mq_decode_batch_launch_count": (C.c_int, [C.c_int]),
     "mq_prefill_launch_count": (C.c_int, [C.c_int]),
     "mq_launch_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                       C.c_int, C.c_void_p, C.c_void_p]),

@@ -249,10 +249,15 @@ __global__ void __launch_bounds__(256) k_pf_rmsnorm(const bf16* __restrict__ h, 
 // One warp per head: 16 q + 8 k + 8 v = 32 warps per position.
 __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, const bf16* __restrict__ wq, const bf16* __restrict__ wk,
                                                         const bf16* __restrict__ cos, const bf16* __restrict__ sin, bf16* __restrict__ k_cache,
-                                                        bf16* __restrict__ v_cache, int layer, int pos0, int max_seq) {
+                                                        bf16* __restrict__ v_cache, int layer, int pos0, int max_seq,
+                                                        const int* __restrict__ pos_rows, size_t seq_stride) {
+    // pos_rows == nullptr: one sequence, row s sits at position pos0 + s.
+    // pos_rows != nullptr: row s is sequence s at position pos_rows[s]; its cache starts s * seq_stride elements in.
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.y * 8 + (threadIdx.x >> 5);   // 0..31
-    const int s = blockIdx.x, pos = pos0 + s;
+    const int s = blockIdx.x;
+    const int pos = pos_rows ? min(max(pos_rows[s], 0), max_seq - 1) : pos0 + s;
+    if (pos_rows) { k_cache += (size_t)s * seq_stride; v_cache += (size_t)s * seq_stride; }
     bf16* row = qkv + (size_t)s * QKV;
     if (unit >= NQ + NKV) {   // V head: raw copy into the cache
         const int g = unit - NQ - NKV;
@@ -531,6 +536,130 @@ __global__ void k_pf_copy_row(const bf16* __restrict__ src, bf16* __restrict__ d
 
 }  // namespace mq
 
+namespace mq {
+
+// ---------------------------------------------------------------- batched decode (one new token per sequence)
+// Attention of sequence b's new token over its own cache: one CTA per
+// (sequence, kv head); the two query heads of the kv head share the K/V stream.
+// Each warp walks positions warp*4 + 32*i .. with an online softmax of its own;
+// the eight warps are merged through shared memory.
+__global__ void __launch_bounds__(256) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                                                      const bf16* __restrict__ v_cache, bf16* __restrict__ out,
+                                                      const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
+    __shared__ float s_m[8][2], s_l[8][2], s_acc[8][2][D];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x, g = blockIdx.y;
+    const int pos = min(max(positions[b], 0), max_seq - 1);
+    const int len = pos + 1;
+    const bf16* kb = k_cache + (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
+    const bf16* vb = v_cache + (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
+    const bf16* qrow = qkv + (size_t)b * QKV + 2 * g * D;
+    const int psub = lane >> 3, prt = lane & 7;
+    float q0[16], q1[16];
+    {
+        const uint4 a0 = *reinterpret_cast<const uint4*>(qrow + prt * 8), a1 = *reinterpret_cast<const uint4*>(qrow + 64 + prt * 8);
+        const uint4 b0 = *reinterpret_cast<const uint4*>(qrow + D + prt * 8), b1 = *reinterpret_cast<const uint4*>(qrow + D + 64 + prt * 8);
+        const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { q0[2 * e] = bf_lo(wa[e]); q0[2 * e + 1] = bf_hi(wa[e]); q1[2 * e] = bf_lo(wb[e]); q1[2 * e + 1] = bf_hi(wb[e]); }
+    }
+    const float scale = 0.08838834764831845f;
+    float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p4 = warp * 4; p4 < len; p4 += 32) {
+        const int p = p4 + psub;
+        float s0 = 0.f, s1 = 0.f;
+        if (p < len) {
+            const uint4 ua = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + prt * 8);
+            const uint4 ub = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + 64 + prt * 8);
+            const uint32_t wk[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float klo = bf_lo(wk[e]), khi = bf_hi(wk[e]);
+                s0 = fmaf(klo, q0[2 * e], s0); s0 = fmaf(khi, q0[2 * e + 1], s0);
+                s1 = fmaf(klo, q1[2 * e], s1); s1 = fmaf(khi, q1[2 * e + 1], s1);
+            }
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        }
+        s0 = (p < len) ? s0 * scale : -1e30f;
+        s1 = (p < len) ? s1 * scale : -1e30f;
+        float sj0[4], sj1[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { sj0[j] = __shfl_sync(0xffffffffu, s0, j * 8); sj1[j] = __shfl_sync(0xffffffffu, s1, j * 8); }
+        const float mn0 = fmaxf(m0, fmaxf(fmaxf(sj0[0], sj0[1]), fmaxf(sj0[2], sj0[3])));
+        const float mn1 = fmaxf(m1, fmaxf(fmaxf(sj1[0], sj1[1]), fmaxf(sj1[2], sj1[3])));
+        const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+        m0 = mn0; m1 = mn1;
+        l0 *= c0; l1 *= c1;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (p4 + j < len) {
+                const float e0 = expf(sj0[j] - m0), e1 = expf(sj1[j] - m1);
+                l0 += e0; l1 += e1;
+                const float pb0 = rbf(e0), pb1 = rbf(e1);
+                const uint2 uv = *reinterpret_cast<const uint2*>(vb + (size_t)(p4 + j) * D + lane * 4);
+                const float vv[4] = {bf_lo(uv.x), bf_hi(uv.x), bf_lo(uv.y), bf_hi(uv.y)};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { acc0[e] = fmaf(pb0, vv[e], acc0[e]); acc1[e] = fmaf(pb1, vv[e], acc1[e]); }
+            }
+        }
+    }
+    if (lane == 0) { s_m[warp][0] = m0; s_m[warp][1] = m1; s_l[warp][0] = l0; s_l[warp][1] = l1; }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { s_acc[warp][0][lane * 4 + e] = acc0[e]; s_acc[warp][1][lane * 4 + e] = acc1[e]; }
+    __syncthreads();
+    const int hh = tid >> 7, d = tid & 127;
+    float M = -1e30f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) M = fmaxf(M, s_m[w8][hh]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) {
+        const float f = expf(s_m[w8][hh] - M);
+        den = fmaf(s_l[w8][hh], f, den);
+        num = fmaf(s_acc[w8][hh][d], f, num);
+    }
+    out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den);
+}
+
+// out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
+__global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restrict__ logits, int vocab, int* __restrict__ out_tokens,
+                                                            int* __restrict__ positions, float* __restrict__ logits_f32) {
+    __shared__ unsigned long long s_best[32];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const bf16* row = logits + (size_t)b * vocab;
+    unsigned long long best = 0ull;
+    for (int i = tid; i < vocab; i += blockDim.x) {
+        const float v = bf2f(row[i]);
+        if (logits_f32) logits_f32[(size_t)b * vocab + i] = v;
+        uint32_t u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        const unsigned long long key = ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i);
+        best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((tid & 31) == 0) s_best[tid >> 5] = best;
+    __syncthreads();
+    if (tid == 0) {
+        for (int i = 1; i < (int)(blockDim.x >> 5); ++i) best = s_best[i] > best ? s_best[i] : best;
+        out_tokens[b] = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
+        positions[b] += 1;
+    }
+}
+
+}  // namespace mq
+
 using namespace mq;
 
 extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 10 + 2; }
@@ -577,7 +706,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         if (rc) return rc;
         k_pf_qknorm_rope<<<dim3(S, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
-                                                         model->max_seq_len);
+                                                         model->max_seq_len, nullptr, 0);
         k_pf_attention<<<dim3((S + FA_BQ - 1) / FA_BQ, NQ), FA_THREADS, fa_smem, stream>>>(qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
                                                                                           attn, S, pos0, l, model->max_seq_len);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
@@ -593,4 +722,51 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     return launch_lmhead_only(model, dbuf, out_token, logits, stream);
+}
+
+extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
+
+extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens, int* out_tokens,
+                                      float* logits_f32, void* stream_v) {
+    if (!model || !bb || !in_tokens || !out_tokens) return MQ_ERR_BAD_ARG;
+    if (!bb->k_cache || !bb->v_cache || !bb->positions || !bb->logits || !bb->status) return MQ_ERR_BAD_ARG;
+    const MqPrefillBuffers* pb = &bb->act;
+    if (!pb->h || !pb->x || !pb->qkv || !pb->attn || !pb->act) return MQ_ERR_BAD_ARG;
+    const int B = bb->batch;
+    if (B <= 0 || B > pb->max_tokens) return MQ_ERR_BAD_ARG;
+    if (model->vocab_size % 128 != 0) return MQ_ERR_UNSUPPORTED;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    bf16* h = (bf16*)pb->h; bf16* x = (bf16*)pb->x; bf16* qkv = (bf16*)pb->qkv; bf16* attn = (bf16*)pb->attn; bf16* act = (bf16*)pb->act;
+    unsigned int* status = bb->status;
+    const size_t seq_stride = (size_t)model->num_layers * NKV * model->max_seq_len * D;
+    k_pf_embed<<<B, 128, 0, stream>>>(in_tokens, (const bf16*)model->embed, h, model->vocab_size, status);
+    int rc;
+    for (int l = 0; l < model->num_layers; ++l) {
+        const MqLayerWeights& w = model->layers[l];
+        k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.input_layernorm, x, B);
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, nullptr, qkv, nullptr, B, QSZ, H, QKV, status, stream);
+        if (rc) return rc;
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.k_proj, nullptr, qkv + QSZ, nullptr, B, KVSZ, H, QKV, status, stream);
+        if (rc) return rc;
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.v_proj, nullptr, qkv + QSZ + KVSZ, nullptr, B, KVSZ, H, QKV, status, stream);
+        if (rc) return rc;
+        k_pf_qknorm_rope<<<dim3(B, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+                                                         (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
+                                                         model->max_seq_len, bb->positions, seq_stride);
+        k_bd_attention<<<dim3(B, NKV), 256, 0, stream>>>(qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
+                                                         model->max_seq_len, seq_stride);
+        rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
+        if (rc) return rc;
+        k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.post_attn_layernorm, x, B);
+        rc = launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, B, I, H, I, status, stream);
+        if (rc) return rc;
+        rc = launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, B, H, I, H, status, stream);
+        if (rc) return rc;
+    }
+    k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)model->final_norm, x, B);
+    rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
+                                     model->vocab_size, status, stream);
+    if (rc) return rc;
+    k_bd_argmax_advance<<<B, 1024, 0, stream>>>((const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, logits_f32);
+    return (int)cudaGetLastError();
 }
