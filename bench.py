@@ -80,30 +80,7 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def dist_env():
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
-
-
-def init_dist(world):
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # control plane only (start barrier, max of the timings): CPU tensors over gloo
-        dist.init_process_group("gloo")
-        return dist
-    return None
-
-
-def barrier_max(dist, values):
-    """Max over ranks of a list of floats (identity when single-process)."""
-    if dist is None:
-        return values
-    t = torch.tensor(values, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return t.tolist()
+from megaqwen_b200.replicas import aggregate_throughput, barrier, dist_env, init_control_plane, max_over_ranks  # noqa: E402
 
 
 def cpu_reference(sample_new: int, threads: int | None = None):
@@ -155,7 +132,7 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist = init_dist(world)
+    dist = init_control_plane(world)
     from megaqwen_b200.decoder import MegakernelDecoder
 
     w = random_weights(QWEN3_0_6B, MAX_SEQ)
@@ -205,8 +182,7 @@ def run_ours(args):
 
     for _ in range(args.warmup):
         one_step(False)
-    if dist is not None:
-        dist.barrier()
+    barrier(dist)
     torch.cuda.synchronize(dev)
     sampler = ClockSampler(local)
     sampler.start()
@@ -216,16 +192,15 @@ def run_ours(args):
         a, b, c, l = one_step(True)
         dev_ms.append(a); e2e_ms.append(b); pre_ms.append(c); launches += l
     torch.cuda.synchronize(dev)
-    if dist is not None:
-        dist.barrier()
+    barrier(dist)
     wall = time.perf_counter() - wall0
     clocks = sampler.stop()
-    tot_dev, tot_e2e, tot_pre = barrier_max(dist, [sum(dev_ms), sum(e2e_ms), sum(pre_ms)])
+    tot_dev, tot_e2e, tot_pre = max_over_ranks(dist, [sum(dev_ms), sum(e2e_ms), sum(pre_ms)])
     if rank != 0:
         return
     n_tok = NEW_TOKENS * args.steps * world
-    value = n_tok / (tot_dev / 1e3)
-    e2e = n_tok / (tot_e2e / 1e3)
+    value = aggregate_throughput(NEW_TOKENS * args.steps, world, tot_dev / 1e3)
+    e2e = aggregate_throughput(NEW_TOKENS * args.steps, world, tot_e2e / 1e3)
     peak, peak_kind = load_peaks()
     # algorithmic bytes of the decode steps of one pass: cache length after step i is 2048 + i + 1
     bytes_pass = sum(QWEN3_0_6B.decode_bytes(PROMPT_LEN + i + 1) for i in range(NEW_TOKENS))
@@ -268,6 +243,21 @@ def run_ncu_case(args):
     embed = w["embed_weight"].to(dev)
     dec = MegakernelDecoder(embed, [t.to(dev) for t in w["layer_weights"]], w["final_norm_weight"].to(dev), embed,
                             w["cos_table"].to(dev), w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, PROMPT_LEN)
+    if args.ncu_batch > 0:
+        from megaqwen_b200.batch import MegakernelBatchDecoder
+        del dec
+        B = args.ncu_batch
+        bd = MegakernelBatchDecoder(embed, [t.to(dev) for t in w["layer_weights"]], w["final_norm_weight"].to(dev), embed,
+                                    w["cos_table"].to(dev), w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, B, 64)
+        first = bd.prefill_batch([random_prompt(QWEN3_0_6B, 16, 5, i) for i in range(B)])
+        bd.k_cache_.normal_(0, 1)
+        bd.v_cache_.normal_(0, 1)
+        bd._positions[:B].fill_(args.ncu_pos)
+        out = bd.decode_batch_steps(first, args.ncu_case, use_graph=False)
+        torch.cuda.synchronize(dev)
+        bd.check_status()
+        print(json.dumps({"ncu_batch": B, "steps": args.ncu_case, "position": args.ncu_pos, "tokens": out[-1][:4].tolist()}))
+        return
     if args.ncu_prefill > 0:
         prompt = random_prompt(QWEN3_0_6B, args.ncu_prefill, 3, 0)
         tok = None
@@ -300,6 +290,7 @@ def main():
     ap.add_argument("--ncu-case", type=int, default=0, help="run N eager decode steps at --ncu-pos and exit (profiler case)")
     ap.add_argument("--ncu-pos", type=int, default=PROMPT_LEN)
     ap.add_argument("--ncu-prefill", type=int, default=0, help="profiler case: N prefills of this many tokens instead of decode steps")
+    ap.add_argument("--ncu-batch", type=int, default=0, help="profiler case: batched decode steps with this batch size")
     ap.add_argument("--ncu-persistent", action="store_true", help="profiler case runs the persistent chain kernel")
     args = ap.parse_args()
     if args.ncu_case > 0:
