@@ -249,7 +249,8 @@ def run_ncu_case(args):
         B = args.ncu_batch
         bd = MegakernelBatchDecoder(embed, [t.to(dev) for t in w["layer_weights"]], w["final_norm_weight"].to(dev), embed,
                                     w["cos_table"].to(dev), w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, B, 64)
-        first = bd.prefill_batch([random_prompt(QWEN3_0_6B, 16, 5, i) for i in range(B)])
+        first = random_prompt(QWEN3_0_6B, B, 5, 0)
+        bd.batch_ = B                      # no prefill: the caches are filled with random values below
         bd.k_cache_.normal_(0, 1)
         bd.v_cache_.normal_(0, 1)
         bd._positions[:B].fill_(args.ncu_pos)

@@ -221,6 +221,8 @@ typedef struct MqBatchBuffers {
     MqPrefillBuffers act;     /* activation buffers, max_tokens >= batch        */
     unsigned int* status;
     int batch;
+    float* partials;          /* optional fp32 scratch of the split-K path (batch <= 64):        */
+    size_t partials_bytes;    /* at least 4 * batch * 6144 * 4 bytes; NULL = 128-row tile GEMMs  */
 } MqBatchBuffers;
 
 /* One greedy decode step for every sequence of the batch: sequence b consumes

@@ -59,6 +59,8 @@ class MegakernelBatchDecoder:
             self._counters = torch.zeros(16, dtype=i32, device=dev)
             self._slot = torch.zeros(1, dtype=torch.int64, device=dev)
             self._tok_a = torch.zeros(B, dtype=i32, device=dev)
+            self._partials = torch.empty(4 * min(B, 64) * 2 * _INTER, dtype=torch.float32, device=dev)
+            self.use_splitk = True
             self._chain = None
             self._graphs = {}
         self.batch_ = 0
@@ -70,7 +72,8 @@ class MegakernelBatchDecoder:
 
     def _bb(self, batch: int) -> MqBatchBuffers:
         return MqBatchBuffers(_ptr(self.k_cache_), _ptr(self.v_cache_), _ptr(self._positions), _ptr(self._logits),
-                              self._pf, _ptr(self._scalars) + 4, batch)
+                              self._pf, _ptr(self._scalars) + 4, batch,
+                              _ptr(self._partials) if self.use_splitk else None, self._partials.numel() * 4)
 
     def check_status(self) -> None:
         st = int(self._scalars[1].item())

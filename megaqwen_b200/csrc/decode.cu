@@ -200,8 +200,10 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     const int pos = ld_cg_i32(a.pos);
     const bool valid = pos >= 0 && pos < a.max_seq;
     const int len = pos + 1;
+    // one CTA per kv head while the context fits its shared memory (no split, no merge);
+    // beyond that the positions are spread evenly over the splits
     int chunk = (len + a.nsplit - 1) / a.nsplit;
-    chunk = max(ATT_MIN_CHUNK, (chunk + 15) & ~15);
+    chunk = (len <= cap) ? cap : max(ATT_MIN_CHUNK, (chunk + 15) & ~15);
     const int n_act = valid ? (len + chunk - 1) / chunk : 0;
     const bool active = s < n_act && chunk <= cap;
     if (valid && chunk > cap && tid == 0) atomicOr(a.status, MQ_STATUS_BAD_POSITION);
@@ -337,14 +339,38 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    float M = -INFINITY;
-    for (int j = 0; j < n_act; ++j) M = fmaxf(M, ld_cg_f32(a.partials + ((size_t)qhead * a.nsplit + j) * PART_STRIDE));
-    float num = 0.f, den = 0.f;
-    for (int j = 0; j < n_act; ++j) {
-        const float* pj = a.partials + ((size_t)qhead * a.nsplit + j) * PART_STRIDE;
-        const float f = expf(ld_cg_f32(pj) - M);
-        den = fmaf(ld_cg_f32(pj + 1), f, den);
-        num = fmaf(ld_cg_f32(pj + 2 + d), f, num);
+    // Merge of the n_act (<= 64) partials of this thread's head.  (m, l) of split
+    // lane and lane + 32 are fetched by one load each per lane, the accumulator
+    // column in batches of eight independent loads: the merge costs a few L2
+    // round trips instead of one per split.
+    const int lane_m = tid & 31;
+    float mj[2] = {-INFINITY, -INFINITY}, lj[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+        const int j = lane_m + 32 * h2;
+        if (j < n_act) {
+            const float* pj = a.partials + ((size_t)qhead * a.nsplit + j) * PART_STRIDE;
+            mj[h2] = ld_cg_f32(pj);
+            lj[h2] = ld_cg_f32(pj + 1);
+        }
+    }
+    const float M = warp_max(fmaxf(mj[0], mj[1]));
+    float fj[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) fj[h2] = (lane_m + 32 * h2 < n_act) ? expf(mj[h2] - M) : 0.f;
+    const float den = warp_sum(lj[0] * fj[0] + lj[1] * fj[1]);
+    float num = 0.f;
+    for (int j0 = 0; j0 < n_act; j0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            v[e] = (j0 + e < n_act) ? ld_cg_f32(a.partials + ((size_t)qhead * a.nsplit + j0 + e) * PART_STRIDE + 2 + d) : 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int j = j0 + e;
+            const float f0 = __shfl_sync(0xffffffffu, fj[0], j & 31), f1 = __shfl_sync(0xffffffffu, fj[1], j & 31);
+            num = fmaf(v[e], (j < 32) ? f0 : f1, num);
+        }
     }
     a.attn[qhead * D + d] = __float2bfloat16_rn(num / den);
     if (tid == 0) a.counters[g] = 0u;

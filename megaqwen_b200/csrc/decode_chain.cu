@@ -69,6 +69,8 @@ constexpr int CH_MAX_SPLIT = 16;                          // 8 kv heads x 16 spl
 constexpr int CH_MAX_CAP = 192;                           // positions per attention CTA
 constexpr int CH_MIN_CHUNK = 64;
 constexpr int CH_PART = D + 2;
+constexpr int CH_REP = 1;                                 // replicas of every exchanged vector (readers per line / 16)
+constexpr int CH_XWORDS = H + QKV + QSZ + H + I;          // tagged words per replica
 
 struct ChainArgs {
     const bf16* embed;
@@ -126,8 +128,13 @@ __device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned l
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 // value must already be exactly representable in bf16
+// Every value is stored into all CH_REP replicas of the exchange buffers (CTA c reads
+// replica c % CH_REP).  Measured on B200: 16 replicas did not shorten the polls and the
+// extra stores cost more than they saved, so one replica is used.
 __device__ __forceinline__ void publish(uint32_t* dst, int idx, float v, uint32_t tag16) {
-    st_relaxed_u32(dst + idx, (__float_as_uint(v) & 0xffff0000u) | tag16);
+    const uint32_t wv = (__float_as_uint(v) & 0xffff0000u) | tag16;
+#pragma unroll
+    for (int r = 0; r < CH_REP; ++r) st_relaxed_u32(dst + (size_t)r * CH_XWORDS + idx, wv);
 }
 __device__ __forceinline__ void publish_f32(unsigned long long* dst, size_t idx, float v, uint32_t tag32) {
     st_relaxed_u64(dst + idx, ((unsigned long long)tag32 << 32) | (unsigned long long)__float_as_uint(v));
@@ -185,12 +192,26 @@ __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" 
 
 // Gather a tagged vector of `nwords` (multiple of 4) into shared memory as bf16.
 __device__ __forceinline__ void poll_vector(Poller& po, const uint32_t* src, int nwords, uint32_t tag16, bf16* dst, int ctid) {
-    for (int c = ctid; c < nwords / 4; c += CH_CONSUMERS) {
-        const uint4 v = po.words4(src + 4 * c, tag16);
-        uint2 o;
-        o.x = (v.x >> 16) | (v.y & 0xffff0000u);
-        o.y = (v.z >> 16) | (v.w & 0xffff0000u);
-        *reinterpret_cast<uint2*>(dst + 4 * c) = o;
+    // up to three 16-byte chunks per thread (3072 words / 256 threads): all loads are
+    // issued before the first tag check, stale chunks are then re-polled one by one
+    const int nch = nwords / 4;
+    uint4 v[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        const int c = ctid + k * CH_CONSUMERS;
+        if (c < nch) v[k] = ld_relaxed_v4(src + 4 * c);
+    }
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        const int c = ctid + k * CH_CONSUMERS;
+        if (c < nch) {
+            const bool ok = ((v[k].x & 0xffffu) == tag16) & ((v[k].y & 0xffffu) == tag16) & ((v[k].z & 0xffffu) == tag16) & ((v[k].w & 0xffffu) == tag16);
+            if (!ok) v[k] = po.words4(src + 4 * c, tag16);
+            uint2 o;
+            o.x = (v[k].x >> 16) | (v[k].y & 0xffff0000u);
+            o.y = (v[k].z >> 16) | (v[k].w & 0xffff0000u);
+            *reinterpret_cast<uint2*>(dst + 4 * c) = o;
+        }
     }
 }
 
@@ -497,8 +518,8 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                     }
                     if (ap.active && ap.n_cached > 0) {   // K chunk pieces, then V chunk pieces
                         const size_t head_off = ((size_t)(l * NKV + ge.att_g) * a.max_seq + ap.c0) * D;
-                        // rows written by earlier steps of this launch came from other SMs' generic stores
-                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                        // rows written by earlier steps of this launch were stored by other SMs, which
+                        // fenced them (__threadfence) a full layer pass before this copy is issued
                         for (int kv = 0; kv < 2; ++kv)
                             for (int p0 = 0; p0 < ap.n_cached; p0 += PR_KV) {
                                 const int rows = min(PR_KV, ap.n_cached - p0);
@@ -550,7 +571,13 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
     }
 
     // ============================================================== consumers
-    const int ctid = tid;   // 0..383
+    const int ctid = tid;   // 0..255
+    const size_t rofs = (size_t)(cta % CH_REP) * CH_XWORDS;   // this CTA's replica of the exchanged vectors
+    const uint32_t* rxh = a.xh + rofs;
+    const uint32_t* rxqkv = a.xqkv + rofs;
+    const uint32_t* rxattn = a.xattn + rofs;
+    const uint32_t* rxh1 = a.xh1 + rofs;
+    const uint32_t* rxact = a.xact + rofs;
     Poller po{a.status, false, (a.exp_flags & 2) != 0};
     po.refresh();
     RingCursor rc{0u, 0u};
@@ -585,9 +612,12 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
     // stage timers (thread 0 of each CTA): 0 poll A, 1 poll B, 2 poll C, 3 poll D, 4 poll E, 5 weights, 6 lm, 7 total
     // accumulated in shared memory so that they cost no registers
     unsigned long long* tacc = reinterpret_cast<unsigned long long*>(s_layers + CH_MAX_LAYERS);   // [16]
-    if (ctid == 0) for (int i = 0; i < 16; ++i) tacc[i] = 0ull;
+    unsigned long long* ttrace = tacc + 16;   // [64] phase time stamps of step 2, layers 0..2 (cycles since the step began)
+    if (ctid == 0) for (int i = 0; i < 80; ++i) tacc[i] = 0ull;
+    long long t_step = 0;
     const bool timing = a.dbg != nullptr && ctid == 0;
     const long long t_begin = clock64();
+#define TRACE(i) do { if (timing && step == 20 && l >= 10 && l < 13) ttrace[(l - 10) * 20 + (i)] = (unsigned long long)(clock64() - t_step); } while (0)
 #define TSTART() long long _t0 = timing ? clock64() : 0
 #ifdef MQ_CHAIN_FINE_TIMERS
 #define TSTART2() long long _t1 = timing ? clock64() : 0
@@ -630,6 +660,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
         const int pos = pos0 + step;
         const AttPlan ap = att_plan(ge, pos, a.nsplit, (a.exp_flags & 4) != 0);
         if (ctid < ge.on) resid = bf2f(a.embed[(size_t)token * H + ge.o0 + ctid]);
+        if (timing && step == 20) t_step = clock64();
 
         for (int l = 0; l < L; ++l) {
             const MqLayerWeights w = s_layers[l];
@@ -637,6 +668,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
             float x[32];
 
             // ---------------- phase A: RMSNorm + QKV rows
+            TRACE(0);
             {
                 bf16* xb = xbuf + xsel * I; xsel ^= 1;
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -649,7 +681,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 } else {
                     TSTART();
                     if (has) {
-                        const uint4 u = po.words4(a.xh + 4 * ctid, tag16_of(step, l - 1));
+                        const uint4 u = po.words4(rxh + 4 * ctid, tag16_of(step, l - 1));
                         v[0] = bf_hi(u.x); v[1] = bf_hi(u.y); v[2] = bf_hi(u.z); v[3] = bf_hi(u.w);
                     }
                     TSTOP(0);
@@ -661,6 +693,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 single_release(kn);
                 load_x_smem<4>(x, xb, lane);
                 TSTOP2(13);
+                TRACE(1);
             }
             {
                 TSTART2();
@@ -687,6 +720,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 }
                 pieces_release(P);
                 TSTOP2(8);
+                TRACE(2);
             }
 
             // ---------------- phase B: attention item (g, s)
@@ -700,7 +734,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                     if (ctid < 128) {
                         const int which = ctid >> 5, c = ctid & 31;
                         const int base = which < 2 ? (2 * g + which) * D : (which == 2 ? QSZ + g * D : QSZ + KVSZ + g * D);
-                        const uint4 v = po.words4(a.xqkv + base + 4 * c, t16);
+                        const uint4 v = po.words4(rxqkv + base + 4 * c, t16);
                         uint2 o;
                         o.x = (v.x >> 16) | (v.y & 0xffff0000u);
                         o.y = (v.z >> 16) | (v.w & 0xffff0000u);
@@ -709,6 +743,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                     consumer_bar();
                     TSTOP(1);
                 }
+                TRACE(3);
                 // constants piece (q_norm | k_norm | cos | sin), then K and V pieces: placed now to
                 // keep the cursor in step with the producer, waited for where they are needed
                 const uint32_t kc = rc.seg;
@@ -747,6 +782,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 }
                 single_release(kc);
                 consumer_bar();
+                TRACE(4);
                 // scores: 8 lanes per position, 4 positions per warp pass
                 {
                     const int psub = lane >> 3, prt = lane & 7;
@@ -781,6 +817,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 }
                 if (ap.n_cached > 0) pieces_release(PK);
                 consumer_bar();
+                TRACE(5);
                 if (warp < 2) {
                     float* srow = sc + warp * CH_MAX_CAP;
                     float m = -INFINITY;
@@ -796,6 +833,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                     if (lane == 0) { ml[warp * 2] = m; ml[warp * 2 + 1] = lsum; }
                 }
                 consumer_bar();
+                TRACE(6);
                 {   // PV: thread = (head, half of the positions, pair of dims)
                     const int hh = ctid >> 7, third = (ctid >> 6) & 1, dp = ctid & 63;   // two halves of the positions
                     const int nt = (n + 1) / 2;
@@ -820,6 +858,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 }
                 if (ap.n_cached > 0) pieces_release(PV);
                 consumer_bar();
+                TRACE(7);
                 if (ctid < 2 * D) {
                     const int hh = ctid >> 7, d = ctid & 127;
                     const float acc = accb[(hh * 2) * D + d] + accb[(hh * 2 + 1) * D + d];
@@ -866,12 +905,15 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 }
                 if (ap.is_last) __threadfence();   // new K/V rows must be visible to later bulk copies
                 TSTOP2(9);
+                TRACE(8);
             }
 
             // ---------------- phase C: Wo rows + residual
             {
                 bf16* xb = xbuf + xsel * I; xsel ^= 1;
-                { TSTART(); poll_vector(po, a.xattn, QSZ, t16, xb, ctid); consumer_bar(); TSTOP(2); }
+                TRACE(9);
+                { TSTART(); poll_vector(po, rxattn, QSZ, t16, xb, ctid); consumer_bar(); TSTOP(2); }
+                TRACE(10);
                 TSTART2();
                 const int half = warp & 1;
                 load_x_smem<4>(x, xb + half * 1024, lane);
@@ -903,6 +945,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                     publish(a.xh1, ge.o0 + ctid, resid, t16);
                 }
                 TSTOP2(10);
+                TRACE(11);
             }
 
             // ---------------- phase D: RMSNorm + gate/up rows + SiLU*up
@@ -913,7 +956,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 {
                     TSTART();
                     if (has) {
-                        const uint4 u = po.words4(a.xh1 + 4 * ctid, t16);
+                        const uint4 u = po.words4(rxh1 + 4 * ctid, t16);
                         v[0] = bf_hi(u.x); v[1] = bf_hi(u.y); v[2] = bf_hi(u.z); v[3] = bf_hi(u.w);
                     }
                     TSTOP(3);
@@ -924,6 +967,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 coop_rmsnorm_store(v, has, reinterpret_cast<const bf16*>(ring + noff), xb, red, ctid, lane, warp);
                 single_release(kn);
                 load_x_smem<4>(x, xb, lane);
+                TRACE(12);
                 const Pieces P = place_pieces(rc, ge.gn, PR_GU, 2 * H * 2);
                 // pairs i = warp, warp + 8, warp + 16: rows {gate_i, up_i} x 3
                 const bf16* rows[6];
@@ -954,12 +998,14 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 }
                 pieces_release(P);
                 TSTOP2(11);
+                TRACE(13);
             }
 
             // ---------------- phase E: Wd rows + residual
             {
                 bf16* xb = xbuf + xsel * I; xsel ^= 1;
-                { TSTART(); poll_vector(po, a.xact, I, t16, xb, ctid); consumer_bar(); TSTOP(4); }
+                { TSTART(); poll_vector(po, rxact, I, t16, xb, ctid); consumer_bar(); TSTOP(4); }
+                TRACE(14);
                 TSTART2();
                 // K = 3072 in four quarters of 768 columns: warp = (row group, quarter)
                 const int quarter = warp & 3;
@@ -993,6 +1039,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                     publish(a.xh, ge.o0 + ctid, resid, t16);
                 }
                 TSTOP2(12);
+                TRACE(15);
             }
         }
 
@@ -1005,7 +1052,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
                 const bool has = ctid < H / 4;
                 if (has) {
-                    const uint4 u = po.words4(a.xh + 4 * ctid, tag16_of(step, L - 1));
+                    const uint4 u = po.words4(rxh + 4 * ctid, tag16_of(step, L - 1));
                     v[0] = bf_hi(u.x); v[1] = bf_hi(u.y); v[2] = bf_hi(u.z); v[3] = bf_hi(u.w);
                 }
                 uint32_t kn;
@@ -1086,9 +1133,10 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
     }
     if (timing) {
         tacc[7] = (unsigned long long)(clock64() - t_begin);
-        for (int i = 0; i < 16; ++i) a.dbg[(size_t)cta * 16 + i] = tacc[i];
+        for (int i = 0; i < 80; ++i) a.dbg[(size_t)cta * 80 + i] = tacc[i];
     }
 #undef TSTART
+#undef TRACE
 #undef TSTART2
 #undef TSTOP2
 #undef TSTOP
@@ -1098,7 +1146,7 @@ __global__ void __launch_bounds__(CH_THREADS, 1) k_decode_chain(ChainArgs a) {
 }
 
 static size_t chain_smem_bytes() {
-    return (size_t)CH_RING_BYTES + 2 * I * 2 + (2 * CH_MAX_CAP + 2 * D + 6 * D + 4 + 32 + 16) * 4 + CH_CONSUMER_WARPS * 8 + 2 * CH_NB * 8 + 16 + CH_MAX_LAYERS * sizeof(MqLayerWeights) + 16 * 8;
+    return (size_t)CH_RING_BYTES + 2 * I * 2 + (2 * CH_MAX_CAP + 2 * D + 6 * D + 4 + 32 + 16) * 4 + CH_CONSUMER_WARPS * 8 + 2 * CH_NB * 8 + 16 + CH_MAX_LAYERS * sizeof(MqLayerWeights) + 16 * 8 + 64 * 8;
 }
 
 static int chain_nsplit(int max_seq) {
@@ -1160,7 +1208,7 @@ extern "C" int mq_chain_max_seq_len(void) { return CH_MAX_SPLIT * CH_MAX_CAP; }
 extern "C" size_t mq_chain_scratch_bytes(void) {
     // tagged vectors + split partials + per-CTA maxima + epoch word, each 256-byte aligned
     size_t n = 0;
-    n += (size_t)(H + QKV + QSZ + H + I) * 4;
+    n += (size_t)CH_REP * CH_XWORDS * 4;
     n = (n + 255) & ~(size_t)255;
     n += (size_t)NQ * CH_MAX_SPLIT * CH_PART * 8;
     n = (n + 255) & ~(size_t)255;
@@ -1201,7 +1249,7 @@ extern "C" int mq_launch_decode_chain(const MqModel* model, const MqLayerWeights
     a.xattn = a.xqkv + QKV;
     a.xh1 = a.xattn + QSZ;
     a.xact = a.xh1 + H;
-    size_t off = ((size_t)(H + QKV + QSZ + H + I) * 4 + 255) & ~(size_t)255;
+    size_t off = ((size_t)CH_REP * CH_XWORDS * 4 + 255) & ~(size_t)255;
     a.xpart = reinterpret_cast<unsigned long long*>(s + off);
     off = (off + (size_t)NQ * CH_MAX_SPLIT * CH_PART * 8 + 255) & ~(size_t)255;
     a.xlm = reinterpret_cast<unsigned long long*>(s + off);

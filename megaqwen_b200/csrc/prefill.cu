@@ -205,6 +205,152 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+// ---------------------------------------------------------------- skinny GEMM for M <= 64 (batched decode)
+// With a handful of activation rows the linears are weight-streaming problems: a
+// 128-row output tile per CTA gives 8-48 CTAs, each latency-bound on its own TMA
+// ring.  Here the operands are swapped (the 128 weight rows of a tile are the MMA's
+// M dimension, the batch is its N) and K is split across CTAs, so every GEMM
+// spreads over roughly all SMs and each CTA has its whole K slice in flight at
+// once.  Each CTA writes an fp32 partial tile part[ks][b][n]; the consumer kernels
+// below sum the K splits in a fixed order (deterministic) and apply the bf16
+// rounding, residual, norm or SwiGLU.
+constexpr int SK_MAXKB = 6;       // k-blocks (64 columns) per CTA, all in flight
+
+template <int MPAD>
+__global__ void __launch_bounds__(GM_THREADS, 1)
+k_gemm_skinny(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW2,
+              int tiles0, int tiles1, const __grid_constant__ CUtensorMap tmX, float* __restrict__ part, int M, int ldp,
+              int kb_per_cta, unsigned int* status) {
+    // Up to three weight matrices are concatenated along the output dimension (q|k|v,
+    // gate|up): tile blockIdx.x belongs to matrix 0, 1 or 2; ldp is the row length of
+    // one partial plane part[ks] = [M, ldp].
+    constexpr int W_BYTES = 128 * GM_BK * 2, X_BYTES = MPAD * GM_BK * 2;
+    constexpr int TM_COLS = MPAD < 32 ? 32 : MPAD;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* xs = smem + SK_MAXKB * W_BYTES;                               // X tiles, each 1024-byte aligned
+    constexpr int X_STRIDE = (X_BYTES + 1023) & ~1023;
+    uint64_t* full = reinterpret_cast<uint64_t*>(xs + SK_MAXKB * X_STRIDE);
+    uint64_t* accum = full + SK_MAXKB;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tile = blockIdx.x, ks = blockIdx.y;
+    const int kb0 = ks * kb_per_cta;
+    const CUtensorMap* tmW = tile < tiles0 ? &tmW0 : (tile < tiles0 + tiles1 ? &tmW1 : &tmW2);
+    const int wrow0 = (tile < tiles0 ? tile : (tile < tiles0 + tiles1 ? tile - tiles0 : tile - tiles0 - tiles1)) * 128;
+
+    if (tid == 0) {
+        for (int s = 0; s < SK_MAXKB; ++s) mbar_init(&full[s], 1);
+        mbar_init(accum, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < kb_per_cta; ++i) {
+                mbar_expect_tx(&full[i], (uint32_t)(W_BYTES + X_BYTES));
+                tma_load_2d(smem + i * W_BYTES, tmW, (kb0 + i) * GM_BK, wrow0, &full[i]);
+                tma_load_2d(xs + i * X_STRIDE, &tmX, (kb0 + i) * GM_BK, 0, &full[i]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(MPAD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            for (int i = 0; i < kb_per_cta; ++i) {
+                mbar_wait(&full[i], 0, status);
+                tc_fence_after();
+                const uint64_t dw = smem_desc_sw128(smem + i * W_BYTES);
+                const uint64_t dx = smem_desc_sw128(xs + i * X_STRIDE);
+#pragma unroll
+                for (int k = 0; k < GM_BK / 16; ++k) umma_bf16(tmem_base, dw + 2 * k, dx + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        mbar_wait(accum, 0, status);
+        tc_fence_after();
+        const int quarter = warp & 3;
+        const int n = tile * 128 + quarter * 32 + lane;
+        const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float* dst = part + (size_t)ks * M * ldp + n;
+#pragma unroll
+        for (int c0 = 0; c0 < MPAD; c0 += 16) {
+            uint32_t v[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                : "r"(trow + c0) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (c0 + j < M) dst[(size_t)(c0 + j) * ldp] = __uint_as_float(v[j]);
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TM_COLS);
+}
+
+// consumers of the fp32 K-split partials part[ks][row][col] (ks summed in index order)
+__device__ __forceinline__ float sum_splits(const float* part, int ksplit, size_t plane, size_t idx) {
+    float s = 0.f;
+    for (int k = 0; k < ksplit; ++k) s += part[(size_t)k * plane + idx];
+    return s;
+}
+
+// out[row, col0 + c] = bf16(sum)            (q / k / v projections into the qkv buffer)
+__global__ void __launch_bounds__(256) k_sk_store(const float* __restrict__ part, int ksplit, int M, int N, bf16* __restrict__ out, int ldo) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (size_t)M * N) return;
+    const int row = (int)(i / N), col = (int)(i % N);
+    out[(size_t)row * ldo + col] = __float2bfloat16_rn(sum_splits(part, ksplit, (size_t)M * N, i));
+}
+
+// h = bf16(h + bf16(sum));  x = rmsnorm(h) * w      one CTA per row (N = 1024), 4 columns per thread
+__global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ h,
+                                                       const bf16* __restrict__ w, bf16* __restrict__ x) {
+    __shared__ float s_red[8];
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t base = (size_t)row * H + 4 * tid, plane = (size_t)M * H;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < ksplit; ++k) {
+        const float4 p = *reinterpret_cast<const float4*>(part + (size_t)k * plane + base);
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+    }
+    const uint2 hu = *reinterpret_cast<const uint2*>(h + base);
+    float v[4] = {rbf(bf_lo(hu.x) + rbf(acc.x)), rbf(bf_hi(hu.x) + rbf(acc.y)), rbf(bf_lo(hu.y) + rbf(acc.z)), rbf(bf_hi(hu.y) + rbf(acc.w))};
+    *reinterpret_cast<uint2*>(h + base) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+    float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+    if (lane == 0) s_red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_red[i];
+    const float r = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
+    const uint2 wu = *reinterpret_cast<const uint2*>(w + 4 * tid);
+    const uint2 o = make_uint2(pack_bf16x2(rbf(bf_lo(wu.x) * rbf(v[0] * r)), rbf(bf_hi(wu.x) * rbf(v[1] * r))),
+                               pack_bf16x2(rbf(bf_lo(wu.y) * rbf(v[2] * r)), rbf(bf_hi(wu.y) * rbf(v[3] * r))));
+    *reinterpret_cast<uint2*>(x + base) = o;
+}
+
+// act[row, c] = bf16( bf16(silu(bf16(sum gate))) * bf16(sum up) )   gate/up partials are column blocks [0,I) and [I,2I)
+__global__ void __launch_bounds__(256) k_sk_swiglu(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ act) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (size_t)M * I) return;
+    const int row = (int)(i / I), col = (int)(i % I);
+    const size_t plane = (size_t)M * 2 * I, base = (size_t)row * 2 * I + col;
+    const float g = rbf(sum_splits(part, ksplit, plane, base)), u = rbf(sum_splits(part, ksplit, plane, base + I));
+    act[i] = __float2bfloat16_rn(rbf(silu_f32(g)) * u);
+}
+
 // ---------------------------------------------------------------- row-wise kernels
 // h[s,:] = embed[ids[s],:]      (reference: prefill_embed_kernel, fused_prefill_kernels.inl:3-20)
 __global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, const bf16* __restrict__ embed, bf16* __restrict__ h,
@@ -527,6 +673,45 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
     return (int)cudaGetLastError();
 }
 
+// Skinny path: part[ks][M][ldp] = X[M,K] * [W0;W1;W2][.,K]^T, K split in `ksplit` slices.
+template <int MPAD>
+static int launch_skinny_t(const bf16* const* W, const int* rowsW, int nW, const bf16* X, int ldx, float* part, int M, int K, int ksplit,
+                           unsigned int* status, cudaStream_t stream) {
+    constexpr int X_STRIDE = ((MPAD * GM_BK * 2) + 1023) & ~1023;
+    const size_t smem = (size_t)SK_MAXKB * (128 * GM_BK * 2 + X_STRIDE) + 1024 + 256;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_skinny<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set[dev] = true;
+    }
+    const int kb = K / GM_BK;
+    if (K % GM_BK != 0 || kb % ksplit != 0 || kb / ksplit > SK_MAXKB) return MQ_ERR_BAD_ARG;
+    CUtensorMap mw[3], mx;
+    int tiles[3] = {0, 0, 0}, ldp = 0;
+    for (int i = 0; i < 3; ++i) {
+        const int j = i < nW ? i : 0;
+        if (rowsW[j] % 128 != 0) return MQ_ERR_BAD_ARG;
+        int rc = get_map(W[j], (uint64_t)rowsW[j], (uint64_t)K, (uint64_t)K, 128, &mw[i]);
+        if (rc != MQ_OK) return rc;
+        if (i < nW) { tiles[i] = rowsW[i] / 128; ldp += rowsW[i]; }
+    }
+    int rc = get_map(X, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, MPAD, &mx);
+    if (rc != MQ_OK) return rc;
+    dim3 grid(tiles[0] + tiles[1] + tiles[2], ksplit);
+    k_gemm_skinny<MPAD><<<grid, GM_THREADS, smem, stream>>>(mw[0], mw[1], mw[2], tiles[0], tiles[1], mx, part, M, ldp, kb / ksplit, status);
+    return (int)cudaGetLastError();
+}
+static int launch_skinny(const bf16* const* W, const int* rowsW, int nW, const bf16* X, int ldx, float* part, int M, int K, int ksplit,
+                         unsigned int* status, cudaStream_t stream) {
+    if (M <= 16) return launch_skinny_t<16>(W, rowsW, nW, X, ldx, part, M, K, ksplit, status, stream);
+    if (M <= 32) return launch_skinny_t<32>(W, rowsW, nW, X, ldx, part, M, K, ksplit, status, stream);
+    if (M <= 64) return launch_skinny_t<64>(W, rowsW, nW, X, ldx, part, M, K, ksplit, status, stream);
+    return MQ_ERR_BAD_ARG;
+}
+
 // defined in decode.cu: final RMSNorm + LM head + arg-max on buf->hidden
 int launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream);
 
@@ -567,47 +752,68 @@ __global__ void __launch_bounds__(256) k_bd_attention(const bf16* __restrict__ q
     const float scale = 0.08838834764831845f;
     float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
     float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int p4 = warp * 4; p4 < len; p4 += 32) {
-        const int p = p4 + psub;
-        float s0 = 0.f, s1 = 0.f;
-        if (p < len) {
-            const uint4 ua = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + prt * 8);
-            const uint4 ub = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + 64 + prt * 8);
-            const uint32_t wk[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+    for (int pbase = warp * 4; pbase < len; pbase += 64) {
+        // two passes of four positions each (pbase.. and pbase+32..); every K and V load of
+        // both passes is issued before any arithmetic so that ~4 KB per warp is in flight
+        uint4 ka[2], kc[2];
+        uint2 vq[2][4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float klo = bf_lo(wk[e]), khi = bf_hi(wk[e]);
-                s0 = fmaf(klo, q0[2 * e], s0); s0 = fmaf(khi, q0[2 * e + 1], s0);
-                s1 = fmaf(klo, q1[2 * e], s1); s1 = fmaf(khi, q1[2 * e + 1], s1);
+        for (int u = 0; u < 2; ++u) {
+            const int p = pbase + 32 * u + psub;
+            ka[u] = make_uint4(0, 0, 0, 0); kc[u] = make_uint4(0, 0, 0, 0);
+            if (p < len) {
+                ka[u] = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + prt * 8);
+                kc[u] = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + 64 + prt * 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int pv = pbase + 32 * u + j;
+                vq[u][j] = make_uint2(0, 0);
+                if (pv < len) vq[u][j] = *reinterpret_cast<const uint2*>(vb + (size_t)pv * D + lane * 4);
             }
         }
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) {
-            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-        }
-        s0 = (p < len) ? s0 * scale : -1e30f;
-        s1 = (p < len) ? s1 * scale : -1e30f;
-        float sj0[4], sj1[4];
+        for (int u = 0; u < 2; ++u) {
+            const int p4 = pbase + 32 * u;
+            if (p4 >= len) break;
+            const int p = p4 + psub;
+            float s0 = 0.f, s1 = 0.f;
+            {
+                const uint32_t wk[8] = {ka[u].x, ka[u].y, ka[u].z, ka[u].w, kc[u].x, kc[u].y, kc[u].z, kc[u].w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { sj0[j] = __shfl_sync(0xffffffffu, s0, j * 8); sj1[j] = __shfl_sync(0xffffffffu, s1, j * 8); }
-        const float mn0 = fmaxf(m0, fmaxf(fmaxf(sj0[0], sj0[1]), fmaxf(sj0[2], sj0[3])));
-        const float mn1 = fmaxf(m1, fmaxf(fmaxf(sj1[0], sj1[1]), fmaxf(sj1[2], sj1[3])));
-        const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
-        m0 = mn0; m1 = mn1;
-        l0 *= c0; l1 *= c1;
+                for (int e = 0; e < 8; ++e) {
+                    const float klo = bf_lo(wk[e]), khi = bf_hi(wk[e]);
+                    s0 = fmaf(klo, q0[2 * e], s0); s0 = fmaf(khi, q0[2 * e + 1], s0);
+                    s1 = fmaf(klo, q1[2 * e], s1); s1 = fmaf(khi, q1[2 * e + 1], s1);
+                }
+            }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
+            for (int o = 4; o > 0; o >>= 1) {
+                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            }
+            s0 = (p < len) ? s0 * scale : -1e30f;
+            s1 = (p < len) ? s1 * scale : -1e30f;
+            float sj0[4], sj1[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (p4 + j < len) {
-                const float e0 = expf(sj0[j] - m0), e1 = expf(sj1[j] - m1);
-                l0 += e0; l1 += e1;
-                const float pb0 = rbf(e0), pb1 = rbf(e1);
-                const uint2 uv = *reinterpret_cast<const uint2*>(vb + (size_t)(p4 + j) * D + lane * 4);
-                const float vv[4] = {bf_lo(uv.x), bf_hi(uv.x), bf_lo(uv.y), bf_hi(uv.y)};
+            for (int j = 0; j < 4; ++j) { sj0[j] = __shfl_sync(0xffffffffu, s0, j * 8); sj1[j] = __shfl_sync(0xffffffffu, s1, j * 8); }
+            const float mn0 = fmaxf(m0, fmaxf(fmaxf(sj0[0], sj0[1]), fmaxf(sj0[2], sj0[3])));
+            const float mn1 = fmaxf(m1, fmaxf(fmaxf(sj1[0], sj1[1]), fmaxf(sj1[2], sj1[3])));
+            const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+            m0 = mn0; m1 = mn1;
+            l0 *= c0; l1 *= c1;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { acc0[e] = fmaf(pb0, vv[e], acc0[e]); acc1[e] = fmaf(pb1, vv[e], acc1[e]); }
+            for (int e = 0; e < 4; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (p4 + j < len) {
+                    const float e0 = expf(sj0[j] - m0), e1 = expf(sj1[j] - m1);
+                    l0 += e0; l1 += e1;
+                    const float pb0 = rbf(e0), pb1 = rbf(e1);
+                    const float vv[4] = {bf_lo(vq[u][j].x), bf_hi(vq[u][j].x), bf_lo(vq[u][j].y), bf_hi(vq[u][j].y)};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { acc0[e] = fmaf(pb0, vv[e], acc0[e]); acc1[e] = fmaf(pb1, vv[e], acc1[e]); }
+                }
             }
         }
     }
@@ -741,6 +947,40 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
     const size_t seq_stride = (size_t)model->num_layers * NKV * model->max_seq_len * D;
     k_pf_embed<<<B, 128, 0, stream>>>(in_tokens, (const bf16*)model->embed, h, model->vocab_size, status);
     int rc;
+    const size_t need_part = (size_t)4 * B * 2 * I * sizeof(float);   // largest partial: gate|up, 4 K-splits
+    const bool skinny = B <= 64 && bb->partials != nullptr && bb->partials_bytes >= need_part;
+    if (skinny) {
+        float* part = bb->partials;
+        k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)model->layers[0].input_layernorm, x, B);
+        for (int l = 0; l < model->num_layers; ++l) {
+            const MqLayerWeights& w = model->layers[l];
+            const bf16* wqkv[3] = {(const bf16*)w.q_proj, (const bf16*)w.k_proj, (const bf16*)w.v_proj};
+            const int rqkv[3] = {QSZ, KVSZ, KVSZ};
+            rc = launch_skinny(wqkv, rqkv, 3, x, H, part, B, H, 4, status, stream);
+            if (rc) return rc;
+            k_sk_store<<<(B * QKV + 255) / 256, 256, 0, stream>>>(part, 4, B, QKV, qkv, QKV);
+            k_pf_qknorm_rope<<<dim3(B, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+                                                             (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
+                                                             model->max_seq_len, bb->positions, seq_stride);
+            k_bd_attention<<<dim3(B, NKV), 256, 0, stream>>>(qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
+                                                             model->max_seq_len, seq_stride);
+            const bf16* wo[1] = {(const bf16*)w.o_proj};
+            const int ro[1] = {H};
+            rc = launch_skinny(wo, ro, 1, attn, QSZ, part, B, QSZ, 8, status, stream);
+            if (rc) return rc;
+            k_sk_resid_norm<<<B, 256, 0, stream>>>(part, 8, B, h, (const bf16*)w.post_attn_layernorm, x);
+            const bf16* wgu[2] = {(const bf16*)w.gate_proj, (const bf16*)w.up_proj};
+            const int rgu[2] = {I, I};
+            rc = launch_skinny(wgu, rgu, 2, x, H, part, B, H, 4, status, stream);
+            if (rc) return rc;
+            k_sk_swiglu<<<(B * I + 255) / 256, 256, 0, stream>>>(part, 4, B, act);
+            const bf16* wd[1] = {(const bf16*)w.down_proj};
+            rc = launch_skinny(wd, ro, 1, act, I, part, B, I, 8, status, stream);
+            if (rc) return rc;
+            const bf16* next_norm = (l + 1 < model->num_layers) ? (const bf16*)model->layers[l + 1].input_layernorm : (const bf16*)model->final_norm;
+            k_sk_resid_norm<<<B, 256, 0, stream>>>(part, 8, B, h, next_norm, x);
+        }
+    } else {
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
         k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.input_layernorm, x, B);
@@ -764,6 +1004,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
         if (rc) return rc;
     }
     k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)model->final_norm, x, B);
+    }
     rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
                                      model->vocab_size, status, stream);
     if (rc) return rc;

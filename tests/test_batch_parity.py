@@ -95,6 +95,24 @@ def test_batch_one_equals_batch1_decoder(setup):
     assert agree >= 8, (a, b)
 
 
+def test_splitk_and_tile_gemm_paths_agree(setup):
+    """The split-K path (default for batch <= 64) against the 128-row tile GEMMs."""
+    bd, _ = setup
+    prompts = [random_prompt(QWEN3_TINY, n, 7, i) for i, n in enumerate(LENS)]
+    outs = []
+    for splitk in (True, False):
+        bd.use_splitk = splitk
+        bd.reset()
+        first = bd.prefill_batch(prompts)
+        toks, lg = bd.decode_batch(first, return_logits=True)
+        outs.append((toks.tolist(), lg.cpu()))
+    bd.use_splitk = True
+    r = logit_report(outs[0][1], outs[1][1])
+    assert r["max"] <= 6e-2 and r["mean"] <= 6e-3, r
+    agree = sum(1 for a, b in zip(outs[0][0], outs[1][0]) if a == b)
+    assert agree >= len(LENS) - 1
+
+
 def test_batch_errors(setup):
     bd, _ = setup
     bd.reset()
