@@ -247,6 +247,24 @@ int mq_prefill_launch_count(int num_layers);
 int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* C, const void* R,
                         int M, int N, int K, int ldc, unsigned int* status, void* stream);
 
+/* Standalone bf16 ops with the rounding points of the fused kernels.  They
+ * replace the reference's csrc/kernels launchers (declared in
+ * csrc/kernels/__init__.py:40-95): launch_rms_norm (rms_norm.cu:60-170),
+ * launch_silu_mul (silu_mul.cu:22-111), launch_rope / launch_rope_single
+ * (rope.cu:31-188; q/k laid out [seq_len, heads, head_dim], cos/sin
+ * [positions, head_dim]) and launch_attention_decode (attention_decode.cu:
+ * 110-357; q/out [batch, n_q_heads, head_dim], caches [batch, n_kv_heads,
+ * max_seq_len, head_dim]). */
+int mq_launch_rms_norm(const void* x, const void* weight, void* out, int n_rows, int n_cols, float eps, void* stream);
+int mq_launch_silu_mul(const void* gate, const void* up, void* out, long long n_elements, void* stream);
+int mq_launch_rope(const void* q, const void* k, const void* cos, const void* sin, void* q_out, void* k_out,
+                   int seq_len, int n_q_heads, int n_kv_heads, int head_dim, void* stream);
+int mq_launch_rope_single(const void* x, const void* cos, const void* sin, void* out, int n_heads, int head_dim,
+                          int position, void* stream);
+int mq_launch_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, int batch_size,
+                               int cache_len, int n_q_heads, int n_kv_heads, int head_dim, int max_seq_len,
+                               float scale, void* stream);
+
 /* dst[i] = start + i.  Replaces launch_ldg_fill_iota
  * (csrc/megakernel/fused_decode_ldg_launch.inl:5-17). */
 int mq_launch_fill_iota(int* dst, int start, int n, void* stream);
