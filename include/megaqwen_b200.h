@@ -284,6 +284,12 @@ int mq_device_info(int* sm_count, int* cc_major, int* cc_minor);
  * MQ_ERR_UNSUPPORTED on anything but an sm_100 device. */
 int mq_init_device(void);
 
+/* Benchmark-only switches of mq_launch_decode (results become meaningless):
+ * 1 skip the dot products, 2 skip the RMSNorms.  0 restores normal operation.  Used to attribute time per stage; only
+ * available when the library is built with -DMQ_DECODE_EXPERIMENTS (otherwise
+ * any non-zero value returns MQ_ERR_UNSUPPORTED). */
+int mq_decode_set_experiment(int flags);
+
 /* ABI version of this header. */
 int mq_abi_version(void);
 

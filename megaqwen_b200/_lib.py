@@ -54,6 +54,7 @@ class MqBatchBuffers(C.Structure):
 # name -> (restype, argtypes); every symbol include/megaqwen_b200.h declares.
 SIGNATURES = {
     "mq_abi_version": (C.c_int, []),
+    "mq_decode_set_experiment": (C.c_int, [C.c_int]),
     "mq_init_device": (C.c_int, []),
     "mq_device_info": (C.c_int, [C.POINTER(C.c_int)] * 3),
     "mq_decode_attn_nsplit": (C.c_int, [C.c_int]),

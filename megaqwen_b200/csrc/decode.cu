@@ -34,6 +34,14 @@
 
 namespace mq {
 
+// The experiment switches cost registers and branches in every kernel, so they are
+// compiled in only with -DMQ_DECODE_EXPERIMENTS.
+#ifdef MQ_DECODE_EXPERIMENTS
+#define EXPF(a) ((a).exp_flags)
+#else
+#define EXPF(a) 0
+#endif
+
 struct DecodeArgs {
     const bf16* embed;
     const bf16* final_norm;
@@ -58,7 +66,12 @@ struct DecodeArgs {
     int max_seq;
     int nsplit;
     int chunk_cap;
+    int exp_flags;   // experiments (benchmarks only): 1 skip dot products, 2 skip RMSNorm, 4 no weight copies in the per-layer GEMV kernels
 };
+
+__device__ __forceinline__ float dot_x(const DecodeArgs& a, const bf16* wrow, const float (&x)[32], int lane) {
+    return (EXPF(a) & 1) ? x[0] : dot_slice(wrow, x, lane);
+}
 
 constexpr int GEMV_THREADS = 256;
 constexpr int DOWN_THREADS = 384;
@@ -81,18 +94,22 @@ __device__ __forceinline__ void row_range(int total, int& r0, int& n) {
 __global__ void __launch_bounds__(GEMV_THREADS) k_qkv(DecodeArgs a, MqLayerWeights w, int layer) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)QKV_MAXROWS * H * 2);
+    bf16* nrm = wbuf + (size_t)QKV_MAXROWS * H;      // input RMSNorm weight, copied with the first chunk: a
+                                                     // global load after the wait would be an HBM miss
+                                                     // (the weight stream evicts everything else from L2)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)(QKV_MAXROWS + 1) * H * 2);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int r0, n;
     row_range(QKV, r0, n);
     constexpr int CH = 8;  // rows per barrier
-    if (tid == 0) {
+    if (tid == 0 && !(EXPF(a) & 4)) {
         const int nch = (n + CH - 1) / CH;
         for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
         mbar_fence_init();
         for (int c = 0; c < nch; ++c) {
             const int a0 = r0 + c * CH, a1 = min(r0 + n, a0 + CH);
-            mbar_expect_tx(&bars[c], (uint32_t)(a1 - a0) * H * 2);
+            mbar_expect_tx(&bars[c], (uint32_t)(a1 - a0) * H * 2 + (c == 0 ? H * 2 : 0));
+            if (c == 0) bulk_g2s(nrm, w.input_layernorm, H * 2, &bars[0]);
             // a chunk may straddle the q|k|v matrix boundaries
             int r = a0;
             while (r < a1) {
@@ -130,16 +147,17 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_qkv(DecodeArgs a, MqLayerWeigh
     } else {
         load_x_slice(x, a.hidden, lane);
     }
-    rmsnorm_slice(x, (const bf16*)w.input_layernorm, lane);
+    if (!(EXPF(a) & 4)) mbar_wait(&bars[0], 0, a.status);
+    if (!(EXPF(a) & 2)) rmsnorm_slice(x, nrm, lane);
 
     for (int i = warp; i < n; i += 16) {
         const int i2 = i + 8;
-        mbar_wait(&bars[i / CH], 0, a.status);
-        float d0 = dot_slice(wbuf + (size_t)i * H, x, lane);
+        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
+        float d0 = dot_x(a, wbuf + (size_t)i * H, x, lane);
         float d1 = 0.f;
         if (i2 < n) {
-            mbar_wait(&bars[i2 / CH], 0, a.status);
-            d1 = dot_slice(wbuf + (size_t)i2 * H, x, lane);
+            if (!(EXPF(a) & 4)) mbar_wait(&bars[i2 / CH], 0, a.status);
+            d1 = dot_x(a, wbuf + (size_t)i2 * H, x, lane);
         }
         d0 = warp_sum(d0);
         d1 = warp_sum(d1);
@@ -192,7 +210,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     float* qh = sc + 2 * cap;                                         // [2][128]
     float* accb = qh + 2 * D;                                         // [2][2][128]
     float* ml = accb + 4 * D;                                         // [2][2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ml + 4);             // [2]
+    float* wm = ml + 4;                                               // [8][2] per-warp running max
+    float* wl = wm + 16;                                              // [8][2] per-warp sum
+    float* wacc = wl + 16;                                            // [8][2][128] per-warp accumulators
+    bf16* cst = reinterpret_cast<bf16*>(wacc + 16 * D);               // q_norm | k_norm | cos[pos] | sin[pos]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(cst + 4 * D);        // [3]
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -216,7 +238,15 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     if (tid == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
+        mbar_init(&bars[2], 1);
         mbar_fence_init();
+        if (active) {   // per-head norm weights and this position's RoPE rows (HBM misses if loaded after the wait)
+            mbar_expect_tx(&bars[2], 4 * D * 2);
+            bulk_g2s(cst, w.q_norm, D * 2, &bars[2]);
+            bulk_g2s(cst + D, w.k_norm, D * 2, &bars[2]);
+            bulk_g2s(cst + 2 * D, a.cos + (size_t)pos * D, D * 2, &bars[2]);
+            bulk_g2s(cst + 3 * D, a.sin + (size_t)pos * D, D * 2, &bars[2]);
+        }
         if (n_cached > 0) {
             mbar_expect_tx(&bars[0], (uint32_t)n_cached * D * 2);
             bulk_g2s(kt, a.k_cache + head_off + (size_t)c0 * D, (uint32_t)n_cached * D * 2, &bars[0]);
@@ -232,12 +262,14 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     // ---- per-head norm + RoPE of q (both heads), and of the new k; v raw
     if (warp < 2) {
         float lo[2], hi[2];
-        norm_rope_head(a.qkv + (2 * g + warp) * D, (const bf16*)w.q_norm, a.cos + (size_t)pos * D, a.sin + (size_t)pos * D, lane, lo, hi);
+        mbar_wait(&bars[2], 0, a.status);
+        norm_rope_head(a.qkv + (2 * g + warp) * D, cst, cst + 2 * D, cst + 3 * D, lane, lo, hi);
         qh[warp * D + 2 * lane] = lo[0]; qh[warp * D + 2 * lane + 1] = lo[1];
         qh[warp * D + 64 + 2 * lane] = hi[0]; qh[warp * D + 64 + 2 * lane + 1] = hi[1];
     } else if (warp == 2 && is_last) {
         float lo[2], hi[2];
-        norm_rope_head(a.qkv + QSZ + g * D, (const bf16*)w.k_norm, a.cos + (size_t)pos * D, a.sin + (size_t)pos * D, lane, lo, hi);
+        mbar_wait(&bars[2], 0, a.status);
+        norm_rope_head(a.qkv + QSZ + g * D, cst + D, cst + 2 * D, cst + 3 * D, lane, lo, hi);
         const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
         bf16* krow = kt + (size_t)(n - 1) * D;
         *reinterpret_cast<uint32_t*>(krow + 2 * lane) = plo;
@@ -253,7 +285,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     __syncthreads();
     if (n_cached > 0) mbar_wait(&bars[0], 0, a.status);
 
-    // ---- scores: 8 lanes per position, 4 positions per warp pass
+    if (n_cached > 0) mbar_wait(&bars[1], 0, a.status);
+
+    // ---- every warp walks positions warp*4 + 32*i .. with its own online softmax
+    // (8 lanes per key for the scores, the whole warp per value row); the eight warps
+    // are merged through shared memory: two block barriers in the whole kernel.
     {
         const int psub = lane >> 3, part = lane & 7;
         float q0[16], q1[16];
@@ -263,6 +299,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
             q1[e] = qh[D + part * 8 + e]; q1[8 + e] = qh[D + 64 + part * 8 + e];
         }
         const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+        float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
         for (int p4 = warp * 4; p4 < n; p4 += (ATT_THREADS / 32) * 4) {
             const int p = p4 + psub;
             float s0 = 0.f, s1 = 0.f;
@@ -279,48 +317,53 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
                 s0 += __shfl_xor_sync(0xffffffffu, s0, o);
                 s1 += __shfl_xor_sync(0xffffffffu, s1, o);
             }
-            if (part == 0 && p < n) { sc[p] = s0 * scale; sc[cap + p] = s1 * scale; }
+            s0 = (p < n) ? s0 * scale : -1e30f;
+            s1 = (p < n) ? s1 * scale : -1e30f;
+            float sj0[4], sj1[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { sj0[j] = __shfl_sync(0xffffffffu, s0, j * 8); sj1[j] = __shfl_sync(0xffffffffu, s1, j * 8); }
+            const float mn0 = fmaxf(m0, fmaxf(fmaxf(sj0[0], sj0[1]), fmaxf(sj0[2], sj0[3])));
+            const float mn1 = fmaxf(m1, fmaxf(fmaxf(sj1[0], sj1[1]), fmaxf(sj1[2], sj1[3])));
+            const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+            m0 = mn0; m1 = mn1;
+            l0 *= c0; l1 *= c1;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (p4 + j < n) {
+                    const float e0 = expf(sj0[j] - m0), e1 = expf(sj1[j] - m1);
+                    l0 += e0; l1 += e1;
+                    const float pb0 = rbf(e0), pb1 = rbf(e1);
+                    const uint2 uv = *reinterpret_cast<const uint2*>(vt + (size_t)(p4 + j) * D + lane * 4);
+                    const float vv[4] = {bf_lo(uv.x), bf_hi(uv.x), bf_lo(uv.y), bf_hi(uv.y)};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { acc0[e] = fmaf(pb0, vv[e], acc0[e]); acc1[e] = fmaf(pb1, vv[e], acc1[e]); }
+                }
+            }
         }
-    }
-    __syncthreads();
-
-    // ---- chunk-local softmax statistics; probabilities rounded to bf16 for the PV product
-    if (warp < 2) {
-        float* srow = sc + warp * cap;
-        float m = -INFINITY;
-        for (int p = lane; p < n; p += 32) m = fmaxf(m, srow[p]);
-        m = warp_max(m);
-        float l = 0.f;
-        for (int p = lane; p < n; p += 32) {
-            const float e = expf(srow[p] - m);
-            l += e;
-            srow[p] = rbf(e);
-        }
-        l = warp_sum(l);
-        if (lane == 0) { ml[warp * 2] = m; ml[warp * 2 + 1] = l; }
-    }
-    __syncthreads();
-    if (n_cached > 0) mbar_wait(&bars[1], 0, a.status);
-
-    // ---- PV: thread = (head, half of the positions, pair of dims)
-    {
-        const int hh = tid >> 7, half = (tid >> 6) & 1, dp = tid & 63;
-        const int nh = (n + 1) >> 1;
-        const int pb = half * nh, pe = min(n, pb + nh);
-        const float* prow = sc + hh * cap;
-        float a0 = 0.f, a1 = 0.f;
-        for (int p = pb; p < pe; ++p) {
-            const uint32_t u = *reinterpret_cast<const uint32_t*>(vt + (size_t)p * D + 2 * dp);
-            const float pv = prow[p];
-            a0 = fmaf(pv, bf_lo(u), a0);
-            a1 = fmaf(pv, bf_hi(u), a1);
-        }
-        accb[(hh * 2 + half) * D + 2 * dp] = a0;
-        accb[(hh * 2 + half) * D + 2 * dp + 1] = a1;
+        if (lane == 0) { wm[warp * 2] = m0; wm[warp * 2 + 1] = m1; wl[warp * 2] = l0; wl[warp * 2 + 1] = l1; }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { wacc[(warp * 2) * D + lane * 4 + e] = acc0[e]; wacc[(warp * 2 + 1) * D + lane * 4 + e] = acc1[e]; }
     }
     __syncthreads();
     const int hh = tid >> 7, d = tid & 127;
-    const float acc = accb[(hh * 2) * D + d] + accb[(hh * 2 + 1) * D + d];
+    float acc = 0.f;
+    {
+        float M = -1e30f;
+#pragma unroll
+        for (int w8 = 0; w8 < ATT_THREADS / 32; ++w8) M = fmaxf(M, wm[w8 * 2 + hh]);
+        float lsum = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < ATT_THREADS / 32; ++w8) {
+            const float f = expf(wm[w8 * 2 + hh] - M);
+            lsum = fmaf(wl[w8 * 2 + hh], f, lsum);
+            acc = fmaf(wacc[(w8 * 2 + hh) * D + d], f, acc);
+        }
+        if (d == 0) { ml[hh * 2] = M; ml[hh * 2 + 1] = lsum; }
+        // every thread of a head needs (M, l): publish through shared memory
+        __syncthreads();
+    }
     const int qhead = 2 * g + hh;
     if (n_act == 1) {
         a.attn[qhead * D + d] = __float2bfloat16_rn(acc / ml[hh * 2 + 1]);
@@ -387,7 +430,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_oproj(DecodeArgs a, MqLayerWei
     int r0, n;
     row_range(H, r0, n);
     constexpr int CH = 4;
-    if (tid == 0) {
+    if (tid == 0 && !(EXPF(a) & 4)) {
         const int nch = (n + CH - 1) / CH;
         for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
         mbar_fence_init();
@@ -406,8 +449,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_oproj(DecodeArgs a, MqLayerWei
     float x[32];
     load_x_slice(x, a.attn + slice * 1024, lane);
     for (int i = rg; i < n; i += 4) {
-        mbar_wait(&bars[i / CH], 0, a.status);
-        const float dsum = warp_sum(dot_slice(wbuf + (size_t)i * QSZ + slice * 1024, x, lane));
+        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
+        const float dsum = warp_sum(dot_x(a, wbuf + (size_t)i * QSZ + slice * 1024, x, lane));
         if (lane == 0) part[i * 2 + slice] = dsum;
     }
     __syncthreads();
@@ -425,19 +468,21 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gateup(DecodeArgs a, MqLayerWe
     extern __shared__ __align__(128) uint8_t smem_raw[];
     bf16* gbuf = reinterpret_cast<bf16*>(smem_raw);
     bf16* ubuf = gbuf + (size_t)GU_MAXROWS * H;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)2 * GU_MAXROWS * H * 2);
+    bf16* nrm = ubuf + (size_t)GU_MAXROWS * H;       // post-attention RMSNorm weight (see k_qkv)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)(2 * GU_MAXROWS + 1) * H * 2);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int r0, n;
     row_range(I, r0, n);
     constexpr int CH = 8;
-    if (tid == 0) {
+    if (tid == 0 && !(EXPF(a) & 4)) {
         const int nch = (n + CH - 1) / CH;
         for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
         mbar_fence_init();
         for (int c = 0; c < nch; ++c) {
             const int a0 = c * CH, a1 = min(n, a0 + CH);
             const uint32_t bytes = (uint32_t)(a1 - a0) * H * 2;
-            mbar_expect_tx(&bars[c], 2 * bytes);
+            mbar_expect_tx(&bars[c], 2 * bytes + (c == 0 ? H * 2 : 0));
+            if (c == 0) bulk_g2s(nrm, w.post_attn_layernorm, H * 2, &bars[0]);
             bulk_g2s(gbuf + (size_t)a0 * H, (const bf16*)w.gate_proj + (size_t)(r0 + a0) * H, bytes, &bars[c]);
             bulk_g2s(ubuf + (size_t)a0 * H, (const bf16*)w.up_proj + (size_t)(r0 + a0) * H, bytes, &bars[c]);
         }
@@ -448,11 +493,12 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_gateup(DecodeArgs a, MqLayerWe
 
     float x[32];
     load_x_slice(x, a.hidden, lane);
-    rmsnorm_slice(x, (const bf16*)w.post_attn_layernorm, lane);
+    if (!(EXPF(a) & 4)) mbar_wait(&bars[0], 0, a.status);
+    if (!(EXPF(a) & 2)) rmsnorm_slice(x, nrm, lane);
     for (int i = warp; i < n; i += 8) {
-        mbar_wait(&bars[i / CH], 0, a.status);
-        float gsum = dot_slice(gbuf + (size_t)i * H, x, lane);
-        float usum = dot_slice(ubuf + (size_t)i * H, x, lane);
+        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
+        float gsum = dot_x(a, gbuf + (size_t)i * H, x, lane);
+        float usum = dot_x(a, ubuf + (size_t)i * H, x, lane);
         gsum = warp_sum(gsum);
         usum = warp_sum(usum);
         if (lane == 0) {
@@ -473,7 +519,7 @@ __global__ void __launch_bounds__(DOWN_THREADS) k_down(DecodeArgs a, MqLayerWeig
     int r0, n;
     row_range(H, r0, n);
     constexpr int CH = 4;
-    if (tid == 0) {
+    if (tid == 0 && !(EXPF(a) & 4)) {
         const int nch = (n + CH - 1) / CH;
         for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
         mbar_fence_init();
@@ -492,8 +538,8 @@ __global__ void __launch_bounds__(DOWN_THREADS) k_down(DecodeArgs a, MqLayerWeig
     float x[32];
     load_x_slice(x, a.act + slice * 1024, lane);
     for (int i = rg; i < n; i += 4) {
-        mbar_wait(&bars[i / CH], 0, a.status);
-        const float dsum = warp_sum(dot_slice(wbuf + (size_t)i * I + slice * 1024, x, lane));
+        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
+        const float dsum = warp_sum(dot_x(a, wbuf + (size_t)i * I + slice * 1024, x, lane));
         if (lane == 0) part[i * 3 + slice] = dsum;
     }
     __syncthreads();
@@ -526,6 +572,8 @@ __global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)LM_STAGES * LM_ROWS * H * 2);
     uint64_t* empty = full + LM_STAGES;
     unsigned long long* wbest = reinterpret_cast<unsigned long long*>(empty + LM_STAGES);  // [LM_CONSUMERS]
+    uint64_t* nbar = reinterpret_cast<uint64_t*>(wbest + LM_CONSUMERS);
+    bf16* nrm = reinterpret_cast<bf16*>(nbar + 2);                     // final RMSNorm weight
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r0 = (int)(((long long)blockIdx.x * a.vocab) / gridDim.x);
     const int r1 = (int)(((long long)(blockIdx.x + 1) * a.vocab) / gridDim.x);
@@ -541,7 +589,10 @@ __global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
     };
     if (tid == LM_CONSUMERS * 32) {
         for (int s = 0; s < LM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], LM_CONSUMERS); }
+        mbar_init(nbar, 1);
         mbar_fence_init();
+        mbar_expect_tx(nbar, H * 2);
+        bulk_g2s(nrm, a.final_norm, H * 2, nbar);
         for (int it = 0; it < min(nst, LM_STAGES); ++it) issue(it);
     }
     __syncthreads();
@@ -562,7 +613,8 @@ __global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
     } else {
         float x[32];
         load_x_slice(x, a.hidden, lane);
-        rmsnorm_slice(x, a.final_norm, lane);
+        mbar_wait(nbar, 0, a.status);
+        rmsnorm_slice(x, nrm, lane);
         float bestv = -INFINITY;
         int besti = 0x7fffffff;
         for (int it = 0; it < nst; ++it) {
@@ -630,12 +682,12 @@ struct DeviceState {
 };
 static DeviceState g_dev[64];
 
-static size_t smem_qkv() { return (size_t)QKV_MAXROWS * H * 2 + MAX_BARS * 8; }
+static size_t smem_qkv() { return (size_t)(QKV_MAXROWS + 1) * H * 2 + MAX_BARS * 8; }
 static size_t smem_oproj() { return (size_t)O_MAXROWS * QSZ * 2 + MAX_BARS * 8 + O_MAXROWS * 2 * 4; }
-static size_t smem_gateup() { return (size_t)2 * GU_MAXROWS * H * 2 + MAX_BARS * 8; }
+static size_t smem_gateup() { return (size_t)(2 * GU_MAXROWS + 1) * H * 2 + MAX_BARS * 8; }
 static size_t smem_down() { return (size_t)DN_MAXROWS * I * 2 + MAX_BARS * 8 + DN_MAXROWS * 3 * 4; }
-static size_t smem_lmhead() { return (size_t)LM_STAGES * LM_ROWS * H * 2 + 2 * LM_STAGES * 8 + LM_CONSUMERS * 8; }
-static size_t smem_attn(int cap) { return (size_t)cap * D * 2 * 2 + (size_t)2 * cap * 4 + 2 * D * 4 + 4 * D * 4 + 4 * 4 + 2 * 8; }
+static size_t smem_lmhead() { return (size_t)LM_STAGES * LM_ROWS * H * 2 + 2 * LM_STAGES * 8 + LM_CONSUMERS * 8 + 16 + H * 2; }
+static size_t smem_attn(int cap) { return (size_t)cap * D * 2 * 2 + (size_t)2 * cap * 4 + 2 * D * 4 + 4 * D * 4 + 4 * 4 + 32 * 4 + 16 * D * 4 + 4 * D * 2 + 3 * 8; }
 
 constexpr int ATT_MAX_CAP = 384;    // positions per CTA: 384 * 520 B + 3 KB of shared memory
 constexpr int ATT_MAX_SPLIT = 64;
@@ -667,8 +719,13 @@ static int ensure_device(DeviceState** out) {
         st.cc_major = p.major;
         st.cc_minor = p.minor;
         if (p.major != 10 || st.sm_count < MIN_GRID) return MQ_ERR_UNSUPPORTED;
+// All kernels of the chain ask for the same (maximum) shared-memory carve-out: kernels
+// whose carve-out differs cannot be resident on an SM together, which would serialise
+// the programmatic-dependent-launch chain.
 #define MQ_SET_SMEM(k, bytes)                                                                   \
     e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes));     \
+    if (e != cudaSuccess) return (int)e;                                                        \
+    e = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared); \
     if (e != cudaSuccess) return (int)e;
         MQ_SET_SMEM(k_qkv, smem_qkv());
         MQ_SET_SMEM(k_oproj, smem_oproj());
@@ -701,6 +758,8 @@ static cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 // Final RMSNorm + LM head + arg-max on buf->hidden (used by the prefill path).
 int launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream);
 
+static int g_decode_exp_flags = 0;
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace mq
@@ -723,6 +782,15 @@ int mq::launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int
     a.vocab = model->vocab_size;
     a.max_seq = model->max_seq_len;
     return (int)launch(k_lmhead, dim3(st->sm_count), dim3(LM_THREADS), smem_lmhead(), stream, false, a);
+}
+
+extern "C" int mq_decode_set_experiment(int flags) {
+#ifdef MQ_DECODE_EXPERIMENTS
+    g_decode_exp_flags = flags;
+    return MQ_OK;
+#else
+    return flags == 0 ? MQ_OK : MQ_ERR_UNSUPPORTED;
+#endif
 }
 
 extern "C" int mq_abi_version(void) { return 1; }
@@ -799,6 +867,7 @@ extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf
     a.max_seq = model->max_seq_len;
     a.nsplit = nsplit;
     a.chunk_cap = cap;
+    a.exp_flags = g_decode_exp_flags;
 
     const bool pdl = !(flags & MQ_FLAG_NO_PDL);
     const int G = st->sm_count;
