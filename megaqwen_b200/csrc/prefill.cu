@@ -94,7 +94,11 @@ struct GemmCfg {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
+       const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
        bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
+    // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
+    // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
+    // and tmB2 (up) for the same tile.
     using Cfg = GemmCfg<BN, EPI>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -106,6 +110,13 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * GM_BM, n0 = blockIdx.x * BN;
     const int nk = K / GM_BK;
+    const int tile = blockIdx.x;
+    const CUtensorMap* mapB = &tmB;
+    int brow0 = n0;
+    if (EPI != EPI_SWIGLU && tile >= tiles0) {
+        mapB = tile < tiles0 + tiles1 ? &tmB2 : &tmB3;
+        brow0 = (tile < tiles0 + tiles1 ? tile - tiles0 : tile - tiles0 - tiles1) * BN;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -126,7 +137,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
                 mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
                 tma_load_2d(st, &tmA, kb * GM_BK, m0, &full[s]);
-                tma_load_2d(st + GM_BM * GM_BK * 2, &tmB, kb * GM_BK, n0, &full[s]);
+                tma_load_2d(st + GM_BM * GM_BK * 2, mapB, kb * GM_BK, brow0, &full[s]);
                 if (EPI == EPI_SWIGLU) tma_load_2d(st + GM_BM * GM_BK * 2 + BN * GM_BK * 2, &tmB2, kb * GM_BK, n0, &full[s]);
             }
         }
@@ -647,7 +658,8 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
 
 template <int BN, int EPI>
 static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf16* C, const bf16* R, int M, int N, int K, int ldc,
-                       unsigned int* status, cudaStream_t stream) {
+                       unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0) {
+    // rows0 > 0: B, B2, B3 hold rows0, rows1 and N - rows0 - rows1 output columns (concatenated along N)
     using Cfg = GemmCfg<BN, EPI>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -661,15 +673,24 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
     CUtensorMap ma, mb, mb2;
     int rc = get_map(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, GM_BM, &ma);
     if (rc != MQ_OK) return rc;
-    rc = get_map(B, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, &mb);
+    const bool concat = rows0 > 0;
+    if (concat && (rows0 % BN || rows1 % BN || EPI == EPI_SWIGLU)) return MQ_ERR_BAD_ARG;
+    rc = get_map(B, (uint64_t)(concat ? rows0 : N), (uint64_t)K, (uint64_t)K, BN, &mb);
     if (rc != MQ_OK) return rc;
     mb2 = mb;
+    CUtensorMap mb3 = mb;
     if (EPI == EPI_SWIGLU) {
         rc = get_map(B2, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN, &mb2);
         if (rc != MQ_OK) return rc;
+    } else if (concat) {
+        rc = get_map(B2, (uint64_t)rows1, (uint64_t)K, (uint64_t)K, BN, &mb2);
+        if (rc != MQ_OK) return rc;
+        rc = get_map(B3, (uint64_t)(N - rows0 - rows1), (uint64_t)K, (uint64_t)K, BN, &mb3);
+        if (rc != MQ_OK) return rc;
     }
     dim3 grid(N / BN, (M + GM_BM - 1) / GM_BM);
-    k_gemm<BN, EPI><<<grid, GM_THREADS, Cfg::SMEM, stream>>>(ma, mb, mb2, C, R, M, N, K, ldc, status);
+    k_gemm<BN, EPI><<<grid, GM_THREADS, Cfg::SMEM, stream>>>(ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
+                                                             C, R, M, N, K, ldc, status);
     return (int)cudaGetLastError();
 }
 
@@ -868,7 +889,7 @@ __global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restri
 
 using namespace mq;
 
-extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 10 + 2; }
+extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 8 + 2; }
 
 // C[M,N] = A[M,K] * B[N,K]^T on the tcgen05 path (bf16 in/out, fp32 accumulate);
 // optional residual R (same shape and leading dimension as C, may alias C).
@@ -904,23 +925,24 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
         k_pf_rmsnorm<<<(S + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.input_layernorm, x, S);
-        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, nullptr, qkv, nullptr, S, QSZ, H, QKV, status, stream);
-        if (rc) return rc;
-        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.k_proj, nullptr, qkv + QSZ, nullptr, S, KVSZ, H, QKV, status, stream);
-        if (rc) return rc;
-        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.v_proj, nullptr, qkv + QSZ + KVSZ, nullptr, S, KVSZ, H, QKV, status, stream);
+        // q | k | v in one launch: 32 column tiles from three weight matrices
+        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
+                                         (const bf16*)w.v_proj, QSZ, KVSZ);
         if (rc) return rc;
         k_pf_qknorm_rope<<<dim3(S, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0);
         k_pf_attention<<<dim3((S + FA_BQ - 1) / FA_BQ, NQ), FA_THREADS, fa_smem, stream>>>(qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
                                                                                           attn, S, pos0, l, model->max_seq_len);
-        rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
+        // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
+        rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream)
+                         : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
         if (rc) return rc;
         k_pf_rmsnorm<<<(S + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.post_attn_layernorm, x, S);
         rc = launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
         if (rc) return rc;
-        rc = launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream);
+        rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream)
+                         : launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream);
         if (rc) return rc;
     }
     // last row -> decode hidden buffer, then the decode path's LM head + arg-max
