@@ -461,6 +461,11 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
 // one warp per (query, head) walking the keys serially.)
 constexpr int FA_BQ = 64, FA_BK = 64, FA_LD = D + 8, FA_THREADS = 128;
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
@@ -504,7 +509,9 @@ __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restr
 #pragma unroll
     for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
-    const float scale = 0.08838834764831845f;
+    // scores are kept in the log2 domain (scale * log2(e) folded in) so that the softmax uses
+    // the single-instruction exp2 instead of expf; the probabilities are the same numbers
+    const float scale = 0.08838834764831845f * 1.4426950408889634f;
     const int row_a = pos0 + q0 + warp * 16 + (lane >> 2);   // absolute position of this thread's first row; second is +8
     const int kv_end = min(pos0 + S, pos0 + q0 + FA_BQ);     // exclusive bound of keys any row of the tile may see
     const int ntiles = (kv_end + FA_BK - 1) / FA_BK;
@@ -556,7 +563,7 @@ __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restr
             mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
             mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
             const float m_new = fmaxf(m_run[h2], mx[h2]);
-            corr[h2] = expf(m_run[h2] - m_new);
+            corr[h2] = fast_exp2(m_run[h2] - m_new);
             m_run[h2] = m_new;
         }
         float rs[2] = {0.f, 0.f};
@@ -566,7 +573,7 @@ __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restr
             float pe[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                pe[e] = (sacc[nt][e] <= -1e29f) ? 0.f : expf(sacc[nt][e] - m_run[e >> 1]);
+                pe[e] = (sacc[nt][e] <= -1e29f) ? 0.f : fast_exp2(sacc[nt][e] - m_run[e >> 1]);
                 rs[e >> 1] += pe[e];
             }
             pf[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(pe[0], pe[1]);
