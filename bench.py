@@ -126,6 +126,79 @@ def run_reference(args):
     }))
 
 
+def measure_other_configs(dev, w):
+    """The remaining BASELINE configurations on one GPU (reported beside the headline):
+    config 3 (1024-token prefill + 32 steps), config 4 (batch 32, ragged 256-512 prompts,
+    128 steps) and config 5 (batch 64, 1024-token prompts, 256 steps)."""
+    from megaqwen_b200.batch import MegakernelBatchDecoder
+    from megaqwen_b200.decoder import MegakernelDecoder
+    from megaqwen_b200.synthetic import random_lengths
+    spec = QWEN3_0_6B
+    out = {}
+    lw = [t.to(dev) for t in w["layer_weights"]]
+    embed = w["embed_weight"].to(dev)
+    common = (embed, lw, w["final_norm_weight"].to(dev), embed)
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    # config 3
+    dec = MegakernelDecoder(*common, w["cos_table"].to(dev), w["sin_table"].to(dev), spec.num_layers, MAX_SEQ, 1024)
+    prompt = random_prompt(spec, 1024, 3, 0).to(dev)
+    best = 1e9
+    for _ in range(4):
+        dec.reset()
+        torch.cuda.synchronize(dev)
+        e0, e1 = events()
+        e0.record(); tok = dec.prefill_step(prompt); e1.record()
+        torch.cuda.synchronize(dev)
+        best = min(best, e0.elapsed_time(e1))
+    e0, e1 = events()
+    e0.record(); dec._chain(tok, 32, True); e1.record()
+    torch.cuda.synchronize(dev)
+    out["config3_prefill1024"] = {"prefill_ms": best, "prefill_tokens_per_s": 1024 / best * 1e3,
+                                  "prefill_tflops": spec.prefill_flops(1024) / best / 1e9,
+                                  "decode32_tokens_per_s": 32 / e0.elapsed_time(e1) * 1e3}
+    del dec
+    torch.cuda.empty_cache()
+
+    def batched(name, lens, steps, max_seq, cfg_idx):
+        B = len(lens)
+        cos, sin = w["cos_table"][:max_seq].contiguous().to(dev), w["sin_table"][:max_seq].contiguous().to(dev)
+        bd = MegakernelBatchDecoder(*common, cos, sin, spec.num_layers, max_seq, B, max(lens))
+        prompts = [random_prompt(spec, n, cfg_idx, i) for i, n in enumerate(lens)]
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        first = bd.prefill_batch(prompts)
+        torch.cuda.synchronize(dev)
+        t1 = time.perf_counter()
+        chunk = 32
+        bd.decode_batch_steps(first, chunk)                    # builds the graph
+        bd._positions[:B].copy_(torch.tensor(lens, dtype=torch.int32))
+        torch.cuda.synchronize(dev)
+        e0, e1 = events()
+        e0.record()
+        cur, done = first, 0
+        while done < steps:
+            o = bd.decode_batch_steps(cur, chunk)
+            cur = o[-1]
+            done += chunk
+        e1.record()
+        torch.cuda.synchronize(dev)
+        bd.check_status()
+        ms = e0.elapsed_time(e1)
+        mean_len = sum(lens) / B + steps / 2
+        step_bytes = spec.weight_bytes() + B * spec.kv_bytes_per_position() * (mean_len + 1)
+        out[name] = {"batch": B, "prefill_tokens_per_s": sum(lens) / (t1 - t0), "decode_tokens_per_s": B * steps / ms * 1e3,
+                     "ms_per_step": ms / steps, "achieved_GBps": step_bytes / (ms / steps * 1e-3) / 1e9}
+        del bd
+        torch.cuda.empty_cache()
+
+    batched("config4_batch32_ragged", random_lengths(32, 256, 512), 128, 1024, 4)
+    batched("config5_batch64_ctx1024", [1024] * 64, 256, 1280, 5)
+    return out
+
+
 def run_ours(args):
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
@@ -222,6 +295,13 @@ def run_ours(args):
         "clocks": clocks,
         "wall_s": wall,
     }
+    if args.other_configs and world == 1:
+        try:
+            del dec
+            torch.cuda.empty_cache()
+            line["other_configs"] = measure_other_configs(dev, w)
+        except Exception as exc:
+            line["other_configs"] = {"error": repr(exc)[:200]}
     if not args.no_cpu and world == 1:
         try:
             tps, prefill_s, cores = cpu_reference(16)
@@ -288,6 +368,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunk", type=int, default=32, help="decode steps per CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-other-configs", dest="other_configs", action="store_false",
+                    help="skip the extra single-GPU measurements of configs 3-5")
     ap.add_argument("--ncu-case", type=int, default=0, help="run N eager decode steps at --ncu-pos and exit (profiler case)")
     ap.add_argument("--ncu-pos", type=int, default=PROMPT_LEN)
     ap.add_argument("--ncu-prefill", type=int, default=0, help="profiler case: N prefills of this many tokens instead of decode steps")
