@@ -42,6 +42,32 @@ namespace mq {
 #define EXPF(a) 0
 #endif
 
+// Timeline builds (-DMQ_TIMELINE) stamp %globaltimer at entry (0), after the dependency
+// wait (1), before the dot products (2) and at the end (3) of every CTA of every kernel of
+// the last step executed; mq_debug_timeline copies the table out.
+#ifdef MQ_TIMELINE
+constexpr int TL_KERNELS = 160, TL_CTAS = 148;
+__device__ unsigned long long g_tl[TL_KERNELS * TL_CTAS * 8];
+#define TL(a, w)                                                                              \
+    do {                                                                                      \
+        const int cta_ = blockIdx.x;                                                          \
+        if (threadIdx.x == 0 && cta_ < TL_CTAS && (unsigned)(a).kseq < (unsigned)TL_KERNELS) {                    \
+            unsigned long long t_;                                                            \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
+            g_tl[((a).kseq * TL_CTAS + cta_) * 8 + (w)] = t_;                                 \
+            if ((w) == 0) {                                                                   \
+                unsigned sm_;                                                                 \
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));                              \
+                g_tl[((a).kseq * TL_CTAS + cta_) * 8 + 7] = sm_;                              \
+            }                                                                                 \
+        }                                                                                     \
+    } while (0)
+#define TL_SYNC() __syncthreads()
+#else
+#define TL(a, w) do { } while (0)
+#define TL_SYNC() do { } while (0)
+#endif
+
 struct DecodeArgs {
     const bf16* embed;
     const bf16* final_norm;
@@ -66,21 +92,13 @@ struct DecodeArgs {
     int max_seq;
     int nsplit;
     int chunk_cap;
+    int kseq;        // launch index within the step (timeline builds only)
     int exp_flags;   // experiments (benchmarks only): 1 skip dot products, 2 skip RMSNorm, 4 no weight copies in the per-layer GEMV kernels
 };
 
-__device__ __forceinline__ float dot_x(const DecodeArgs& a, const bf16* wrow, const float (&x)[32], int lane) {
-    return (EXPF(a) & 1) ? x[0] : dot_slice(wrow, x, lane);
-}
-
 constexpr int GEMV_THREADS = 256;
-constexpr int DOWN_THREADS = 384;
-constexpr int MIN_GRID = 128;                 // row caps below assume at least this many CTAs
-constexpr int QKV_MAXROWS = QKV / MIN_GRID;   // 32 rows x 2 KB
-constexpr int O_MAXROWS = H / MIN_GRID;       // 8 rows x 4 KB
-constexpr int GU_MAXROWS = I / MIN_GRID;      // 24 rows x 2 KB, twice
-constexpr int DN_MAXROWS = H / MIN_GRID;      // 8 rows x 6 KB
-constexpr int MAX_BARS = 8;
+constexpr int DOWN_THREADS = 256;
+constexpr int MIN_GRID = 128;                 // at most 32 qkv, 24 gate/up and 8 o/down rows per CTA
 
 __device__ __forceinline__ void row_range(int total, int& r0, int& n) {
     r0 = (int)(((long long)blockIdx.x * total) / gridDim.x);
@@ -91,44 +109,73 @@ __device__ __forceinline__ void row_range(int total, int& r0, int& n) {
 // ---------------------------------------------------------------- k_qkv
 // qkv[r] = bf16( [Wq;Wk;Wv][r,:] . rmsnorm(hidden) ), r in this CTA's rows.
 // For layer 0 the residual stream is first gathered from the embedding table.
+//
+// All four GEMV kernels have the same shape.  Before the dependency wait, warp 0 copies
+// the CTA's weight rows (and the norm weight) into shared memory, one bulk copy per row
+// so that rows can be padded (mq_device.cuh, mma_gemv).  After the wait the CTA reads the
+// activation vector ONCE (every warp of every CTA reading the same sixteen L2 lines
+// serialises on those lines for over a microsecond), normalises it cooperatively, and the
+// warps split the K dimension of an mma.sync GEMV; partial sums meet in shared memory and
+// are added in a fixed order.
+constexpr int WPAD = 8;
+constexpr int H_LD = H + WPAD, O_LD = QSZ + WPAD, DN_LD = I + WPAD;
+
+// Cooperative RMSNorm of a 1024-wide vector by 256 threads, four elements each:
+// xs <- bf16(w * bf16(x * rsqrt(mean(x^2) + eps))).  Two block barriers, the second by the caller.
+__device__ __forceinline__ void stage_norm_1024(const DecodeArgs& a, bf16* xs, float* ssp, const uint2 u, const bf16* nrm,
+                                                uint64_t* bar, int tid) {
+    const float x0 = bf_lo(u.x), x1 = bf_hi(u.x), x2 = bf_lo(u.y), x3 = bf_hi(u.y);
+    const float part = warp_sum(fmaf(x0, x0, fmaf(x1, x1, fmaf(x2, x2, x3 * x3))));
+    if ((tid & 31) == 0) ssp[tid >> 5] = part;
+    __syncthreads();
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < GEMV_THREADS / 32; ++i) ss += ssp[i];
+    const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+    if (!(EXPF(a) & 4)) mbar_wait(bar, 0, a.status);   // norm weight and weight rows have landed
+    uint2 o = u;
+    if (!(EXPF(a) & 6)) {
+        const uint2 wv = *reinterpret_cast<const uint2*>(nrm + tid * 4);
+        o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(x0 * r)), rbf(bf_hi(wv.x) * rbf(x1 * r)));
+        o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(x2 * r)), rbf(bf_hi(wv.y) * rbf(x3 * r)));
+    }
+    *reinterpret_cast<uint2*>(xs + tid * 4) = o;
+}
+
 __global__ void __launch_bounds__(GEMV_THREADS) k_qkv(DecodeArgs a, MqLayerWeights w, int layer) {
+    TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
-    bf16* nrm = wbuf + (size_t)QKV_MAXROWS * H;      // input RMSNorm weight, copied with the first chunk: a
-                                                     // global load after the wait would be an HBM miss
-                                                     // (the weight stream evicts everything else from L2)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)(QKV_MAXROWS + 1) * H * 2);
+    bf16* nrm = reinterpret_cast<bf16*>(smem_raw);                // input RMSNorm weight
+    bf16* xs = nrm + H;                                           // normalised input vector
+    float* red = reinterpret_cast<float*>(xs + H);                // [8 warps][32 rows]
+    float* ssp = red + (GEMV_THREADS / 32) * 32;                  // [8]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(ssp + 8);
+    bf16* wbuf = reinterpret_cast<bf16*>(bar + 2);                // [rows of this CTA][H_LD]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int r0, n;
     row_range(QKV, r0, n);
-    constexpr int CH = 8;  // rows per barrier
-    if (tid == 0 && !(EXPF(a) & 4)) {
-        const int nch = (n + CH - 1) / CH;
-        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
-        mbar_fence_init();
-        for (int c = 0; c < nch; ++c) {
-            const int a0 = r0 + c * CH, a1 = min(r0 + n, a0 + CH);
-            mbar_expect_tx(&bars[c], (uint32_t)(a1 - a0) * H * 2 + (c == 0 ? H * 2 : 0));
-            if (c == 0) bulk_g2s(nrm, w.input_layernorm, H * 2, &bars[0]);
-            // a chunk may straddle the q|k|v matrix boundaries
-            int r = a0;
-            while (r < a1) {
-                const bf16* base;
-                int local, lim;
-                if (r < QSZ) { base = (const bf16*)w.q_proj; local = r; lim = QSZ; }
-                else if (r < QSZ + KVSZ) { base = (const bf16*)w.k_proj; local = r - QSZ; lim = QSZ + KVSZ; }
-                else { base = (const bf16*)w.v_proj; local = r - QSZ - KVSZ; lim = QKV; }
-                const int e = min(a1, lim);
-                bulk_g2s(wbuf + (size_t)(r - r0) * H, base + (size_t)local * H, (uint32_t)(e - r) * H * 2, &bars[c]);
-                r = e;
-            }
+    if (warp == 0 && !(EXPF(a) & 4)) {
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            mbar_fence_init();
+            mbar_expect_tx(bar, (uint32_t)(n + 1) * H * 2);
+            bulk_g2s(nrm, w.input_layernorm, H * 2, bar);
+        }
+        __syncwarp();
+        if (lane < n) {
+            const int r = r0 + lane;
+            const bf16* src = r < QSZ ? (const bf16*)w.q_proj + (size_t)r * H
+                            : r < QSZ + KVSZ ? (const bf16*)w.k_proj + (size_t)(r - QSZ) * H
+                                             : (const bf16*)w.v_proj + (size_t)(r - QSZ - KVSZ) * H;
+            bulk_g2s(wbuf + (size_t)lane * H_LD, src, H * 2, bar);
         }
     }
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
+    pdl_wait_cta();
+    TL(a, 1);
 
-    float x[32];
+    const bf16* src = a.hidden;
     if (layer == 0) {
         int tok = ld_cg_i32(a.in_token);
         const int p = ld_cg_i32(a.pos);
@@ -137,35 +184,37 @@ __global__ void __launch_bounds__(GEMV_THREADS) k_qkv(DecodeArgs a, MqLayerWeigh
             if (p < 0 || p >= a.max_seq) atomicOr(a.status, MQ_STATUS_BAD_POSITION);
         }
         tok = min(max(tok, 0), a.vocab - 1);
-        const bf16* src = a.embed + (size_t)tok * H;
-        if (blockIdx.x == 0 && warp == 0) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                *reinterpret_cast<uint4*>(a.hidden + j * 256 + lane * 8) = ld_cg_u4(src + j * 256 + lane * 8);
-        }
-        load_x_slice(x, src, lane);
-    } else {
-        load_x_slice(x, a.hidden, lane);
+        src = a.embed + (size_t)tok * H;
     }
-    if (!(EXPF(a) & 4)) mbar_wait(&bars[0], 0, a.status);
-    if (!(EXPF(a) & 2)) rmsnorm_slice(x, nrm, lane);
+    const uint2 u = ld_cg_u2(src + tid * 4);
+    if (layer == 0 && blockIdx.x == 0) *reinterpret_cast<uint2*>(a.hidden + tid * 4) = u;
+    stage_norm_1024(a, xs, ssp, u, nrm, bar, tid);
+    __syncthreads();
+    TL(a, 2);
 
-    for (int i = warp; i < n; i += 16) {
-        const int i2 = i + 8;
-        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
-        float d0 = dot_x(a, wbuf + (size_t)i * H, x, lane);
-        float d1 = 0.f;
-        if (i2 < n) {
-            if (!(EXPF(a) & 4)) mbar_wait(&bars[i2 / CH], 0, a.status);
-            d1 = dot_x(a, wbuf + (size_t)i2 * H, x, lane);
-        }
-        d0 = warp_sum(d0);
-        d1 = warp_sum(d1);
-        if (lane == 0) {
-            a.qkv[r0 + i] = __float2bfloat16_rn(d0);
-            if (i2 < n) a.qkv[r0 + i2] = __float2bfloat16_rn(d1);
+    uint32_t rowaddr[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+        rowaddr[t] = smem_u32(wbuf) + (uint32_t)((min(t * 16 + (lane & 15), n - 1) * H_LD + (lane >> 4) * 8) * 2);
+    float c[2][4] = {};
+    constexpr int KS = H / 16 / (GEMV_THREADS / 32);   // k-steps per warp
+    if (!(EXPF(a) & 1)) mma_gemv<2>(rowaddr, smem_u32(xs), warp * KS, warp * KS + KS, lane, c);
+    if ((lane & 3) == 0) {
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            red[warp * 32 + t * 16 + (lane >> 2)] = c[t][0];
+            red[warp * 32 + t * 16 + 8 + (lane >> 2)] = c[t][2];
         }
     }
+    __syncthreads();
+    if (tid < n) {
+        float s = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < GEMV_THREADS / 32; ++wi) s += red[wi * 32 + tid];
+        a.qkv[r0 + tid] = __float2bfloat16_rn(s);
+    }
+    TL_SYNC();
+    TL(a, 3);
 }
 
 // ---------------------------------------------------------------- k_attn
@@ -201,7 +250,23 @@ __device__ __forceinline__ void norm_rope_head(const bf16* raw, const bf16* wn, 
     }
 }
 
+// CTAs of the attention grid that have no positions to work on keep their SM's shared-memory
+// slot until the working CTAs are done (counters[NKV + 1] counts them, the last one publishes
+// the launch's tag in counters[NKV + 2]).  If they left at once, their SMs would be empty for
+// a moment and the block scheduler would put two CTAs of the next kernel on some of them.
+// The hold is only a scheduling aid: it is bounded and a stale tag merely ends it early.
+constexpr long long ATT_HOLD_CYCLES = 200000;
+__device__ __forceinline__ void attn_cta_done(const DecodeArgs& a, unsigned int n_working, unsigned int tag) {
+    const unsigned int t = atomicAdd(&a.counters[NKV + 1], 1u);
+    if (t == n_working - 1u) {
+        a.counters[NKV + 1] = 0u;
+        __threadfence();
+        atomicExch(&a.counters[NKV + 2], tag);
+    }
+}
+
 __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeights w, int layer) {
+    TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int cap = a.chunk_cap;
     bf16* kt = reinterpret_cast<bf16*>(smem_raw);                     // [cap][128]
@@ -218,7 +283,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = blockIdx.x, s = blockIdx.y;
+    const int g = blockIdx.x % NKV, s = blockIdx.x / NKV;   // CTAs beyond 8 * nsplit only hold their SM's slot
     const int pos = ld_cg_i32(a.pos);
     const bool valid = pos >= 0 && pos < a.max_seq;
     const int len = pos + 1;
@@ -227,7 +292,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     int chunk = (len + a.nsplit - 1) / a.nsplit;
     chunk = (len <= cap) ? cap : max(ATT_MIN_CHUNK, (chunk + 15) & ~15);
     const int n_act = valid ? (len + chunk - 1) / chunk : 0;
-    const bool active = s < n_act && chunk <= cap;
+    const bool active = s < a.nsplit && s < n_act && chunk <= cap;
     if (valid && chunk > cap && tid == 0) atomicOr(a.status, MQ_STATUS_BAD_POSITION);
     const int c0 = s * chunk;
     const int n = active ? min(len, c0 + chunk) - c0 : 0;  // positions handled here
@@ -256,8 +321,20 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     }
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
-    if (!active) return;
+    pdl_wait_cta();
+    TL(a, 1);
+    const unsigned int tag = (unsigned int)pos * 64u + (unsigned int)layer + 1u;
+    const unsigned int n_working = (unsigned int)(NKV * n_act);
+    if (!active) {
+        if (tid == 0 && n_act > 0 && chunk <= cap) {
+            const long long t0 = clock64();
+            unsigned int seen;
+            do {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.counters + NKV + 2) : "memory");
+            } while (seen != tag && clock64() - t0 < ATT_HOLD_CYCLES);
+        }
+        return;
+    }
 
     // ---- per-head norm + RoPE of q (both heads), and of the new k; v raw
     if (warp < 2) {
@@ -283,6 +360,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
         *reinterpret_cast<uint2*>(a.v_cache + head_off + (size_t)pos * D + 4 * lane) = u;
     }
     __syncthreads();
+    TL(a, 2);
     if (n_cached > 0) mbar_wait(&bars[0], 0, a.status);
 
     if (n_cached > 0) mbar_wait(&bars[1], 0, a.status);
@@ -367,6 +445,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     const int qhead = 2 * g + hh;
     if (n_act == 1) {
         a.attn[qhead * D + d] = __float2bfloat16_rn(acc / ml[hh * 2 + 1]);
+        __syncthreads();
+        if (tid == 0) attn_cta_done(a, n_working, tag);
+        TL(a, 3);
         return;
     }
     // ---- split-KV: publish the partial, the last CTA of this kv head merges
@@ -380,7 +461,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
         s_last = (t == (unsigned int)(n_act - 1));
     }
     __syncthreads();
-    if (!s_last) return;
+    TL(a, 3);
+    if (!s_last) {
+        if (tid == 0) attn_cta_done(a, n_working, tag);
+        return;
+    }
     __threadfence();
     // Merge of the n_act (<= 64) partials of this thread's head.  (m, l) of split
     // lane and lane + 32 are fetched by one load each per lane, the accumulator
@@ -416,139 +501,180 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
         }
     }
     a.attn[qhead * D + d] = __float2bfloat16_rn(num / den);
-    if (tid == 0) a.counters[g] = 0u;
+    __syncthreads();
+    if (tid == 0) {
+        a.counters[g] = 0u;
+        attn_cta_done(a, n_working, tag);
+    }
+    TL(a, 3);
 }
 
 // ---------------------------------------------------------------- k_oproj
 // hidden[r] = bf16( hidden[r] + bf16( Wo[r,:] . attn ) )
 __global__ void __launch_bounds__(GEMV_THREADS) k_oproj(DecodeArgs a, MqLayerWeights w) {
+    TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)O_MAXROWS * QSZ * 2);
-    float* part = reinterpret_cast<float*>(bars + MAX_BARS);  // [rows][2]
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                 // the CTA's copy of the attention output
+    float* red = reinterpret_cast<float*>(xs + QSZ);              // [8 warps][8 rows]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(red + (GEMV_THREADS / 32) * 8);
+    bf16* wbuf = reinterpret_cast<bf16*>(bar + 2);                // [rows of this CTA][O_LD]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int r0, n;
     row_range(H, r0, n);
-    constexpr int CH = 4;
-    if (tid == 0 && !(EXPF(a) & 4)) {
-        const int nch = (n + CH - 1) / CH;
-        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
-        mbar_fence_init();
-        for (int c = 0; c < nch; ++c) {
-            const int a0 = c * CH, a1 = min(n, a0 + CH);
-            const uint32_t bytes = (uint32_t)(a1 - a0) * QSZ * 2;
-            mbar_expect_tx(&bars[c], bytes);
-            bulk_g2s(wbuf + (size_t)a0 * QSZ, (const bf16*)w.o_proj + (size_t)(r0 + a0) * QSZ, bytes, &bars[c]);
+    if (warp == 0 && !(EXPF(a) & 4)) {
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            mbar_fence_init();
+            mbar_expect_tx(bar, (uint32_t)n * QSZ * 2);
         }
+        __syncwarp();
+        if (lane < n) bulk_g2s(wbuf + (size_t)lane * O_LD, (const bf16*)w.o_proj + (size_t)(r0 + lane) * QSZ, QSZ * 2, bar);
     }
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
+    pdl_wait_cta();
+    TL(a, 1);
 
-    const int slice = warp & 1, rg = warp >> 1;
-    float x[32];
-    load_x_slice(x, a.attn + slice * 1024, lane);
-    for (int i = rg; i < n; i += 4) {
-        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
-        const float dsum = warp_sum(dot_x(a, wbuf + (size_t)i * QSZ + slice * 1024, x, lane));
-        if (lane == 0) part[i * 2 + slice] = dsum;
-    }
+    *reinterpret_cast<uint4*>(xs + tid * 8) = ld_cg_u4(a.attn + tid * 8);   // 256 threads x 16 B = 2048 bf16
+    unsigned short hb = 0;
+    if (tid < n) hb = __ldcg(reinterpret_cast<const unsigned short*>(a.hidden + r0 + tid));
+    if (!(EXPF(a) & 4)) mbar_wait(bar, 0, a.status);
     __syncthreads();
+    TL(a, 2);
+
+    uint32_t rowaddr[1] = {smem_u32(wbuf) + (uint32_t)((min(lane & 15, n - 1) * O_LD + (lane >> 4) * 8) * 2)};
+    float c[1][4] = {};
+    constexpr int KS = QSZ / 16 / (GEMV_THREADS / 32);
+    if (!(EXPF(a) & 1)) mma_gemv<1>(rowaddr, smem_u32(xs), warp * KS, warp * KS + KS, lane, c);
+    if ((lane & 3) == 0) red[warp * 8 + (lane >> 2)] = c[0][0];
+    TL(a, 4);
+    __syncthreads();
+    TL(a, 5);
     if (tid < n) {
-        const float o = rbf(part[tid * 2] + part[tid * 2 + 1]);
-        const unsigned short hb = __ldcg(reinterpret_cast<const unsigned short*>(a.hidden + r0 + tid));
+        float s = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < GEMV_THREADS / 32; ++wi) s += red[wi * 8 + tid];
         const float hres = __uint_as_float((uint32_t)hb << 16);
-        a.hidden[r0 + tid] = __float2bfloat16_rn(hres + o);
+        a.hidden[r0 + tid] = __float2bfloat16_rn(hres + rbf(s));
     }
+    TL_SYNC();
+    TL(a, 3);
 }
 
 // ---------------------------------------------------------------- k_gateup
 // act[i] = bf16( bf16(silu(bf16(Wg[i,:].x))) * bf16(Wu[i,:].x) ), x = rmsnorm(hidden)
 __global__ void __launch_bounds__(GEMV_THREADS) k_gateup(DecodeArgs a, MqLayerWeights w) {
+    TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    bf16* gbuf = reinterpret_cast<bf16*>(smem_raw);
-    bf16* ubuf = gbuf + (size_t)GU_MAXROWS * H;
-    bf16* nrm = ubuf + (size_t)GU_MAXROWS * H;       // post-attention RMSNorm weight (see k_qkv)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)(2 * GU_MAXROWS + 1) * H * 2);
+    bf16* nrm = reinterpret_cast<bf16*>(smem_raw);                // post-attention RMSNorm weight
+    bf16* xs = nrm + H;
+    float* red = reinterpret_cast<float*>(xs + H);                // [8 warps][48 rows]
+    float* ssp = red + (GEMV_THREADS / 32) * 48;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(ssp + 8);
+    bf16* wbuf = reinterpret_cast<bf16*>(bar + 2);                // [2 x rows of this CTA][H_LD]: gate rows, then up rows
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int r0, n;
     row_range(I, r0, n);
-    constexpr int CH = 8;
-    if (tid == 0 && !(EXPF(a) & 4)) {
-        const int nch = (n + CH - 1) / CH;
-        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
-        mbar_fence_init();
-        for (int c = 0; c < nch; ++c) {
-            const int a0 = c * CH, a1 = min(n, a0 + CH);
-            const uint32_t bytes = (uint32_t)(a1 - a0) * H * 2;
-            mbar_expect_tx(&bars[c], 2 * bytes + (c == 0 ? H * 2 : 0));
-            if (c == 0) bulk_g2s(nrm, w.post_attn_layernorm, H * 2, &bars[0]);
-            bulk_g2s(gbuf + (size_t)a0 * H, (const bf16*)w.gate_proj + (size_t)(r0 + a0) * H, bytes, &bars[c]);
-            bulk_g2s(ubuf + (size_t)a0 * H, (const bf16*)w.up_proj + (size_t)(r0 + a0) * H, bytes, &bars[c]);
+    if (warp == 0 && !(EXPF(a) & 4)) {
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            mbar_fence_init();
+            mbar_expect_tx(bar, (uint32_t)(2 * n + 1) * H * 2);
+            bulk_g2s(nrm, w.post_attn_layernorm, H * 2, bar);
+        }
+        __syncwarp();
+        for (int cidx = lane; cidx < 2 * n; cidx += 32) {
+            const bf16* src = cidx < n ? (const bf16*)w.gate_proj + (size_t)(r0 + cidx) * H
+                                       : (const bf16*)w.up_proj + (size_t)(r0 + cidx - n) * H;
+            bulk_g2s(wbuf + (size_t)cidx * H_LD, src, H * 2, bar);
         }
     }
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
+    pdl_wait_cta();
+    TL(a, 1);
 
-    float x[32];
-    load_x_slice(x, a.hidden, lane);
-    if (!(EXPF(a) & 4)) mbar_wait(&bars[0], 0, a.status);
-    if (!(EXPF(a) & 2)) rmsnorm_slice(x, nrm, lane);
-    for (int i = warp; i < n; i += 8) {
-        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
-        float gsum = dot_x(a, gbuf + (size_t)i * H, x, lane);
-        float usum = dot_x(a, ubuf + (size_t)i * H, x, lane);
-        gsum = warp_sum(gsum);
-        usum = warp_sum(usum);
-        if (lane == 0) {
-            const float act = rbf(silu_f32(rbf(gsum)));
-            a.act[r0 + i] = __float2bfloat16_rn(act * rbf(usum));
+    const uint2 u = ld_cg_u2(a.hidden + tid * 4);
+    stage_norm_1024(a, xs, ssp, u, nrm, bar, tid);
+    __syncthreads();
+    TL(a, 2);
+
+    uint32_t rowaddr[3];
+#pragma unroll
+    for (int t = 0; t < 3; ++t)
+        rowaddr[t] = smem_u32(wbuf) + (uint32_t)((min(t * 16 + (lane & 15), 2 * n - 1) * H_LD + (lane >> 4) * 8) * 2);
+    float c[3][4] = {};
+    constexpr int KS = H / 16 / (GEMV_THREADS / 32);
+    if (!(EXPF(a) & 1)) mma_gemv<3>(rowaddr, smem_u32(xs), warp * KS, warp * KS + KS, lane, c);
+    if ((lane & 3) == 0) {
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+            red[warp * 48 + t * 16 + (lane >> 2)] = c[t][0];
+            red[warp * 48 + t * 16 + 8 + (lane >> 2)] = c[t][2];
         }
     }
+    __syncthreads();
+    if (tid < n) {
+        float gsum = 0.f, usum = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < GEMV_THREADS / 32; ++wi) { gsum += red[wi * 48 + tid]; usum += red[wi * 48 + n + tid]; }
+        const float act = rbf(silu_f32(rbf(gsum)));
+        a.act[r0 + tid] = __float2bfloat16_rn(act * rbf(usum));
+    }
+    TL_SYNC();
+    TL(a, 3);
 }
 
 // ---------------------------------------------------------------- k_down
 // hidden[r] = bf16( hidden[r] + bf16( Wd[r,:] . act ) )
 __global__ void __launch_bounds__(DOWN_THREADS) k_down(DecodeArgs a, MqLayerWeights w) {
+    TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    bf16* wbuf = reinterpret_cast<bf16*>(smem_raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)DN_MAXROWS * I * 2);
-    float* part = reinterpret_cast<float*>(bars + MAX_BARS);  // [rows][3]
+    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                 // the CTA's copy of the MLP activation
+    float* red = reinterpret_cast<float*>(xs + I);                // [8 warps][8 rows]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(red + (DOWN_THREADS / 32) * 8);
+    bf16* wbuf = reinterpret_cast<bf16*>(bar + 2);                // [rows of this CTA][DN_LD]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int r0, n;
     row_range(H, r0, n);
-    constexpr int CH = 4;
-    if (tid == 0 && !(EXPF(a) & 4)) {
-        const int nch = (n + CH - 1) / CH;
-        for (int c = 0; c < nch; ++c) mbar_init(&bars[c], 1);
-        mbar_fence_init();
-        for (int c = 0; c < nch; ++c) {
-            const int a0 = c * CH, a1 = min(n, a0 + CH);
-            const uint32_t bytes = (uint32_t)(a1 - a0) * I * 2;
-            mbar_expect_tx(&bars[c], bytes);
-            bulk_g2s(wbuf + (size_t)a0 * I, (const bf16*)w.down_proj + (size_t)(r0 + a0) * I, bytes, &bars[c]);
+    if (warp == 0 && !(EXPF(a) & 4)) {
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            mbar_fence_init();
+            mbar_expect_tx(bar, (uint32_t)n * I * 2);
         }
+        __syncwarp();
+        if (lane < n) bulk_g2s(wbuf + (size_t)lane * DN_LD, (const bf16*)w.down_proj + (size_t)(r0 + lane) * I, I * 2, bar);
     }
     __syncthreads();
     pdl_trigger();
-    pdl_wait();
+    pdl_wait_cta();
+    TL(a, 1);
 
-    const int slice = warp % 3, rg = warp / 3;
-    float x[32];
-    load_x_slice(x, a.act + slice * 1024, lane);
-    for (int i = rg; i < n; i += 4) {
-        if (!(EXPF(a) & 4)) mbar_wait(&bars[i / CH], 0, a.status);
-        const float dsum = warp_sum(dot_x(a, wbuf + (size_t)i * I + slice * 1024, x, lane));
-        if (lane == 0) part[i * 3 + slice] = dsum;
-    }
+    for (int i = tid; i < I / 8; i += DOWN_THREADS) *reinterpret_cast<uint4*>(xs + i * 8) = ld_cg_u4(a.act + i * 8);
+    unsigned short hb = 0;
+    if (tid < n) hb = __ldcg(reinterpret_cast<const unsigned short*>(a.hidden + r0 + tid));
+    if (!(EXPF(a) & 4)) mbar_wait(bar, 0, a.status);
     __syncthreads();
+    TL(a, 2);
+
+    uint32_t rowaddr[1] = {smem_u32(wbuf) + (uint32_t)((min(lane & 15, n - 1) * DN_LD + (lane >> 4) * 8) * 2)};
+    float c[1][4] = {};
+    constexpr int KS = I / 16 / (DOWN_THREADS / 32);
+    if (!(EXPF(a) & 1)) mma_gemv<1>(rowaddr, smem_u32(xs), warp * KS, warp * KS + KS, lane, c);
+    if ((lane & 3) == 0) red[warp * 8 + (lane >> 2)] = c[0][0];
+    TL(a, 4);
+    __syncthreads();
+    TL(a, 5);
     if (tid < n) {
-        const float dn = rbf(part[tid * 3] + part[tid * 3 + 1] + part[tid * 3 + 2]);
-        const unsigned short hb = __ldcg(reinterpret_cast<const unsigned short*>(a.hidden + r0 + tid));
+        float s = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < DOWN_THREADS / 32; ++wi) s += red[wi * 8 + tid];
         const float hres = __uint_as_float((uint32_t)hb << 16);
-        a.hidden[r0 + tid] = __float2bfloat16_rn(hres + dn);
+        a.hidden[r0 + tid] = __float2bfloat16_rn(hres + rbf(s));
     }
+    TL_SYNC();
+    TL(a, 3);
 }
 
 // ---------------------------------------------------------------- k_lmhead
@@ -567,6 +693,7 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
 }
 
 __global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
+    TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
     bf16* ring = reinterpret_cast<bf16*>(smem_raw);  // [LM_STAGES][LM_ROWS][H]
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)LM_STAGES * LM_ROWS * H * 2);
@@ -599,7 +726,8 @@ __global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
     // The trigger comes AFTER the wait: the next decode step may only begin once
     // every kernel of this step has completed, which makes the KV rows written by
     // this step safe to prefetch in the next step's attention prologues.
-    pdl_wait();
+    pdl_wait_cta();
+    TL(a, 1);
     pdl_trigger();
 
     if (warp == LM_CONSUMERS) {
@@ -658,6 +786,7 @@ __global__ void __launch_bounds__(LM_THREADS) k_lmhead(DecodeArgs a) {
             a.counters[NKV] = 0u;
         }
     }
+    TL(a, 3);
 }
 
 // ---------------------------------------------------------------- small helpers
@@ -682,12 +811,29 @@ struct DeviceState {
 };
 static DeviceState g_dev[64];
 
-static size_t smem_qkv() { return (size_t)(QKV_MAXROWS + 1) * H * 2 + MAX_BARS * 8; }
-static size_t smem_oproj() { return (size_t)O_MAXROWS * QSZ * 2 + MAX_BARS * 8 + O_MAXROWS * 2 * 4; }
-static size_t smem_gateup() { return (size_t)(2 * GU_MAXROWS + 1) * H * 2 + MAX_BARS * 8; }
-static size_t smem_down() { return (size_t)DN_MAXROWS * I * 2 + MAX_BARS * 8 + DN_MAXROWS * 3 * 4; }
+static int rows_per_cta(int total, int grid) { return (total + grid - 1) / grid; }
+static size_t smem_qkv(int G) { return 2 * H * 2 + (GEMV_THREADS / 32) * 32 * 4 + 8 * 4 + 16 + (size_t)rows_per_cta(QKV, G) * H_LD * 2; }
+static size_t smem_oproj(int G) { return QSZ * 2 + (GEMV_THREADS / 32) * 8 * 4 + 16 + (size_t)rows_per_cta(H, G) * O_LD * 2; }
+static size_t smem_gateup(int G) { return 2 * H * 2 + (GEMV_THREADS / 32) * 48 * 4 + 8 * 4 + 16 + (size_t)2 * rows_per_cta(I, G) * H_LD * 2; }
+static size_t smem_down(int G) { return I * 2 + (DOWN_THREADS / 32) * 8 * 4 + 16 + (size_t)rows_per_cta(H, G) * DN_LD * 2; }
 static size_t smem_lmhead() { return (size_t)LM_STAGES * LM_ROWS * H * 2 + 2 * LM_STAGES * 8 + LM_CONSUMERS * 8 + 16 + H * 2; }
 static size_t smem_attn(int cap) { return (size_t)cap * D * 2 * 2 + (size_t)2 * cap * 4 + 2 * D * 4 + 4 * D * 4 + 4 * 4 + 32 * 4 + 16 * D * 4 + 4 * D * 2 + 3 * 8; }
+
+// Shared-memory slots.  The block scheduler places a CTA wherever its resources fit, and on
+// an idle GPU it hands a 148-CTA grid out per GPC, which puts two CTAs on eight SMs and none
+// on eight others; with kernels of unequal footprint it packs up to three CTAs of a small
+// kernel onto one SM.  A doubled-up SM takes twice as long, and the slowest SM sets the pace
+// of every kernel of the chain.  So the kernels of a step ask for shared memory in two
+// alternating sizes, A then B then A ..: A + B fill an SM exactly, two A never fit, and in
+// the steady state an SM always holds the running kernel's CTA plus the next kernel's
+// (which is prefetching its weights), so the slot a finishing CTA leaves takes exactly one
+// CTA of the kernel two places later.  Every kernel gets one CTA per SM.
+// (1.5 KB of an SM's 228 KB stay free for the 1 KB the system reserves per CTA and for static shared memory.)
+constexpr size_t SLOT_A_BYTES = 130 * 1024 + 512, SLOT_B_BYTES = 94 * 1024;
+static size_t slot(int index, size_t need) {
+    const size_t sz = (index & 1) ? SLOT_B_BYTES : SLOT_A_BYTES;
+    return need > sz ? need : sz;
+}
 
 constexpr int ATT_MAX_CAP = 384;    // positions per CTA: 384 * 520 B + 3 KB of shared memory
 constexpr int ATT_MAX_SPLIT = 64;
@@ -723,14 +869,14 @@ static int ensure_device(DeviceState** out) {
 // whose carve-out differs cannot be resident on an SM together, which would serialise
 // the programmatic-dependent-launch chain.
 #define MQ_SET_SMEM(k, bytes)                                                                   \
-    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes));     \
+    e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)slot(0, bytes)); \
     if (e != cudaSuccess) return (int)e;                                                        \
     e = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared); \
     if (e != cudaSuccess) return (int)e;
-        MQ_SET_SMEM(k_qkv, smem_qkv());
-        MQ_SET_SMEM(k_oproj, smem_oproj());
-        MQ_SET_SMEM(k_gateup, smem_gateup());
-        MQ_SET_SMEM(k_down, smem_down());
+        MQ_SET_SMEM(k_qkv, smem_qkv(MIN_GRID));
+        MQ_SET_SMEM(k_oproj, smem_oproj(MIN_GRID));
+        MQ_SET_SMEM(k_gateup, smem_gateup(MIN_GRID));
+        MQ_SET_SMEM(k_down, smem_down(MIN_GRID));
         MQ_SET_SMEM(k_lmhead, smem_lmhead());
         MQ_SET_SMEM(k_attn, smem_attn(ATT_MAX_CAP));
 #undef MQ_SET_SMEM
@@ -868,6 +1014,7 @@ extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf
     a.nsplit = nsplit;
     a.chunk_cap = cap;
     a.exp_flags = g_decode_exp_flags;
+    a.kseq = 0;
 
     const bool pdl = !(flags & MQ_FLAG_NO_PDL);
     const int G = st->sm_count;
@@ -875,18 +1022,24 @@ extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
         const bool first = (l == 0);
-        e = launch(k_qkv, dim3(G), dim3(GEMV_THREADS), smem_qkv(), stream, pdl && (!first || (flags & MQ_FLAG_CHAINED)), a, w, l);
+        a.kseq = 5 * l;
+        e = launch(k_qkv, dim3(G), dim3(GEMV_THREADS), slot(5 * l, smem_qkv(G)), stream, pdl && (!first || (flags & MQ_FLAG_CHAINED)), a, w, l);
         if (e != cudaSuccess) return (int)e;
-        e = launch(k_attn, dim3(NKV, nsplit), dim3(ATT_THREADS), smem_attn(cap), stream, pdl, a, w, l);
+        a.kseq = 5 * l + 1;
+        e = launch(k_attn, dim3(NKV * nsplit > G ? NKV * nsplit : G), dim3(ATT_THREADS), slot(5 * l + 1, smem_attn(cap)), stream, pdl, a, w, l);
         if (e != cudaSuccess) return (int)e;
-        e = launch(k_oproj, dim3(G), dim3(GEMV_THREADS), smem_oproj(), stream, pdl, a, w);
+        a.kseq = 5 * l + 2;
+        e = launch(k_oproj, dim3(G), dim3(GEMV_THREADS), slot(5 * l + 2, smem_oproj(G)), stream, pdl, a, w);
         if (e != cudaSuccess) return (int)e;
-        e = launch(k_gateup, dim3(G), dim3(GEMV_THREADS), smem_gateup(), stream, pdl, a, w);
+        a.kseq = 5 * l + 3;
+        e = launch(k_gateup, dim3(G), dim3(GEMV_THREADS), slot(5 * l + 3, smem_gateup(G)), stream, pdl, a, w);
         if (e != cudaSuccess) return (int)e;
-        e = launch(k_down, dim3(G), dim3(DOWN_THREADS), smem_down(), stream, pdl, a, w);
+        a.kseq = 5 * l + 4;
+        e = launch(k_down, dim3(G), dim3(DOWN_THREADS), slot(5 * l + 4, smem_down(G)), stream, pdl, a, w);
         if (e != cudaSuccess) return (int)e;
     }
-    e = launch(k_lmhead, dim3(G), dim3(LM_THREADS), smem_lmhead(), stream, pdl, a);
+    a.kseq = 5 * model->num_layers;
+    e = launch(k_lmhead, dim3(G), dim3(LM_THREADS), slot(5 * model->num_layers, smem_lmhead()), stream, pdl, a);
     if (e != cudaSuccess) return (int)e;
     return MQ_OK;
 }
@@ -974,3 +1127,13 @@ extern "C" int mq_launch_decode_noalloc(const MqModel* model, void* k_cache, voi
     // kernel must not be launched as a programmatic dependent of an earlier step.
     return mq_launch_decode(model, &buf, in_token, out_token, position, logits, flags & ~MQ_FLAG_CHAINED, stream_v);
 }
+
+#ifdef MQ_TIMELINE
+// Timeline builds only: copies the stamp table (TL_KERNELS x TL_CTAS x 4 u64) to the host.
+extern "C" int mq_debug_timeline(void* host_out, size_t bytes) {
+    if (!host_out || bytes > sizeof(mq::g_tl)) return MQ_ERR_BAD_ARG;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaMemcpyFromSymbol(host_out, mq::g_tl, bytes);
+}
+#endif

@@ -64,6 +64,14 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) { return __ldcg(p); }
 // completed and its memory is visible.  launch_dependents: allow the next
 // kernel of the stream to start its prologue.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The whole CTA waits for the preceding grid, but only warp 0 executes the wait; the other
+// warps sleep on the block barrier.  Warps parked in griddepcontrol.wait compete for issue
+// slots with the co-resident CTA of the running kernel (three waiting CTAs of eight warps
+// each made its dependent mma loop three times slower).
+__device__ __forceinline__ void pdl_wait_cta() {
+    if (threadIdx.x < 32) pdl_wait();
+    __syncthreads();
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- mbarrier + bulk copy
@@ -137,6 +145,48 @@ __device__ __forceinline__ void load_x_slice(float (&x)[32], const bf16* src, in
         x[j * 8 + 2] = bf_lo(u.y); x[j * 8 + 3] = bf_hi(u.y);
         x[j * 8 + 4] = bf_lo(u.z); x[j * 8 + 5] = bf_hi(u.z);
         x[j * 8 + 6] = bf_lo(u.w); x[j * 8 + 7] = bf_hi(u.w);
+    }
+}
+
+// ---------------------------------------------------------------- tensor-core GEMV
+// The per-layer decode kernels multiply a handful of weight rows (in shared memory) with
+// one activation vector.  Done with fp32 FMAs this takes about a thousand straight-line
+// instructions per warp, and a kernel that runs its code exactly once is bound by
+// instruction fetch; mma.sync m16n8k16 does sixteen rows x sixteen columns per
+// instruction in a short loop.  The vector is replicated over the eight B columns, so
+// every column of the accumulator holds the same sixteen dot products.
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+
+// Rows live in shared memory with a stride of K + 8 elements (16 bytes of padding), which
+// spreads the eight 16-byte rows of an ldmatrix over all banks.  Lane l addresses row
+// (l & 15) of a tile at column offset 8 * (l >> 4).  rowaddr[t] is that lane's byte address
+// for tile t at column 0; the warp accumulates k-steps [ks0, ks1) of 16 columns each.
+// Lanes 0, 4, .., 28 end with row l/4 in c[t][0] and row l/4 + 8 in c[t][2].
+template <int NT>
+__device__ __forceinline__ void mma_gemv(const uint32_t (&rowaddr)[NT], uint32_t xs_addr, int ks0, int ks1, int lane, float (&c)[NT][4]) {
+    const uint32_t xb = xs_addr + (uint32_t)(lane & 3) * 4u;
+#pragma unroll 2
+    for (int ks = ks0; ks < ks1; ++ks) {
+        const uint32_t b0 = lds32(xb + (uint32_t)ks * 32u), b1 = lds32(xb + (uint32_t)ks * 32u + 16u);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            uint32_t a[4];
+            ldsm4(a, rowaddr[t] + (uint32_t)ks * 32u);
+            mma16816(c[t], a, b0, b1);
+        }
     }
 }
 
