@@ -251,10 +251,11 @@ __device__ __forceinline__ void norm_rope_head(const bf16* raw, const bf16* wn, 
 }
 
 // CTAs of the attention grid that have no positions to work on keep their SM's shared-memory
-// slot until the working CTAs are done (counters[NKV + 1] counts them, the last one publishes
-// the launch's tag in counters[NKV + 2]).  If they left at once, their SMs would be empty for
-// a moment and the block scheduler would put two CTAs of the next kernel on some of them.
-// The hold is only a scheduling aid: it is bounded and a stale tag merely ends it early.
+// slot until every working CTA has passed its dependency wait (counters[NKV + 1] counts them,
+// the last one publishes the launch's tag in counters[NKV + 2]).  If they left the moment they
+// were launched, their SMs could be empty before the next kernel's CTA has arrived, and the
+// block scheduler would put two CTAs of that kernel on some of them.  The hold is only a
+// scheduling aid: it is bounded and a stale tag merely ends it early.
 constexpr long long ATT_HOLD_CYCLES = 200000;
 __device__ __forceinline__ void attn_cta_done(const DecodeArgs& a, unsigned int n_working, unsigned int tag) {
     const unsigned int t = atomicAdd(&a.counters[NKV + 1], 1u);
@@ -265,21 +266,31 @@ __device__ __forceinline__ void attn_cta_done(const DecodeArgs& a, unsigned int 
     }
 }
 
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+
+constexpr int KV_LD = D + 8;   // K/V rows are padded by 16 bytes in shared memory (conflict-free ldmatrix)
+
 __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeights w, int layer) {
     TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int cap = a.chunk_cap;
-    bf16* kt = reinterpret_cast<bf16*>(smem_raw);                     // [cap][128]
-    bf16* vt = kt + (size_t)cap * D;                                  // [cap][128]
-    float* sc = reinterpret_cast<float*>(vt + (size_t)cap * D);       // [2][cap]
-    float* qh = sc + 2 * cap;                                         // [2][128]
-    float* accb = qh + 2 * D;                                         // [2][2][128]
-    float* ml = accb + 4 * D;                                         // [2][2]
-    float* wm = ml + 4;                                               // [8][2] per-warp running max
+    bf16* kt = reinterpret_cast<bf16*>(smem_raw);                     // [cap][KV_LD]
+    bf16* vt = kt + (size_t)cap * KV_LD;                              // [cap][KV_LD]
+    bf16* qs = vt + (size_t)cap * KV_LD;                              // [2][D] normalised, rotated query heads
+    bf16* ps = qs + 2 * D;                                            // [8 warps][2][16] probabilities of the warp's tile
+    bf16* cst = ps + (ATT_THREADS / 32) * 32;                         // q_norm | k_norm | cos[pos] | sin[pos]
+    float* wm = reinterpret_cast<float*>(cst + 4 * D);                // [8][2] per-warp running max
     float* wl = wm + 16;                                              // [8][2] per-warp sum
-    float* wacc = wl + 16;                                            // [8][2][128] per-warp accumulators
-    bf16* cst = reinterpret_cast<bf16*>(wacc + 16 * D);               // q_norm | k_norm | cos[pos] | sin[pos]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(cst + 4 * D);        // [3]
+    float* ml = wl + 16;                                              // [2][2]
+    float* wacc = ml + 4;                                             // [8][2][128] per-warp accumulators
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -300,26 +311,24 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     const int n_cached = is_last ? n - 1 : n;
     const size_t head_off = ((size_t)(layer * NKV + g) * a.max_seq) * D;
 
-    if (tid == 0) {
-        mbar_init(&bars[0], 1);
-        mbar_init(&bars[1], 1);
-        mbar_init(&bars[2], 1);
-        mbar_fence_init();
-        if (active) {   // per-head norm weights and this position's RoPE rows (HBM misses if loaded after the wait)
-            mbar_expect_tx(&bars[2], 4 * D * 2);
-            bulk_g2s(cst, w.q_norm, D * 2, &bars[2]);
-            bulk_g2s(cst + D, w.k_norm, D * 2, &bars[2]);
-            bulk_g2s(cst + 2 * D, a.cos + (size_t)pos * D, D * 2, &bars[2]);
-            bulk_g2s(cst + 3 * D, a.sin + (size_t)pos * D, D * 2, &bars[2]);
+    // Everything fetched here was written by earlier steps (or is a weight): 16-byte async
+    // copies, issued before the dependency wait, into the padded rows.
+    if (active) {
+        if (tid < 64) {
+            const int v = tid >> 4, c = tid & 15;
+            const bf16* src = v == 0 ? (const bf16*)w.q_norm : v == 1 ? (const bf16*)w.k_norm
+                            : v == 2 ? a.cos + (size_t)pos * D : a.sin + (size_t)pos * D;
+            cp_async16(cst + v * D + c * 8, src + c * 8);
         }
-        if (n_cached > 0) {
-            mbar_expect_tx(&bars[0], (uint32_t)n_cached * D * 2);
-            bulk_g2s(kt, a.k_cache + head_off + (size_t)c0 * D, (uint32_t)n_cached * D * 2, &bars[0]);
-            mbar_expect_tx(&bars[1], (uint32_t)n_cached * D * 2);
-            bulk_g2s(vt, a.v_cache + head_off + (size_t)c0 * D, (uint32_t)n_cached * D * 2, &bars[1]);
+        const bf16* ksrc = a.k_cache + head_off + (size_t)c0 * D;
+        const bf16* vsrc = a.v_cache + head_off + (size_t)c0 * D;
+        for (int i = tid; i < n_cached * 16; i += ATT_THREADS) {
+            const int r = i >> 4, c = i & 15;
+            cp_async16(kt + (size_t)r * KV_LD + c * 8, ksrc + (size_t)r * D + c * 8);
+            cp_async16(vt + (size_t)r * KV_LD + c * 8, vsrc + (size_t)r * D + c * 8);
         }
+        cp_async_commit();
     }
-    __syncthreads();
     pdl_trigger();
     pdl_wait_cta();
     TL(a, 1);
@@ -335,20 +344,23 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
         }
         return;
     }
+    cp_async_wait_all();
+    __syncthreads();   // this thread's copies are complete; the barrier makes everybody's visible
+    // release the slot holders now: by this time the next kernel's CTA is resident on their SMs
+    if (tid == ATT_THREADS - 1) attn_cta_done(a, n_working, tag);
 
-    // ---- per-head norm + RoPE of q (both heads), and of the new k; v raw
+    // ---- per-head norm + RoPE of q (both heads), and of the new k; v raw; zero the V rows
+    //      between n and the end of the last 16-position tile (they are multiplied by p = 0)
     if (warp < 2) {
         float lo[2], hi[2];
-        mbar_wait(&bars[2], 0, a.status);
         norm_rope_head(a.qkv + (2 * g + warp) * D, cst, cst + 2 * D, cst + 3 * D, lane, lo, hi);
-        qh[warp * D + 2 * lane] = lo[0]; qh[warp * D + 2 * lane + 1] = lo[1];
-        qh[warp * D + 64 + 2 * lane] = hi[0]; qh[warp * D + 64 + 2 * lane + 1] = hi[1];
+        *reinterpret_cast<uint32_t*>(qs + warp * D + 2 * lane) = pack_bf16x2(lo[0], lo[1]);
+        *reinterpret_cast<uint32_t*>(qs + warp * D + 64 + 2 * lane) = pack_bf16x2(hi[0], hi[1]);
     } else if (warp == 2 && is_last) {
         float lo[2], hi[2];
-        mbar_wait(&bars[2], 0, a.status);
         norm_rope_head(a.qkv + QSZ + g * D, cst + D, cst + 2 * D, cst + 3 * D, lane, lo, hi);
         const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
-        bf16* krow = kt + (size_t)(n - 1) * D;
+        bf16* krow = kt + (size_t)(n - 1) * KV_LD;
         *reinterpret_cast<uint32_t*>(krow + 2 * lane) = plo;
         *reinterpret_cast<uint32_t*>(krow + 64 + 2 * lane) = phi;
         bf16* gk = a.k_cache + head_off + (size_t)pos * D;
@@ -356,73 +368,93 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
         *reinterpret_cast<uint32_t*>(gk + 64 + 2 * lane) = phi;
     } else if (warp == 3 && is_last) {
         const uint2 u = ld_cg_u2(a.qkv + QSZ + KVSZ + g * D + 4 * lane);
-        *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * D + 4 * lane) = u;
+        *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * KV_LD + 4 * lane) = u;
         *reinterpret_cast<uint2*>(a.v_cache + head_off + (size_t)pos * D + 4 * lane) = u;
+    } else if (warp >= 4) {
+        const int n16 = (n + 15) & ~15;
+        for (int i = (warp - 4) * 32 + lane; i < (n16 - n) * 16; i += 128)
+            *reinterpret_cast<uint4*>(vt + (size_t)(n + (i >> 4)) * KV_LD + (i & 15) * 8) = make_uint4(0u, 0u, 0u, 0u);
     }
     __syncthreads();
     TL(a, 2);
-    if (n_cached > 0) mbar_wait(&bars[0], 0, a.status);
 
-    if (n_cached > 0) mbar_wait(&bars[1], 0, a.status);
-
-    // ---- every warp walks positions warp*4 + 32*i .. with its own online softmax
-    // (8 lanes per key for the scores, the whole warp per value row); the eight warps
-    // are merged through shared memory: two block barriers in the whole kernel.
+    // ---- a warp takes 16-position tiles warp, warp + 8, ..: scores = K_tile . q on the tensor
+    // cores (positions are the M dimension, the two heads two of the eight N columns), softmax
+    // of the tile, probabilities to bf16, out += P . V_tile (heads in M, dims in N).
     {
-        const int psub = lane >> 3, part = lane & 7;
-        float q0[16], q1[16];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            q0[e] = qh[part * 8 + e]; q0[8 + e] = qh[64 + part * 8 + e];
-            q1[e] = qh[D + part * 8 + e]; q1[8 + e] = qh[D + 64 + part * 8 + e];
-        }
+        const int gi = lane >> 2, ti = lane & 3;
         const float scale = 0.08838834764831845f;  // 1/sqrt(128)
         float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
-        float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int p4 = warp * 4; p4 < n; p4 += (ATT_THREADS / 32) * 4) {
-            const int p = p4 + psub;
-            float s0 = 0.f, s1 = 0.f;
-            if (p < n) {
-                const uint4 ua = *reinterpret_cast<const uint4*>(kt + (size_t)p * D + part * 8);
-                const uint4 ub = *reinterpret_cast<const uint4*>(kt + (size_t)p * D + 64 + part * 8);
-                const float kv[16] = {bf_lo(ua.x), bf_hi(ua.x), bf_lo(ua.y), bf_hi(ua.y), bf_lo(ua.z), bf_hi(ua.z), bf_lo(ua.w), bf_hi(ua.w),
-                                      bf_lo(ub.x), bf_hi(ub.x), bf_lo(ub.y), bf_hi(ub.y), bf_lo(ub.z), bf_hi(ub.z), bf_lo(ub.w), bf_hi(ub.w)};
+        float o[16][4];
 #pragma unroll
-                for (int e = 0; e < 16; ++e) { s0 = fmaf(kv[e], q0[e], s0); s1 = fmaf(kv[e], q1[e], s1); }
+        for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+        const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
+        bf16* pw = ps + warp * 32;
+        for (int tile = warp; tile * 16 < n; tile += ATT_THREADS / 32) {
+            const uint32_t rowoff = (uint32_t)(((tile * 16 + (lane & 15)) * KV_LD + (lane >> 4) * 8) * 2);
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t af[4];
+                ldsm4(af, smem_u32(kt) + rowoff + ks * 32);
+                uint32_t b0 = lds32(qaddr + ks * 32), b1 = lds32(qaddr + ks * 32 + 16);
+                if (gi >= 2) { b0 = 0u; b1 = 0u; }
+                mma16816(c, af, b0, b1);
             }
+            // lanes with ti == 0 hold head 0 / head 1 of positions gi (c[0], c[1]) and gi + 8 (c[2], c[3])
+            const int p_lo = tile * 16 + gi, p_hi = p_lo + 8;
+            const bool own = ti == 0;
+            const float s00 = (own && p_lo < n) ? c[0] * scale : -1e30f, s01 = (own && p_lo < n) ? c[1] * scale : -1e30f;
+            const float s10 = (own && p_hi < n) ? c[2] * scale : -1e30f, s11 = (own && p_hi < n) ? c[3] * scale : -1e30f;
+            float t0 = fmaxf(s00, s10), t1 = fmaxf(s01, s11);
 #pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            for (int off = 4; off < 32; off <<= 1) {
+                t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, off));
+                t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, off));
             }
-            s0 = (p < n) ? s0 * scale : -1e30f;
-            s1 = (p < n) ? s1 * scale : -1e30f;
-            float sj0[4], sj1[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { sj0[j] = __shfl_sync(0xffffffffu, s0, j * 8); sj1[j] = __shfl_sync(0xffffffffu, s1, j * 8); }
-            const float mn0 = fmaxf(m0, fmaxf(fmaxf(sj0[0], sj0[1]), fmaxf(sj0[2], sj0[3])));
-            const float mn1 = fmaxf(m1, fmaxf(fmaxf(sj1[0], sj1[1]), fmaxf(sj1[2], sj1[3])));
-            const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
+            t0 = __shfl_sync(0xffffffffu, t0, 0);
+            t1 = __shfl_sync(0xffffffffu, t1, 0);
+            const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+            const float cr0 = expf(m0 - mn0), cr1 = expf(m1 - mn1);
             m0 = mn0; m1 = mn1;
-            l0 *= c0; l1 *= c1;
+            const float e00 = (own && p_lo < n) ? expf(s00 - m0) : 0.f, e01 = (own && p_lo < n) ? expf(s01 - m1) : 0.f;
+            const float e10 = (own && p_hi < n) ? expf(s10 - m0) : 0.f, e11 = (own && p_hi < n) ? expf(s11 - m1) : 0.f;
+            float u0 = e00 + e10, u1 = e01 + e11;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (p4 + j < n) {
-                    const float e0 = expf(sj0[j] - m0), e1 = expf(sj1[j] - m1);
-                    l0 += e0; l1 += e1;
-                    const float pb0 = rbf(e0), pb1 = rbf(e1);
-                    const uint2 uv = *reinterpret_cast<const uint2*>(vt + (size_t)(p4 + j) * D + lane * 4);
-                    const float vv[4] = {bf_lo(uv.x), bf_hi(uv.x), bf_lo(uv.y), bf_hi(uv.y)};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) { acc0[e] = fmaf(pb0, vv[e], acc0[e]); acc1[e] = fmaf(pb1, vv[e], acc1[e]); }
-                }
+            for (int off = 4; off < 32; off <<= 1) {
+                u0 += __shfl_xor_sync(0xffffffffu, u0, off);
+                u1 += __shfl_xor_sync(0xffffffffu, u1, off);
             }
+            l0 = l0 * cr0 + __shfl_sync(0xffffffffu, u0, 0);
+            l1 = l1 * cr1 + __shfl_sync(0xffffffffu, u1, 0);
+            if (own) {
+                pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
+                pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+            }
+            __syncwarp();
+            // A = P: row gi is head gi (rows 2..15 are zero)
+            uint32_t pa[4] = {0u, 0u, 0u, 0u};
+            if (gi < 2) {
+                pa[0] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 2 * ti);
+                pa[2] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 8 + 2 * ti);
+            }
+            const float crg = gi == 0 ? cr0 : cr1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t bv[4];
+                ldsm4_t(bv, smem_u32(vt) + rowoff + j * 32);
+                o[2 * j][0] *= crg; o[2 * j][1] *= crg; o[2 * j + 1][0] *= crg; o[2 * j + 1][1] *= crg;
+                mma16816(o[2 * j], pa, bv[0], bv[1]);
+                mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
+            }
+            __syncwarp();
         }
         if (lane == 0) { wm[warp * 2] = m0; wm[warp * 2 + 1] = m1; wl[warp * 2] = l0; wl[warp * 2 + 1] = l1; }
+        if (gi < 2) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { wacc[(warp * 2) * D + lane * 4 + e] = acc0[e]; wacc[(warp * 2 + 1) * D + lane * 4 + e] = acc1[e]; }
+            for (int j = 0; j < 16; ++j)
+                *reinterpret_cast<float2*>(wacc + (warp * 2 + gi) * D + j * 8 + 2 * ti) = make_float2(o[j][0], o[j][1]);
+        }
     }
     __syncthreads();
     const int hh = tid >> 7, d = tid & 127;
@@ -445,8 +477,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     const int qhead = 2 * g + hh;
     if (n_act == 1) {
         a.attn[qhead * D + d] = __float2bfloat16_rn(acc / ml[hh * 2 + 1]);
-        __syncthreads();
-        if (tid == 0) attn_cta_done(a, n_working, tag);
+        TL_SYNC();
         TL(a, 3);
         return;
     }
@@ -462,24 +493,23 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     }
     __syncthreads();
     TL(a, 3);
-    if (!s_last) {
-        if (tid == 0) attn_cta_done(a, n_working, tag);
-        return;
-    }
+    if (!s_last) return;
     __threadfence();
-    // Merge of the n_act (<= 64) partials of this thread's head.  (m, l) of split
-    // lane and lane + 32 are fetched by one load each per lane, the accumulator
-    // column in batches of eight independent loads: the merge costs a few L2
-    // round trips instead of one per split.
+    // Merge of the n_act (<= 64) partials of this thread's head.  The first sixteen
+    // accumulator columns and the (m, l) pairs (split lane and lane + 32 per lane) are
+    // requested together, so a merge of up to sixteen splits costs one L2 round trip.
     const int lane_m = tid & 31;
+    const float* pbase = a.partials + (size_t)qhead * a.nsplit * PART_STRIDE;
+    float v[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) v[e] = (e < n_act) ? ld_cg_f32(pbase + (size_t)e * PART_STRIDE + 2 + d) : 0.f;
     float mj[2] = {-INFINITY, -INFINITY}, lj[2] = {0.f, 0.f};
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
         const int j = lane_m + 32 * h2;
         if (j < n_act) {
-            const float* pj = a.partials + ((size_t)qhead * a.nsplit + j) * PART_STRIDE;
-            mj[h2] = ld_cg_f32(pj);
-            lj[h2] = ld_cg_f32(pj + 1);
+            mj[h2] = ld_cg_f32(pbase + (size_t)j * PART_STRIDE);
+            lj[h2] = ld_cg_f32(pbase + (size_t)j * PART_STRIDE + 1);
         }
     }
     const float M = warp_max(fmaxf(mj[0], mj[1]));
@@ -488,24 +518,21 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     for (int h2 = 0; h2 < 2; ++h2) fj[h2] = (lane_m + 32 * h2 < n_act) ? expf(mj[h2] - M) : 0.f;
     const float den = warp_sum(lj[0] * fj[0] + lj[1] * fj[1]);
     float num = 0.f;
-    for (int j0 = 0; j0 < n_act; j0 += 8) {
-        float v[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e)
-            v[e] = (j0 + e < n_act) ? ld_cg_f32(a.partials + ((size_t)qhead * a.nsplit + j0 + e) * PART_STRIDE + 2 + d) : 0.f;
+    for (int e = 0; e < 16; ++e) num = fmaf(v[e], __shfl_sync(0xffffffffu, fj[0], e), num);
+    for (int j0 = 16; j0 < n_act; j0 += 16) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < 16; ++e) v[e] = (j0 + e < n_act) ? ld_cg_f32(pbase + (size_t)(j0 + e) * PART_STRIDE + 2 + d) : 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
             const int j = j0 + e;
             const float f0 = __shfl_sync(0xffffffffu, fj[0], j & 31), f1 = __shfl_sync(0xffffffffu, fj[1], j & 31);
             num = fmaf(v[e], (j < 32) ? f0 : f1, num);
         }
     }
     a.attn[qhead * D + d] = __float2bfloat16_rn(num / den);
-    __syncthreads();
-    if (tid == 0) {
-        a.counters[g] = 0u;
-        attn_cta_done(a, n_working, tag);
-    }
+    if (tid == 0) a.counters[g] = 0u;
+    TL_SYNC();
     TL(a, 3);
 }
 
@@ -817,7 +844,7 @@ static size_t smem_oproj(int G) { return QSZ * 2 + (GEMV_THREADS / 32) * 8 * 4 +
 static size_t smem_gateup(int G) { return 2 * H * 2 + (GEMV_THREADS / 32) * 48 * 4 + 8 * 4 + 16 + (size_t)2 * rows_per_cta(I, G) * H_LD * 2; }
 static size_t smem_down(int G) { return I * 2 + (DOWN_THREADS / 32) * 8 * 4 + 16 + (size_t)rows_per_cta(H, G) * DN_LD * 2; }
 static size_t smem_lmhead() { return (size_t)LM_STAGES * LM_ROWS * H * 2 + 2 * LM_STAGES * 8 + LM_CONSUMERS * 8 + 16 + H * 2; }
-static size_t smem_attn(int cap) { return (size_t)cap * D * 2 * 2 + (size_t)2 * cap * 4 + 2 * D * 4 + 4 * D * 4 + 4 * 4 + 32 * 4 + 16 * D * 4 + 4 * D * 2 + 3 * 8; }
+static size_t smem_attn(int cap) { return (size_t)cap * KV_LD * 2 * 2 + (2 * D + (ATT_THREADS / 32) * 32 + 4 * D) * 2 + (16 + 16 + 4) * 4 + 16 * D * 4; }
 
 // Shared-memory slots.  The block scheduler places a CTA wherever its resources fit, and on
 // an idle GPU it hands a 148-CTA grid out per GPC, which puts two CTAs on eight SMs and none
