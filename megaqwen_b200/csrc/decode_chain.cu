@@ -353,9 +353,6 @@ __device__ __forceinline__ uint32_t piece_off(const Pieces& P, int p) {
     for (int j = 1; j < CH_MAXP; ++j) o = (p == j) ? P.off[j] : o;
     return o;
 }
-__device__ __forceinline__ void l2_prefetch(const void* g, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(g), "r"(bytes) : "memory");
-}
 
 struct Geometry {
     int q0, qn;    // rows of [Wq;Wk;Wv]

@@ -38,6 +38,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
 
 // ---------------------------------------------------------------- reductions
+__device__ __forceinline__ unsigned int warp_sum_u32(unsigned int v) { return __reduce_add_sync(0xffffffffu, v); }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -146,6 +147,11 @@ __device__ __forceinline__ void load_x_slice(float (&x)[32], const bf16* src, in
         x[j * 8 + 4] = bf_lo(u.z); x[j * 8 + 5] = bf_hi(u.z);
         x[j * 8 + 6] = bf_lo(u.w); x[j * 8 + 7] = bf_hi(u.w);
     }
+}
+
+// Asks the L2 to fetch bytes (a multiple of 16) that a later kernel will copy to shared memory.
+__device__ __forceinline__ void l2_prefetch(const void* g, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(g), "r"(bytes) : "memory");
 }
 
 // ---------------------------------------------------------------- tensor-core GEMV
