@@ -82,6 +82,26 @@ constexpr int GM_BK = 64;
 constexpr int GM_THREADS = 192;    // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..5 epilogue
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 
+// Every kernel of the prefill and batched-decode chains is launched with programmatic
+// stream serialisation and begins with griddepcontrol.wait + launch_dependents: the next
+// kernel's CTAs are scheduled (parameters loaded, shared memory carved) while this one runs,
+// which takes the launch latency of the ~230 (prefill) / ~310 (batched step) kernels of a
+// pass off the critical path.  Without the launch attribute both instructions are no-ops.
+template <typename... KArgs, typename... Args>
+static void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);   // errors are sticky: callers read cudaGetLastError()
+}
+
 template <int BN, int EPI>
 struct GemmCfg {
     static constexpr int NB = (EPI == EPI_SWIGLU) ? 2 : 1;                       // B operands per stage
@@ -96,6 +116,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
        bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
     // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
     // and tmB2 (up) for the same tile.
@@ -232,6 +254,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm_skinny(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW2,
               int tiles0, int tiles1, const __grid_constant__ CUtensorMap tmX, float* __restrict__ part, int M, int ldp,
               int kb_per_cta, unsigned int* status) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     // Up to three weight matrices are concatenated along the output dimension (q|k|v,
     // gate|up): tile blockIdx.x belongs to matrix 0, 1 or 2; ldp is the row length of
     // one partial plane part[ks] = [M, ldp].
@@ -319,6 +343,8 @@ __device__ __forceinline__ float sum_splits(const float* part, int ksplit, size_
 
 // out[row, col0 + c] = bf16(sum)            (q / k / v projections into the qkv buffer)
 __global__ void __launch_bounds__(256) k_sk_store(const float* __restrict__ part, int ksplit, int M, int N, bf16* __restrict__ out, int ldo) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (size_t)M * N) return;
     const int row = (int)(i / N), col = (int)(i % N);
@@ -328,6 +354,8 @@ __global__ void __launch_bounds__(256) k_sk_store(const float* __restrict__ part
 // h = bf16(h + bf16(sum));  x = rmsnorm(h) * w      one CTA per row (N = 1024), 4 columns per thread
 __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ h,
                                                        const bf16* __restrict__ w, bf16* __restrict__ x) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     __shared__ float s_red[8];
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t base = (size_t)row * H + 4 * tid, plane = (size_t)M * H;
@@ -354,6 +382,8 @@ __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__
 
 // act[row, c] = bf16( bf16(silu(bf16(sum gate))) * bf16(sum up) )   gate/up partials are column blocks [0,I) and [I,2I)
 __global__ void __launch_bounds__(256) k_sk_swiglu(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ act) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (size_t)M * I) return;
     const int row = (int)(i / I), col = (int)(i % I);
@@ -366,6 +396,8 @@ __global__ void __launch_bounds__(256) k_sk_swiglu(const float* __restrict__ par
 // h[s,:] = embed[ids[s],:]      (reference: prefill_embed_kernel, fused_prefill_kernels.inl:3-20)
 __global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, const bf16* __restrict__ embed, bf16* __restrict__ h,
                                                   int vocab, unsigned int* status) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const int s = blockIdx.x;
     int tok = ids[s];
     if (tok < 0 || tok >= vocab) {
@@ -378,6 +410,8 @@ __global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, c
 // x[s,:] = bf16( w * bf16( h[s,:] * rsqrt(mean(h^2) + eps) ) )   one warp per row
 // (reference: prefill_rmsnorm_kernel, fused_prefill_kernels.inl:52-105)
 __global__ void __launch_bounds__(256) k_pf_rmsnorm(const bf16* __restrict__ h, const bf16* __restrict__ w, bf16* __restrict__ x, int rows) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -408,6 +442,8 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
                                                         const bf16* __restrict__ cos, const bf16* __restrict__ sin, bf16* __restrict__ k_cache,
                                                         bf16* __restrict__ v_cache, int layer, int pos0, int max_seq,
                                                         const int* __restrict__ pos_rows, size_t seq_stride) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     // pos_rows == nullptr: one sequence, row s sits at position pos0 + s.
     // pos_rows != nullptr: row s is sequence s at position pos_rows[s]; its cache starts s * seq_stride elements in.
     const int lane = threadIdx.x & 31;
@@ -483,6 +519,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
                                                             const bf16* __restrict__ v_cache, bf16* __restrict__ out, int S, int pos0,
                                                             int layer, int max_seq) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     extern __shared__ __align__(16) uint8_t fa_smem[];
     bf16* sq = reinterpret_cast<bf16*>(fa_smem);        // [64][FA_LD]
     bf16* sk = sq + FA_BQ * FA_LD;                      // [64][FA_LD]
@@ -696,7 +734,7 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
         if (rc != MQ_OK) return rc;
     }
     dim3 grid(N / BN, (M + GM_BM - 1) / GM_BM);
-    k_gemm<BN, EPI><<<grid, GM_THREADS, Cfg::SMEM, stream>>>(ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
+    launch_pdl(k_gemm<BN, EPI>, dim3(grid), dim3(GM_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
                                                              C, R, M, N, K, ldc, status);
     return (int)cudaGetLastError();
 }
@@ -729,7 +767,7 @@ static int launch_skinny_t(const bf16* const* W, const int* rowsW, int nW, const
     int rc = get_map(X, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, MPAD, &mx);
     if (rc != MQ_OK) return rc;
     dim3 grid(tiles[0] + tiles[1] + tiles[2], ksplit);
-    k_gemm_skinny<MPAD><<<grid, GM_THREADS, smem, stream>>>(mw[0], mw[1], mw[2], tiles[0], tiles[1], mx, part, M, ldp, kb / ksplit, status);
+    launch_pdl(k_gemm_skinny<MPAD>, dim3(grid), dim3(GM_THREADS), smem, stream, mw[0], mw[1], mw[2], tiles[0], tiles[1], mx, part, M, ldp, kb / ksplit, status);
     return (int)cudaGetLastError();
 }
 static int launch_skinny(const bf16* const* W, const int* rowsW, int nW, const bf16* X, int ldx, float* part, int M, int K, int ksplit,
@@ -744,6 +782,8 @@ static int launch_skinny(const bf16* const* W, const int* rowsW, int nW, const b
 int launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream);
 
 __global__ void k_pf_copy_row(const bf16* __restrict__ src, bf16* __restrict__ dst) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     reinterpret_cast<uint4*>(dst)[threadIdx.x] = reinterpret_cast<const uint4*>(src)[threadIdx.x];
 }
 
@@ -759,6 +799,8 @@ namespace mq {
 __global__ void __launch_bounds__(256) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
                                                       const bf16* __restrict__ v_cache, bf16* __restrict__ out,
                                                       const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     __shared__ float s_m[8][2], s_l[8][2], s_acc[8][2][D];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, g = blockIdx.y;
@@ -866,6 +908,8 @@ __global__ void __launch_bounds__(256) k_bd_attention(const bf16* __restrict__ q
 // out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
 __global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restrict__ logits, int vocab, int* __restrict__ out_tokens,
                                                             int* __restrict__ positions, float* __restrict__ logits_f32) {
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     __shared__ unsigned long long s_best[32];
     const int b = blockIdx.x, tid = threadIdx.x;
     const bf16* row = logits + (size_t)b * vocab;
@@ -927,25 +971,25 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         if (e != cudaSuccess) return (int)e;
         fa_attr[dev] = true;
     }
-    k_pf_embed<<<S, 128, 0, stream>>>(ids, (const bf16*)model->embed, h, model->vocab_size, status);
+    launch_pdl(k_pf_embed, dim3(S), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status);
     int rc;
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
-        k_pf_rmsnorm<<<(S + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.input_layernorm, x, S);
+        launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, S);
         // q | k | v in one launch: 32 column tiles from three weight matrices
         rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                          (const bf16*)w.v_proj, QSZ, KVSZ);
         if (rc) return rc;
-        k_pf_qknorm_rope<<<dim3(S, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+        launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0);
-        k_pf_attention<<<dim3((S + FA_BQ - 1) / FA_BQ, NQ), FA_THREADS, fa_smem, stream>>>(qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
+        launch_pdl(k_pf_attention, dim3(dim3((S + FA_BQ - 1) / FA_BQ, NQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
                                                                                           attn, S, pos0, l, model->max_seq_len);
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
         rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream)
                          : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
         if (rc) return rc;
-        k_pf_rmsnorm<<<(S + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.post_attn_layernorm, x, S);
+        launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, S);
         rc = launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
         if (rc) return rc;
         rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream)
@@ -953,7 +997,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         if (rc) return rc;
     }
     // last row -> decode hidden buffer, then the decode path's LM head + arg-max
-    k_pf_copy_row<<<1, H / 8, 0, stream>>>(h + (size_t)(S - 1) * H, (bf16*)dbuf->hidden);
+    launch_pdl(k_pf_copy_row, dim3(1), dim3(H / 8), 0, stream, h + (size_t)(S - 1) * H, (bf16*)dbuf->hidden);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     return launch_lmhead_only(model, dbuf, out_token, logits, stream);
@@ -974,69 +1018,69 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
     bf16* h = (bf16*)pb->h; bf16* x = (bf16*)pb->x; bf16* qkv = (bf16*)pb->qkv; bf16* attn = (bf16*)pb->attn; bf16* act = (bf16*)pb->act;
     unsigned int* status = bb->status;
     const size_t seq_stride = (size_t)model->num_layers * NKV * model->max_seq_len * D;
-    k_pf_embed<<<B, 128, 0, stream>>>(in_tokens, (const bf16*)model->embed, h, model->vocab_size, status);
+    launch_pdl(k_pf_embed, dim3(B), dim3(128), 0, stream, in_tokens, (const bf16*)model->embed, h, model->vocab_size, status);
     int rc;
     const size_t need_part = (size_t)4 * B * 2 * I * sizeof(float);   // largest partial: gate|up, 4 K-splits
     const bool skinny = B <= 64 && bb->partials != nullptr && bb->partials_bytes >= need_part;
     if (skinny) {
         float* part = bb->partials;
-        k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)model->layers[0].input_layernorm, x, B);
+        launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)model->layers[0].input_layernorm, x, B);
         for (int l = 0; l < model->num_layers; ++l) {
             const MqLayerWeights& w = model->layers[l];
             const bf16* wqkv[3] = {(const bf16*)w.q_proj, (const bf16*)w.k_proj, (const bf16*)w.v_proj};
             const int rqkv[3] = {QSZ, KVSZ, KVSZ};
             rc = launch_skinny(wqkv, rqkv, 3, x, H, part, B, H, 4, status, stream);
             if (rc) return rc;
-            k_sk_store<<<(B * QKV + 255) / 256, 256, 0, stream>>>(part, 4, B, QKV, qkv, QKV);
-            k_pf_qknorm_rope<<<dim3(B, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+            launch_pdl(k_sk_store, dim3((B * QKV + 255) / 256), dim3(256), 0, stream, part, 4, B, QKV, qkv, QKV);
+            launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                              (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                              model->max_seq_len, bb->positions, seq_stride);
-            k_bd_attention<<<dim3(B, NKV), 256, 0, stream>>>(qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
+            launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(256), 0, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                              model->max_seq_len, seq_stride);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
             const int ro[1] = {H};
             rc = launch_skinny(wo, ro, 1, attn, QSZ, part, B, QSZ, 8, status, stream);
             if (rc) return rc;
-            k_sk_resid_norm<<<B, 256, 0, stream>>>(part, 8, B, h, (const bf16*)w.post_attn_layernorm, x);
+            launch_pdl(k_sk_resid_norm, dim3(B), dim3(256), 0, stream, part, 8, B, h, (const bf16*)w.post_attn_layernorm, x);
             const bf16* wgu[2] = {(const bf16*)w.gate_proj, (const bf16*)w.up_proj};
             const int rgu[2] = {I, I};
             rc = launch_skinny(wgu, rgu, 2, x, H, part, B, H, 4, status, stream);
             if (rc) return rc;
-            k_sk_swiglu<<<(B * I + 255) / 256, 256, 0, stream>>>(part, 4, B, act);
+            launch_pdl(k_sk_swiglu, dim3((B * I + 255) / 256), dim3(256), 0, stream, part, 4, B, act);
             const bf16* wd[1] = {(const bf16*)w.down_proj};
             rc = launch_skinny(wd, ro, 1, act, I, part, B, I, 8, status, stream);
             if (rc) return rc;
             const bf16* next_norm = (l + 1 < model->num_layers) ? (const bf16*)model->layers[l + 1].input_layernorm : (const bf16*)model->final_norm;
-            k_sk_resid_norm<<<B, 256, 0, stream>>>(part, 8, B, h, next_norm, x);
+            launch_pdl(k_sk_resid_norm, dim3(B), dim3(256), 0, stream, part, 8, B, h, next_norm, x);
         }
     } else {
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
-        k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.input_layernorm, x, B);
+        launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, B);
         rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, nullptr, qkv, nullptr, B, QSZ, H, QKV, status, stream);
         if (rc) return rc;
         rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.k_proj, nullptr, qkv + QSZ, nullptr, B, KVSZ, H, QKV, status, stream);
         if (rc) return rc;
         rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.v_proj, nullptr, qkv + QSZ + KVSZ, nullptr, B, KVSZ, H, QKV, status, stream);
         if (rc) return rc;
-        k_pf_qknorm_rope<<<dim3(B, 4), 256, 0, stream>>>(qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+        launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                          model->max_seq_len, bb->positions, seq_stride);
-        k_bd_attention<<<dim3(B, NKV), 256, 0, stream>>>(qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
+        launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(256), 0, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                          model->max_seq_len, seq_stride);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
         if (rc) return rc;
-        k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)w.post_attn_layernorm, x, B);
+        launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, B);
         rc = launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, B, I, H, I, status, stream);
         if (rc) return rc;
         rc = launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, B, H, I, H, status, stream);
         if (rc) return rc;
     }
-    k_pf_rmsnorm<<<(B + 7) / 8, 256, 0, stream>>>(h, (const bf16*)model->final_norm, x, B);
+    launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)model->final_norm, x, B);
     }
     rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
                                      model->vocab_size, status, stream);
     if (rc) return rc;
-    k_bd_argmax_advance<<<B, 1024, 0, stream>>>((const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, logits_f32);
+    launch_pdl(k_bd_argmax_advance, dim3(B), dim3(1024), 0, stream, (const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, logits_f32);
     return (int)cudaGetLastError();
 }
