@@ -266,16 +266,6 @@ __device__ __forceinline__ void attn_cta_done(const DecodeArgs& a, unsigned int 
     }
 }
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t saddr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
-}
-
 constexpr int KV_LD = D + 8;   // K/V rows are padded by 16 bytes in shared memory (conflict-free ldmatrix)
 
 __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeights w, int layer) {

@@ -116,8 +116,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
        bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
     // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
     // and tmB2 (up) for the same tile.
@@ -254,8 +254,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1)
 k_gemm_skinny(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW2,
               int tiles0, int tiles1, const __grid_constant__ CUtensorMap tmX, float* __restrict__ part, int M, int ldp,
               int kb_per_cta, unsigned int* status) {
-    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
+    pdl_trigger();   // the next grid may be scheduled already
+    // The weight tiles do not depend on the preceding kernel: they are requested before
+    // griddepcontrol.wait and arrive while that kernel is still running; only the activation
+    // tiles (and everything downstream of them) come after the wait.
     // Up to three weight matrices are concatenated along the output dimension (q|k|v,
     // gate|up): tile blockIdx.x belongs to matrix 0, 1 or 2; ldp is the row length of
     // one partial plane part[ks] = [M, ldp].
@@ -290,8 +292,9 @@ k_gemm_skinny(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ 
             for (int i = 0; i < kb_per_cta; ++i) {
                 mbar_expect_tx(&full[i], (uint32_t)(W_BYTES + X_BYTES));
                 tma_load_2d(smem + i * W_BYTES, tmW, (kb0 + i) * GM_BK, wrow0, &full[i]);
-                tma_load_2d(xs + i * X_STRIDE, &tmX, (kb0 + i) * GM_BK, 0, &full[i]);
             }
+            pdl_wait();
+            for (int i = 0; i < kb_per_cta; ++i) tma_load_2d(xs + i * X_STRIDE, &tmX, (kb0 + i) * GM_BK, 0, &full[i]);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -343,8 +346,8 @@ __device__ __forceinline__ float sum_splits(const float* part, int ksplit, size_
 
 // out[row, col0 + c] = bf16(sum)            (q / k / v projections into the qkv buffer)
 __global__ void __launch_bounds__(256) k_sk_store(const float* __restrict__ part, int ksplit, int M, int N, bf16* __restrict__ out, int ldo) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (size_t)M * N) return;
     const int row = (int)(i / N), col = (int)(i % N);
@@ -354,8 +357,8 @@ __global__ void __launch_bounds__(256) k_sk_store(const float* __restrict__ part
 // h = bf16(h + bf16(sum));  x = rmsnorm(h) * w      one CTA per row (N = 1024), 4 columns per thread
 __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ h,
                                                        const bf16* __restrict__ w, bf16* __restrict__ x) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     __shared__ float s_red[8];
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t base = (size_t)row * H + 4 * tid, plane = (size_t)M * H;
@@ -382,8 +385,8 @@ __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__
 
 // act[row, c] = bf16( bf16(silu(bf16(sum gate))) * bf16(sum up) )   gate/up partials are column blocks [0,I) and [I,2I)
 __global__ void __launch_bounds__(256) k_sk_swiglu(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ act) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= (size_t)M * I) return;
     const int row = (int)(i / I), col = (int)(i % I);
@@ -396,8 +399,8 @@ __global__ void __launch_bounds__(256) k_sk_swiglu(const float* __restrict__ par
 // h[s,:] = embed[ids[s],:]      (reference: prefill_embed_kernel, fused_prefill_kernels.inl:3-20)
 __global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, const bf16* __restrict__ embed, bf16* __restrict__ h,
                                                   int vocab, unsigned int* status) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const int s = blockIdx.x;
     int tok = ids[s];
     if (tok < 0 || tok >= vocab) {
@@ -410,8 +413,8 @@ __global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, c
 // x[s,:] = bf16( w * bf16( h[s,:] * rsqrt(mean(h^2) + eps) ) )   one warp per row
 // (reference: prefill_rmsnorm_kernel, fused_prefill_kernels.inl:52-105)
 __global__ void __launch_bounds__(256) k_pf_rmsnorm(const bf16* __restrict__ h, const bf16* __restrict__ w, bf16* __restrict__ x, int rows) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -442,8 +445,8 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
                                                         const bf16* __restrict__ cos, const bf16* __restrict__ sin, bf16* __restrict__ k_cache,
                                                         bf16* __restrict__ v_cache, int layer, int pos0, int max_seq,
                                                         const int* __restrict__ pos_rows, size_t seq_stride) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     // pos_rows == nullptr: one sequence, row s sits at position pos0 + s.
     // pos_rows != nullptr: row s is sequence s at position pos_rows[s]; its cache starts s * seq_stride elements in.
     const int lane = threadIdx.x & 31;
@@ -519,8 +522,8 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
                                                             const bf16* __restrict__ v_cache, bf16* __restrict__ out, int S, int pos0,
                                                             int layer, int max_seq) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     extern __shared__ __align__(16) uint8_t fa_smem[];
     bf16* sq = reinterpret_cast<bf16*>(fa_smem);        // [64][FA_LD]
     bf16* sk = sq + FA_BQ * FA_LD;                      // [64][FA_LD]
@@ -782,8 +785,8 @@ static int launch_skinny(const bf16* const* W, const int* rowsW, int nW, const b
 int launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int* out_token, float* logits, cudaStream_t stream);
 
 __global__ void k_pf_copy_row(const bf16* __restrict__ src, bf16* __restrict__ dst) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     reinterpret_cast<uint4*>(dst)[threadIdx.x] = reinterpret_cast<const uint4*>(src)[threadIdx.x];
 }
 
@@ -792,115 +795,156 @@ __global__ void k_pf_copy_row(const bf16* __restrict__ src, bf16* __restrict__ d
 namespace mq {
 
 // ---------------------------------------------------------------- batched decode (one new token per sequence)
-// Attention of sequence b's new token over its own cache: one CTA per
-// (sequence, kv head); the two query heads of the kv head share the K/V stream.
-// Each warp walks positions warp*4 + 32*i .. with an online softmax of its own;
-// the eight warps are merged through shared memory.
-__global__ void __launch_bounds__(256) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
-                                                      const bf16* __restrict__ v_cache, bf16* __restrict__ out,
-                                                      const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
+// One CTA per (sequence, kv head); the two query heads share the K/V stream.  Each warp owns
+// the 16-position tiles warp, warp + 8, .. of the sequence and streams them through its own
+// three-stage ring of padded rows in shared memory (16-byte cp.async, two tiles in flight per
+// warp, no block barrier inside the loop).  Per tile: scores = K_tile . q on mma.sync (positions
+// are M, the two heads two of the eight N columns), softmax of the tile, P rounded to bf16,
+// out += P . V_tile (ldmatrix.trans on V).  About a sixth of the instructions of an fp32-FMA
+// loop over the same bytes, which is what bounded the FMA version at 2.7 TB/s.
+constexpr int BD_THREADS = 256, BD_STAGES = 3, BD_LD = D + 8;
+constexpr int BD_STAGE_ELEMS = 2 * 16 * BD_LD;                                  // K tile then V tile
+constexpr size_t BD_SMEM = (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS * 2 + 2 * D * 2 + (BD_THREADS / 32) * 32 * 2;
+
+__device__ __forceinline__ void bd_load_tile(bf16* stage, const bf16* kb, const bf16* vb, int tile, int len, int lane) {
+    // 16 rows x 16 chunks of 16 bytes for K and the same for V: 16 copies per lane.  Rows past
+    // the end of the sequence re-read the last row (their probabilities are zero).
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = i * 32 + lane, r = idx >> 4, c = idx & 15;
+        const int p = min(tile * 16 + r, len - 1);
+        cp_async16(stage + r * BD_LD + c * 8, kb + (size_t)p * D + c * 8);
+        cp_async16(stage + 16 * BD_LD + r * BD_LD + c * 8, vb + (size_t)p * D + c * 8);
+    }
+}
+
+__global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                                                               const bf16* __restrict__ v_cache, bf16* __restrict__ out,
+                                                               const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
-    __shared__ float s_m[8][2], s_l[8][2], s_acc[8][2][D];
+    extern __shared__ __align__(128) uint8_t bd_smem[];
+    bf16* ring = reinterpret_cast<bf16*>(bd_smem);                                    // [8 warps][3 stages][K 16 rows | V 16 rows][BD_LD]
+    bf16* qs = ring + (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS;         // [2][D]
+    bf16* ps = qs + 2 * D;                                                            // [8 warps][2][16]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, g = blockIdx.y;
     const int pos = min(max(positions[b], 0), max_seq - 1);
     const int len = pos + 1;
+    const int ntiles = (len + 15) >> 4;
     const bf16* kb = k_cache + (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
     const bf16* vb = v_cache + (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
-    const bf16* qrow = qkv + (size_t)b * QKV + 2 * g * D;
-    const int psub = lane >> 3, prt = lane & 7;
-    float q0[16], q1[16];
-    {
-        const uint4 a0 = *reinterpret_cast<const uint4*>(qrow + prt * 8), a1 = *reinterpret_cast<const uint4*>(qrow + 64 + prt * 8);
-        const uint4 b0 = *reinterpret_cast<const uint4*>(qrow + D + prt * 8), b1 = *reinterpret_cast<const uint4*>(qrow + D + 64 + prt * 8);
-        const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-        const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    bf16* wring = ring + (size_t)warp * BD_STAGES * BD_STAGE_ELEMS;
+
+    // first two tiles of this warp are requested before anything else
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { q0[2 * e] = bf_lo(wa[e]); q0[2 * e + 1] = bf_hi(wa[e]); q1[2 * e] = bf_lo(wb[e]); q1[2 * e + 1] = bf_hi(wb[e]); }
+    for (int s = 0; s < BD_STAGES - 1; ++s) {
+        const int t = warp + s * (BD_THREADS / 32);
+        if (t < ntiles) bd_load_tile(wring + s * BD_STAGE_ELEMS, kb, vb, t, len, lane);
+        cp_async_commit();
     }
-    const float scale = 0.08838834764831845f;
+    if (tid < 32) *reinterpret_cast<uint4*>(qs + tid * 8) = *reinterpret_cast<const uint4*>(qkv + (size_t)b * QKV + 2 * g * D + tid * 8);
+    __syncthreads();
+
+    const int gi = lane >> 2, ti = lane & 3;
+    const float scale = 0.08838834764831845f;  // 1/sqrt(128)
     float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
-    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int pbase = warp * 4; pbase < len; pbase += 64) {
-        // two passes of four positions each (pbase.. and pbase+32..); every K and V load of
-        // both passes is issued before any arithmetic so that ~4 KB per warp is in flight
-        uint4 ka[2], kc[2];
-        uint2 vq[2][4];
+    float o[16][4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int p = pbase + 32 * u + psub;
-            ka[u] = make_uint4(0, 0, 0, 0); kc[u] = make_uint4(0, 0, 0, 0);
-            if (p < len) {
-                ka[u] = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + prt * 8);
-                kc[u] = *reinterpret_cast<const uint4*>(kb + (size_t)p * D + 64 + prt * 8);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int pv = pbase + 32 * u + j;
-                vq[u][j] = make_uint2(0, 0);
-                if (pv < len) vq[u][j] = *reinterpret_cast<const uint2*>(vb + (size_t)pv * D + lane * 4);
-            }
+    for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+    const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
+    bf16* pw = ps + warp * 32;
+    int it = 0;
+    for (int tile = warp; tile < ntiles; tile += BD_THREADS / 32, ++it) {
+        cp_async_wait<BD_STAGES - 2>();   // this tile has landed (one younger group may be in flight)
+        __syncwarp();
+        const bf16* st = wring + (it % BD_STAGES) * BD_STAGE_ELEMS;
+        // the stage consumed in the previous iteration is free: request the tile two ahead
+        {
+            const int tn = tile + (BD_STAGES - 1) * (BD_THREADS / 32);
+            if (tn < ntiles) bd_load_tile(wring + ((it + BD_STAGES - 1) % BD_STAGES) * BD_STAGE_ELEMS, kb, vb, tn, len, lane);
+            cp_async_commit();
         }
+        const uint32_t rowoff = (uint32_t)(((lane & 15) * BD_LD + (lane >> 4) * 8) * 2);
+        const uint32_t kaddr = smem_u32(st) + rowoff, vaddr = kaddr + 16 * BD_LD * 2;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int p4 = pbase + 32 * u;
-            if (p4 >= len) break;
-            const int p = p4 + psub;
-            float s0 = 0.f, s1 = 0.f;
-            {
-                const uint32_t wk[8] = {ka[u].x, ka[u].y, ka[u].z, ka[u].w, kc[u].x, kc[u].y, kc[u].z, kc[u].w};
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float klo = bf_lo(wk[e]), khi = bf_hi(wk[e]);
-                    s0 = fmaf(klo, q0[2 * e], s0); s0 = fmaf(khi, q0[2 * e + 1], s0);
-                    s1 = fmaf(klo, q1[2 * e], s1); s1 = fmaf(khi, q1[2 * e + 1], s1);
-                }
-            }
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-                s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-                s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            s0 = (p < len) ? s0 * scale : -1e30f;
-            s1 = (p < len) ? s1 * scale : -1e30f;
-            float sj0[4], sj1[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { sj0[j] = __shfl_sync(0xffffffffu, s0, j * 8); sj1[j] = __shfl_sync(0xffffffffu, s1, j * 8); }
-            const float mn0 = fmaxf(m0, fmaxf(fmaxf(sj0[0], sj0[1]), fmaxf(sj0[2], sj0[3])));
-            const float mn1 = fmaxf(m1, fmaxf(fmaxf(sj1[0], sj1[1]), fmaxf(sj1[2], sj1[3])));
-            const float c0 = expf(m0 - mn0), c1 = expf(m1 - mn1);
-            m0 = mn0; m1 = mn1;
-            l0 *= c0; l1 *= c1;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { acc0[e] *= c0; acc1[e] *= c1; }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (p4 + j < len) {
-                    const float e0 = expf(sj0[j] - m0), e1 = expf(sj1[j] - m1);
-                    l0 += e0; l1 += e1;
-                    const float pb0 = rbf(e0), pb1 = rbf(e1);
-                    const float vv[4] = {bf_lo(vq[u][j].x), bf_hi(vq[u][j].x), bf_lo(vq[u][j].y), bf_hi(vq[u][j].y)};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) { acc0[e] = fmaf(pb0, vv[e], acc0[e]); acc1[e] = fmaf(pb1, vv[e], acc1[e]); }
-                }
-            }
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t af[4];
+            ldsm4(af, kaddr + ks * 32);
+            uint32_t b0 = lds32(qaddr + ks * 32), b1 = lds32(qaddr + ks * 32 + 16);
+            if (gi >= 2) { b0 = 0u; b1 = 0u; }
+            mma16816(c, af, b0, b1);
         }
+        // lanes with ti == 0 hold head 0 / head 1 of positions gi (c[0], c[1]) and gi + 8 (c[2], c[3])
+        const int p_lo = tile * 16 + gi, p_hi = p_lo + 8;
+        const bool own = ti == 0;
+        const float s00 = (own && p_lo < len) ? c[0] * scale : -1e30f, s01 = (own && p_lo < len) ? c[1] * scale : -1e30f;
+        const float s10 = (own && p_hi < len) ? c[2] * scale : -1e30f, s11 = (own && p_hi < len) ? c[3] * scale : -1e30f;
+        float t0 = fmaxf(s00, s10), t1 = fmaxf(s01, s11);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, off));
+            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, off));
+        }
+        t0 = __shfl_sync(0xffffffffu, t0, 0);
+        t1 = __shfl_sync(0xffffffffu, t1, 0);
+        const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+        const float cr0 = expf(m0 - mn0), cr1 = expf(m1 - mn1);
+        m0 = mn0; m1 = mn1;
+        const float e00 = (own && p_lo < len) ? expf(s00 - m0) : 0.f, e01 = (own && p_lo < len) ? expf(s01 - m1) : 0.f;
+        const float e10 = (own && p_hi < len) ? expf(s10 - m0) : 0.f, e11 = (own && p_hi < len) ? expf(s11 - m1) : 0.f;
+        float u0 = e00 + e10, u1 = e01 + e11;
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            u0 += __shfl_xor_sync(0xffffffffu, u0, off);
+            u1 += __shfl_xor_sync(0xffffffffu, u1, off);
+        }
+        l0 = l0 * cr0 + __shfl_sync(0xffffffffu, u0, 0);
+        l1 = l1 * cr1 + __shfl_sync(0xffffffffu, u1, 0);
+        if (own) {
+            pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
+            pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+        }
+        __syncwarp();
+        uint32_t pa[4] = {0u, 0u, 0u, 0u};   // A = P: row gi is head gi (rows 2..15 are zero)
+        if (gi < 2) {
+            pa[0] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 2 * ti);
+            pa[2] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 8 + 2 * ti);
+        }
+        const float crg = gi == 0 ? cr0 : cr1;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t bv[4];
+            ldsm4_t(bv, vaddr + j * 32);
+            o[2 * j][0] *= crg; o[2 * j][1] *= crg; o[2 * j + 1][0] *= crg; o[2 * j + 1][1] *= crg;
+            mma16816(o[2 * j], pa, bv[0], bv[1]);
+            mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
+        }
+        __syncwarp();
     }
-    if (lane == 0) { s_m[warp][0] = m0; s_m[warp][1] = m1; s_l[warp][0] = l0; s_l[warp][1] = l1; }
+    cp_async_wait_all();
+    __syncthreads();   // every warp is done with its ring: the merge buffers reuse it
+    float* s_acc = reinterpret_cast<float*>(bd_smem);          // [8][2][D]
+    float* s_m = s_acc + (BD_THREADS / 32) * 2 * D;            // [8][2]
+    float* s_l = s_m + (BD_THREADS / 32) * 2;                  // [8][2]
+    if (lane == 0) { s_m[warp * 2] = m0; s_m[warp * 2 + 1] = m1; s_l[warp * 2] = l0; s_l[warp * 2 + 1] = l1; }
+    if (gi < 2) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) { s_acc[warp][0][lane * 4 + e] = acc0[e]; s_acc[warp][1][lane * 4 + e] = acc1[e]; }
+        for (int j = 0; j < 16; ++j)
+            *reinterpret_cast<float2*>(s_acc + (warp * 2 + gi) * D + j * 8 + 2 * ti) = make_float2(o[j][0], o[j][1]);
+    }
     __syncthreads();
     const int hh = tid >> 7, d = tid & 127;
     float M = -1e30f;
 #pragma unroll
-    for (int w8 = 0; w8 < 8; ++w8) M = fmaxf(M, s_m[w8][hh]);
+    for (int w8 = 0; w8 < BD_THREADS / 32; ++w8) M = fmaxf(M, s_m[w8 * 2 + hh]);
     float num = 0.f, den = 0.f;
 #pragma unroll
-    for (int w8 = 0; w8 < 8; ++w8) {
-        const float f = expf(s_m[w8][hh] - M);
-        den = fmaf(s_l[w8][hh], f, den);
-        num = fmaf(s_acc[w8][hh][d], f, num);
+    for (int w8 = 0; w8 < BD_THREADS / 32; ++w8) {
+        const float f = expf(s_m[w8 * 2 + hh] - M);
+        den = fmaf(s_l[w8 * 2 + hh], f, den);
+        num = fmaf(s_acc[(w8 * 2 + hh) * D + d], f, num);
     }
     out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den);
 }
@@ -908,8 +952,8 @@ __global__ void __launch_bounds__(256) k_bd_attention(const bf16* __restrict__ q
 // out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
 __global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restrict__ logits, int vocab, int* __restrict__ out_tokens,
                                                             int* __restrict__ positions, float* __restrict__ logits_f32) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    pdl_trigger();   // the next grid may be scheduled now (it waits the same way)
     __shared__ unsigned long long s_best[32];
     const int b = blockIdx.x, tid = threadIdx.x;
     const bf16* row = logits + (size_t)b * vocab;
@@ -1018,6 +1062,16 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
     bf16* h = (bf16*)pb->h; bf16* x = (bf16*)pb->x; bf16* qkv = (bf16*)pb->qkv; bf16* attn = (bf16*)pb->attn; bf16* act = (bf16*)pb->act;
     unsigned int* status = bb->status;
     const size_t seq_stride = (size_t)model->num_layers * NKV * model->max_seq_len * D;
+    {
+        static bool bd_attr[64] = {false};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !bd_attr[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(k_bd_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BD_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            bd_attr[dev] = true;
+        }
+    }
     launch_pdl(k_pf_embed, dim3(B), dim3(128), 0, stream, in_tokens, (const bf16*)model->embed, h, model->vocab_size, status);
     int rc;
     const size_t need_part = (size_t)4 * B * 2 * I * sizeof(float);   // largest partial: gate|up, 4 K-splits
@@ -1035,7 +1089,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
             launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                              (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                              model->max_seq_len, bb->positions, seq_stride);
-            launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(256), 0, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
+            launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                              model->max_seq_len, seq_stride);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
             const int ro[1] = {H};
@@ -1066,7 +1120,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                          model->max_seq_len, bb->positions, seq_stride);
-        launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(256), 0, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
+        launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                          model->max_seq_len, seq_stride);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
         if (rc) return rc;
