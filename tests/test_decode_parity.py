@@ -229,3 +229,33 @@ def test_full_determinism(full):
         tok, lg = dec.decode_step_logits(p[-1])
         outs.append((tok, lg.clone(), dec.decode_steps(tok, 32).tolist()))
     assert outs[0][0] == outs[1][0] and torch.equal(outs[0][1], outs[1][1]) and outs[0][2] == outs[1][2]
+
+
+@pytest.mark.gpu
+def test_very_long_context_many_splits():
+    """max_seq_len 16384: the attention grid has more CTAs than the GPU has SMs (8 x 64
+    splits), a CTA's chunk spans several 16-position tiles per warp, and the merge reads
+    more than 32 partials per head.  Checked against the restatement at context 5000."""
+    from oracle.qwen3_restatement import RestatedQwen3
+    max_seq = 16384
+    w = random_weights(QWEN3_TINY, max_seq)
+    dec, _ = make_decoder(QWEN3_TINY, max_seq, w)
+    prompt = random_prompt(QWEN3_TINY, 5000, 11, 0)
+    ref = RestatedQwen3(QWEN3_TINY, w, max_seq)
+    ref.forward(prompt[:-1])
+    dec.prefill_step(prompt[:-1])
+    cur = int(prompt[-1])
+    for step in range(4):
+        tok, lg = dec.decode_step_logits(cur)
+        ref_lg = ref.forward([cur])
+        r = logit_report(lg.cpu(), ref_lg)
+        assert r["max"] <= 6e-2 and r["mean"] <= 8e-3, (step, r)
+        cur = int(ref_lg.argmax())
+    assert dec.position() == 5003
+    # graph replay of the same kernels at this size
+    dec.position_ = 4999
+    a = dec.decode_steps_cuda(int(prompt[-1]), 8).tolist()
+    dec.position_ = 4999
+    b = dec.decode_steps_cuda_graph(int(prompt[-1]), 8).tolist()
+    assert a == b
+    dec.check_status()
