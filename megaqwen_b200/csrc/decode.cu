@@ -475,16 +475,17 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     float* part = a.partials + ((size_t)qhead * a.nsplit + s) * PART_STRIDE;
     part[2 + d] = acc;
     if (d == 0) { part[0] = ml[hh * 2]; part[1] = ml[hh * 2 + 1]; }
-    __threadfence();
+    // the block barrier orders every thread's partial before thread 0's release; the CTA that
+    // takes the last ticket acquires the others' partials with the same instruction
     __syncthreads();
     if (tid == 0) {
-        const unsigned int t = atomicAdd(&a.counters[g], 1u);
+        unsigned int t;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(a.counters + g) : "memory");
         s_last = (t == (unsigned int)(n_act - 1));
     }
     __syncthreads();
     TL(a, 3);
     if (!s_last) return;
-    __threadfence();
     // Merge of the n_act (<= 64) partials of this thread's head.  The first sixteen
     // accumulator columns and the (m, l) pairs (split lane and lane + 32 per lane) are
     // requested together, so a merge of up to sixteen splits costs one L2 round trip.

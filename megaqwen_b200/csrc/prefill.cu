@@ -102,17 +102,21 @@ static void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);   // errors are sticky: callers read cudaGetLastError()
 }
 
+#ifndef MQ_GEMM_BUDGET_KB
+#define MQ_GEMM_BUDGET_KB 200   // shared memory for the operand ring of one CTA
+#define MQ_GEMM_MIN_CTAS 1
+#endif
 template <int BN, int EPI>
 struct GemmCfg {
     static constexpr int NB = (EPI == EPI_SWIGLU) ? 2 : 1;                       // B operands per stage
     static constexpr int STAGE_BYTES = GM_BM * GM_BK * 2 + NB * BN * GM_BK * 2;
-    static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 6 ? 6 : (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES > 6 ? 6 : (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES;
     static constexpr int TMEM_COLS = NB * BN;                                    // power of two >= 32
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(GM_THREADS, 1)
+__global__ void __launch_bounds__(GM_THREADS, MQ_GEMM_MIN_CTAS)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
        bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
