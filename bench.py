@@ -83,12 +83,19 @@ class ClockSampler(threading.Thread):
 from megaqwen_b200.replicas import aggregate_throughput, barrier, dist_env, init_control_plane, max_over_ranks  # noqa: E402
 
 
+def host_threads() -> int:
+    """Host cores this process may run on."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_reference(sample_new: int, threads: int | None = None):
     """The reference's HF bf16 path on the host cores: decode tokens/s at context
     2048 on a bounded sample (2048-token prompt, `sample_new` new tokens)."""
     from oracle.hf_reference import build_hf_model, time_hf_decode
-    if threads:
-        torch.set_num_threads(threads)
+    torch.set_num_threads(threads or host_threads())
     w = random_weights(QWEN3_0_6B, MAX_SEQ)
     model = build_hf_model(QWEN3_0_6B, w)
     prompt = random_prompt(QWEN3_0_6B, PROMPT_LEN, 2, 0)
@@ -103,6 +110,7 @@ def run_reference(args):
     sample_new = 24
     vals, pre = [], []
     from oracle.hf_reference import build_hf_model, time_hf_decode
+    torch.set_num_threads(host_threads())   # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core it may
     w = random_weights(QWEN3_0_6B, MAX_SEQ)
     model = build_hf_model(QWEN3_0_6B, w)
     prompt = random_prompt(QWEN3_0_6B, PROMPT_LEN, 2, 0)
@@ -199,6 +207,27 @@ def measure_other_configs(dev, w):
 
     batched("config4_batch32_ragged", random_lengths(32, 256, 512), 128, 1024, 4)
     batched("config5_batch64_ctx1024", [1024] * 64, 256, 1280, 5)
+    return out
+
+
+def decode_by_context(dec, dev, peak):
+    """Batch-1 decode latency at fixed cache lengths (32 graph-replayed steps starting at
+    each length, over the cache the headline run left behind): microseconds per token and
+    the fraction of the HBM roofline for the bytes of those steps."""
+    out = {}
+    for L in (1, 16, 128, 512, 1024, 2048):
+        best = 1e9
+        for _ in range(3):
+            dec.position_ = L - 1          # the step writes position L-1 and attends over L entries
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); dec._chain(17, 32, True); e1.record()
+            torch.cuda.synchronize(dev)
+            best = min(best, e0.elapsed_time(e1) / 32 * 1e3)
+        nbytes = sum(QWEN3_0_6B.decode_bytes(L + i) for i in range(32)) / 32
+        gbs = nbytes / (best * 1e-6) / 1e9
+        out[str(L)] = {"us_per_token": best, "tokens_per_s": 1e6 / best, "achieved_GBps": gbs, "frac": gbs / peak}
+    dec.check_status()
     return out
 
 
@@ -299,6 +328,10 @@ def run_ours(args):
         "wall_s": wall,
     }
     if args.other_configs and world == 1:
+        try:
+            line["decode_by_context"] = decode_by_context(dec, dev, peak)
+        except Exception as exc:
+            line["decode_by_context"] = {"error": repr(exc)[:200]}
         try:
             del dec
             torch.cuda.empty_cache()
