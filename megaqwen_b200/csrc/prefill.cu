@@ -496,19 +496,33 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
 }
 
 // ---------------------------------------------------------------- causal GQA attention (prefill)
-// One CTA per (64-query tile, query head); 4 warps x 16 query rows; K/V tiles of 64
-// cached positions.  QK^T and PV run on mma.sync m16n8k16 (bf16 in, fp32 accumulate)
-// with an online softmax in registers; probabilities are rounded to bf16 before
-// the PV product and the row sum uses the unrounded fp32 values.
-// (Reference: prefill_causal_attention_kernel, fused_prefill_kernels.inl:265-342,
-// one warp per (query, head) walking the keys serially.)
-constexpr int FA_BQ = 64, FA_BK = 64, FA_LD = D + 8, FA_THREADS = 128;
+// QK^T and PV run on mma.sync m16n8k16 (bf16 in, fp32 accumulate) with an online softmax in
+// registers; probabilities are rounded to bf16 before the PV product and the row sum uses the
+// unrounded values.
+// Causal attention of the prompt.  One CTA per (query head, 64-query tile).  Under the causal
+// mask the last query tile of a prompt has sixteen times the work of the first, and the pass
+// is as long as its longest CTA, so the key tiles of a query tile are dealt out to FA_NG
+// groups of four warps that walk them in parallel (group g takes key tiles g, g + FA_NG, ..)
+// and are merged through shared memory at the end; the grid is ordered longest query tile
+// first.  Each group streams its K/V tiles through its own two-stage ring of padded rows
+// (16-byte cp.async, the next tile in flight while this one is multiplied).
+constexpr int FA_BQ = 64, FA_BK = 64, FA_LD = D + 8, FA_NG = 2, FA_THREADS = FA_NG * 128;
+constexpr int FA_TILE_ELEMS = FA_BK * FA_LD;                                  // one K or V tile
+constexpr size_t FA_SMEM = (size_t)(FA_BQ * FA_LD + FA_NG * 2 * 2 * FA_TILE_ELEMS) * 2;
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void group_barrier(int group) {
+    asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory");
+}
+
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
@@ -523,19 +537,38 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
-                                                            const bf16* __restrict__ v_cache, bf16* __restrict__ out, int S, int pos0,
-                                                            int layer, int max_seq) {
+__global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                                                               const bf16* __restrict__ v_cache, bf16* __restrict__ out, int S, int pos0,
+                                                               int layer, int max_seq) {
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     extern __shared__ __align__(16) uint8_t fa_smem[];
-    bf16* sq = reinterpret_cast<bf16*>(fa_smem);        // [64][FA_LD]
-    bf16* sk = sq + FA_BQ * FA_LD;                      // [64][FA_LD]
-    bf16* sv = sk + FA_BK * FA_LD;                      // [64][FA_LD]
+    bf16* sq = reinterpret_cast<bf16*>(fa_smem);                    // [64][FA_LD]
+    bf16* ring = sq + FA_BQ * FA_LD;                                // [FA_NG][2 stages][K tile | V tile]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int q0 = blockIdx.x * FA_BQ, head = blockIdx.y, g = head / (NQ / NKV);
+    const int grp = warp >> 2, wq = warp & 3, gtid = tid & 127;
+    const int head = blockIdx.x, g = head / (NQ / NKV);
+    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * FA_BQ;  // longest query tiles are dispatched first
     const bf16* kbase = k_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
     const bf16* vbase = v_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
+    bf16* gring = ring + (size_t)grp * 4 * FA_TILE_ELEMS;
+
+    const int kv_end = min(pos0 + S, pos0 + q0 + FA_BQ);     // exclusive bound of keys any row of the tile may see
+    const int ntiles = (kv_end + FA_BK - 1) / FA_BK;
+    auto load_tile = [&](int t, int stage) {
+        bf16* sk = gring + (size_t)stage * 2 * FA_TILE_ELEMS;
+        bf16* sv = sk + FA_TILE_ELEMS;
+        const int p0 = t * FA_BK;
+        for (int c = gtid; c < FA_BK * (D / 8); c += 128) {
+            const int r = c / (D / 8), cc = c % (D / 8);
+            const bool ok = p0 + r < kv_end;
+            const size_t off = (size_t)(ok ? p0 + r : 0) * D + cc * 8;
+            cp_async16_zfill(sk + r * FA_LD + cc * 8, kbase + off, ok);
+            cp_async16_zfill(sv + r * FA_LD + cc * 8, vbase + off, ok);
+        }
+    };
+    if (grp < ntiles) load_tile(grp, 0);
+    cp_async_commit();
 
     // Q tile -> shared (rows past S are zero)
     for (int c = tid; c < FA_BQ * (D / 8); c += FA_THREADS) {
@@ -548,7 +581,7 @@ __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restr
     uint32_t qf[8][4];
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk)
-        ldsm_x4(qf[kk], sq + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * FA_LD + kk * 16 + (lane >> 4) * 8);
+        ldsm_x4(qf[kk], sq + (wq * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * FA_LD + kk * 16 + (lane >> 4) * 8);
 
     float o[16][4];
 #pragma unroll
@@ -557,24 +590,18 @@ __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restr
     // scores are kept in the log2 domain (scale * log2(e) folded in) so that the softmax uses
     // the single-instruction exp2 instead of expf; the probabilities are the same numbers
     const float scale = 0.08838834764831845f * 1.4426950408889634f;
-    const int row_a = pos0 + q0 + warp * 16 + (lane >> 2);   // absolute position of this thread's first row; second is +8
-    const int kv_end = min(pos0 + S, pos0 + q0 + FA_BQ);     // exclusive bound of keys any row of the tile may see
-    const int ntiles = (kv_end + FA_BK - 1) / FA_BK;
+    const int row_a = pos0 + q0 + wq * 16 + (lane >> 2);   // absolute position of this thread's first row; second is +8
 
-    for (int t = 0; t < ntiles; ++t) {
+    int it = 0;
+    for (int t = grp; t < ntiles; t += FA_NG, ++it) {
+        // the other stage was consumed in the previous iteration (barrier at its end): request the next tile
+        if (t + FA_NG < ntiles) load_tile(t + FA_NG, (it + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();          // this thread's copies of tile t have landed
+        group_barrier(grp);          // .. and everybody's in the group
+        const bf16* sk = gring + (size_t)(it & 1) * 2 * FA_TILE_ELEMS;
+        const bf16* sv = sk + FA_TILE_ELEMS;
         const int p0 = t * FA_BK;
-        __syncthreads();   // previous tile fully consumed
-        for (int c = tid; c < FA_BK * (D / 8); c += FA_THREADS) {
-            const int r = c / (D / 8), cc = c % (D / 8);
-            uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
-            if (p0 + r < kv_end) {
-                kv4 = *reinterpret_cast<const uint4*>(kbase + (size_t)(p0 + r) * D + cc * 8);
-                vv4 = *reinterpret_cast<const uint4*>(vbase + (size_t)(p0 + r) * D + cc * 8);
-            }
-            *reinterpret_cast<uint4*>(sk + r * FA_LD + cc * 8) = kv4;
-            *reinterpret_cast<uint4*>(sv + r * FA_LD + cc * 8) = vv4;
-        }
-        __syncthreads();
 
         float sacc[8][4];
 #pragma unroll
@@ -643,9 +670,43 @@ __global__ void __launch_bounds__(FA_THREADS) k_pf_attention(const bf16* __restr
                 mma_bf16_16816(o[2 * dp + 1], pf[j], vf[2], vf[3]);
             }
         }
+        group_barrier(grp);          // the stage may be overwritten by the next iteration's request
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // merge the groups: groups 1.. leave (m, l, O) of every thread in the ring, group 0 combines
+    float* xch = reinterpret_cast<float*>(ring);        // [FA_NG - 1][128 threads][68]
+    if (grp > 0) {
+        float* mine = xch + ((size_t)(grp - 1) * 128 + gtid) * 68;
+        mine[0] = m_run[0]; mine[1] = m_run[1]; mine[2] = l_run[0]; mine[3] = l_run[1];
+#pragma unroll
+        for (int dt = 0; dt < 16; ++dt) *reinterpret_cast<float4*>(mine + 4 + dt * 4) = make_float4(o[dt][0], o[dt][1], o[dt][2], o[dt][3]);
+    }
+    __syncthreads();
+    if (grp > 0) return;
+#pragma unroll
+    for (int og = 1; og < FA_NG; ++og) {
+        const float* oth = xch + ((size_t)(og - 1) * 128 + gtid) * 68;
+        float f_me[2], f_ot[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const float mo = oth[h2], mn = fmaxf(m_run[h2], mo);
+            f_me[h2] = fast_exp2(m_run[h2] - mn);
+            f_ot[h2] = fast_exp2(mo - mn);
+            l_run[h2] = l_run[h2] * f_me[h2] + oth[2 + h2] * f_ot[h2];
+            m_run[h2] = mn;
+        }
+#pragma unroll
+        for (int dt = 0; dt < 16; ++dt) {
+            const float4 ov = *reinterpret_cast<const float4*>(oth + 4 + dt * 4);
+            o[dt][0] = o[dt][0] * f_me[0] + ov.x * f_ot[0];
+            o[dt][1] = o[dt][1] * f_me[0] + ov.y * f_ot[0];
+            o[dt][2] = o[dt][2] * f_me[1] + ov.z * f_ot[1];
+            o[dt][3] = o[dt][3] * f_me[1] + ov.w * f_ot[1];
+        }
     }
     // normalise and store
-    const int r_lo = q0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const int r_lo = q0 + wq * 16 + (lane >> 2), r_hi = r_lo + 8;
     const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
 #pragma unroll
     for (int dt = 0; dt < 16; ++dt) {
@@ -1021,7 +1082,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     static bool fa_attr[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    const size_t fa_smem = (size_t)(FA_BQ + 2 * FA_BK) * FA_LD * 2;
+    const size_t fa_smem = FA_SMEM;
     if (dev >= 0 && dev < 64 && !fa_attr[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_pf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fa_smem);
         if (e != cudaSuccess) return (int)e;
@@ -1039,7 +1100,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0);
-        launch_pdl(k_pf_attention, dim3(dim3((S + FA_BQ - 1) / FA_BQ, NQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
+        launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
                                                                                           attn, S, pos0, l, model->max_seq_len);
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
         rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream)
