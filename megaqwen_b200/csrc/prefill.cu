@@ -453,46 +453,49 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     // pos_rows == nullptr: one sequence, row s sits at position pos0 + s.
     // pos_rows != nullptr: row s is sequence s at position pos_rows[s]; its cache starts s * seq_stride elements in.
+    // A warp handles units (q heads 0..15, k heads 16..23, v heads 24..31) blockIdx.y * 8 + warp,
+    // then every gridDim.y * 8 further: one CTA per row with gridDim.y = 1, four with 4.
     const int lane = threadIdx.x & 31;
-    const int unit = blockIdx.y * 8 + (threadIdx.x >> 5);   // 0..31
     const int s = blockIdx.x;
     const int pos = pos_rows ? min(max(pos_rows[s], 0), max_seq - 1) : pos0 + s;
     if (pos_rows) { k_cache += (size_t)s * seq_stride; v_cache += (size_t)s * seq_stride; }
     bf16* row = qkv + (size_t)s * QKV;
-    if (unit >= NQ + NKV) {   // V head: raw copy into the cache
-        const int g = unit - NQ - NKV;
-        const uint2 u = *reinterpret_cast<const uint2*>(row + QSZ + KVSZ + g * D + 4 * lane);
-        *reinterpret_cast<uint2*>(v_cache + ((size_t)(layer * NKV + g) * max_seq + pos) * D + 4 * lane) = u;
-        return;
-    }
-    const bool is_q = unit < NQ;
-    bf16* head = is_q ? row + unit * D : row + QSZ + (unit - NQ) * D;
-    const bf16* wn = is_q ? wq : wk;
     const bf16* cosr = cos + (size_t)pos * D;
     const bf16* sinr = sin + (size_t)pos * D;
-    const uint32_t ulo = *reinterpret_cast<const uint32_t*>(head + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
-    const float xl[2] = {bf_lo(ulo), bf_hi(ulo)}, xh[2] = {bf_lo(uhi), bf_hi(uhi)};
-    float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
-    ss = warp_sum(ss);
-    const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
-    const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
     const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
     const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
-    const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
     const float clo[2] = {bf_lo(cl), bf_hi(cl)}, chi[2] = {bf_lo(chh), bf_hi(chh)};
     const float slo[2] = {bf_lo(sl), bf_hi(sl)}, shi[2] = {bf_lo(sh), bf_hi(sh)};
-    float lo[2], hi[2];
+    for (int unit = blockIdx.y * 8 + (threadIdx.x >> 5); unit < NQ + 2 * NKV; unit += gridDim.y * 8) {
+        if (unit >= NQ + NKV) {   // V head: raw copy into the cache
+            const int g = unit - NQ - NKV;
+            const uint2 u = *reinterpret_cast<const uint2*>(row + QSZ + KVSZ + g * D + 4 * lane);
+            *reinterpret_cast<uint2*>(v_cache + ((size_t)(layer * NKV + g) * max_seq + pos) * D + 4 * lane) = u;
+            continue;
+        }
+        const bool is_q = unit < NQ;
+        bf16* head = is_q ? row + unit * D : row + QSZ + (unit - NQ) * D;
+        const bf16* wn = is_q ? wq : wk;
+        const uint32_t ulo = *reinterpret_cast<const uint32_t*>(head + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
+        const float xl[2] = {bf_lo(ulo), bf_hi(ulo)}, xh[2] = {bf_lo(uhi), bf_hi(uhi)};
+        float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+        const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
+        const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
+        float lo[2], hi[2];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-        const float nl = rbf(wlo[e] * rbf(xl[e] * r));
-        const float nh = rbf(whi[e] * rbf(xh[e] * r));
-        lo[e] = rbf(rbf(nl * clo[e]) + rbf(-nh * slo[e]));
-        hi[e] = rbf(rbf(nh * chi[e]) + rbf(nl * shi[e]));
+        for (int e = 0; e < 2; ++e) {
+            const float nl = rbf(wlo[e] * rbf(xl[e] * r));
+            const float nh = rbf(whi[e] * rbf(xh[e] * r));
+            lo[e] = rbf(rbf(nl * clo[e]) + rbf(-nh * slo[e]));
+            hi[e] = rbf(rbf(nh * chi[e]) + rbf(nl * shi[e]));
+        }
+        const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
+        bf16* dst = is_q ? head : k_cache + ((size_t)(layer * NKV + (unit - NQ)) * max_seq + pos) * D;
+        *reinterpret_cast<uint32_t*>(dst + 2 * lane) = plo;
+        *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = phi;
     }
-    const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
-    bf16* dst = is_q ? head : k_cache + ((size_t)(layer * NKV + (unit - NQ)) * max_seq + pos) * D;
-    *reinterpret_cast<uint32_t*>(dst + 2 * lane) = plo;
-    *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = phi;
 }
 
 // ---------------------------------------------------------------- causal GQA attention (prefill)
@@ -1097,7 +1100,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                          (const bf16*)w.v_proj, QSZ, KVSZ);
         if (rc) return rc;
-        launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+        launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0);
         launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
