@@ -114,6 +114,9 @@ class MegakernelDecoder:
                                     _ptr(self._slot), _ptr(self._scalars) + 4, nsplit)
         self.position_ = 0
         self.use_pdl = True
+        self.use_step_graph = True  # decode_step replays a captured one-step graph instead of 141 eager launches
+        self._step_graph = None
+        self._step_graph_pdl = None
         self.launches = 0          # kernels launched through the C ABI by this object
 
     # ------------------------------------------------------------------ helpers
@@ -176,11 +179,31 @@ class MegakernelDecoder:
             # scalar fills carry the value as a kernel argument: no host buffer to race on
             self._in_token.fill_(int(input_token_id))
             self._pos_dev.fill_(self.position_)
-            self._launch(_ptr(self._in_token), _ptr(self._scalars), _ptr(self._pos_dev), logits_ptr, False)
+            if logits_ptr is None and self.use_step_graph:
+                self._replay_step_graph()
+            else:
+                self._launch(_ptr(self._in_token), _ptr(self._scalars), _ptr(self._pos_dev), logits_ptr, False)
             self.position_ += 1
             tok, status = self._scalars[:2].tolist()
         self._check_status(status)
         return tok
+
+    def _replay_step_graph(self) -> None:
+        """One decode step (token and position in device scalars) captured once and replayed:
+        the host cost of a step is one graph launch instead of 141 kernel launches."""
+        if self._step_graph is None or self._step_graph_pdl != self.use_pdl:
+            g = torch.cuda.CUDAGraph()
+            launches0 = self.launches
+            s = torch.cuda.Stream(device=self.device)
+            s.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(s):
+                with torch.cuda.graph(g, stream=s):
+                    self._launch(_ptr(self._in_token), _ptr(self._scalars), _ptr(self._pos_dev), None, False)
+            torch.cuda.current_stream(self.device).wait_stream(s)
+            self.launches = launches0
+            self._step_graph, self._step_graph_pdl = g, self.use_pdl
+        self._step_graph.replay()
+        self.launches += 5 * self.num_layers_ + 1
 
     def decode_step(self, input_token_id: int) -> int:
         return self._single(input_token_id, None)
