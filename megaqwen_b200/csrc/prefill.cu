@@ -106,16 +106,20 @@ static void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 #define MQ_GEMM_BUDGET_KB 200   // shared memory for the operand ring of one CTA
 #define MQ_GEMM_MIN_CTAS 1
 #endif
-template <int BN, int EPI>
+// MT = 128-row A tiles per CTA.  With MT = 2 a CTA computes a 256-row output tile with two
+// accumulators that share every B tile: the 128 x 128 tiles are bound by the operand traffic
+// from the L2 into the SMs, and a 256-row tile moves a third less of it per FLOP.
+template <int BN, int EPI, int MT = 1>
 struct GemmCfg {
     static constexpr int NB = (EPI == EPI_SWIGLU) ? 2 : 1;                       // B operands per stage
-    static constexpr int STAGE_BYTES = GM_BM * GM_BK * 2 + NB * BN * GM_BK * 2;
+    static constexpr int A_BYTES = MT * GM_BM * GM_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + NB * BN * GM_BK * 2;
     static constexpr int STAGES = (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES > 6 ? 6 : (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES;
-    static constexpr int TMEM_COLS = NB * BN;                                    // power of two >= 32
+    static constexpr int TMEM_COLS = MT * NB * BN;                               // power of two >= 32, at most 512
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN, int EPI>
+template <int BN, int EPI, int MT>
 __global__ void __launch_bounds__(GM_THREADS, MQ_GEMM_MIN_CTAS)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
@@ -125,7 +129,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
     // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
     // and tmB2 (up) for the same tile.
-    using Cfg = GemmCfg<BN, EPI>;
+    using Cfg = GemmCfg<BN, EPI, MT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
@@ -134,7 +138,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int m0 = blockIdx.y * GM_BM, n0 = blockIdx.x * BN;
+    const int m0 = blockIdx.y * GM_BM * MT, n0 = blockIdx.x * BN;
     const int nk = K / GM_BK;
     const int tile = blockIdx.x;
     const CUtensorMap* mapB = &tmB;
@@ -162,9 +166,10 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 if (kb >= Cfg::STAGES) mbar_wait(&empty[s], (uint32_t)((kb / Cfg::STAGES) - 1) & 1u, status);
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
                 mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
-                tma_load_2d(st, &tmA, kb * GM_BK, m0, &full[s]);
-                tma_load_2d(st + GM_BM * GM_BK * 2, mapB, kb * GM_BK, brow0, &full[s]);
-                if (EPI == EPI_SWIGLU) tma_load_2d(st + GM_BM * GM_BK * 2 + BN * GM_BK * 2, &tmB2, kb * GM_BK, n0, &full[s]);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) tma_load_2d(st + mt * GM_BM * GM_BK * 2, &tmA, kb * GM_BK, m0 + mt * GM_BM, &full[s]);
+                tma_load_2d(st + Cfg::A_BYTES, mapB, kb * GM_BK, brow0, &full[s]);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + Cfg::A_BYTES + BN * GM_BK * 2, &tmB2, kb * GM_BK, n0, &full[s]);
             }
         }
         __syncwarp();
@@ -177,14 +182,17 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 mbar_wait(&full[s], (uint32_t)(kb / Cfg::STAGES) & 1u, status);
                 tc_fence_after();
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
-                const uint64_t da = smem_desc_sw128(st);
-                const uint64_t db = smem_desc_sw128(st + GM_BM * GM_BK * 2);
-                const uint64_t db2 = smem_desc_sw128(st + GM_BM * GM_BK * 2 + BN * GM_BK * 2);
+                const uint64_t db = smem_desc_sw128(st + Cfg::A_BYTES);
+                const uint64_t db2 = smem_desc_sw128(st + Cfg::A_BYTES + BN * GM_BK * 2);
 #pragma unroll
-                for (int k = 0; k < GM_BK / 16; ++k) {
-                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);              // +32 bytes per K=16 step
-                    if (EPI == EPI_SWIGLU) umma_bf16(tmem_base + BN, da + 2 * k, db2 + 2 * k, idesc, acc);
+                for (int mt = 0; mt < MT; ++mt) {   // accumulator (mt, nb) lives at TMEM column (mt * NB + nb) * BN
+                    const uint64_t da = smem_desc_sw128(st + mt * GM_BM * GM_BK * 2);
+#pragma unroll
+                    for (int k = 0; k < GM_BK / 16; ++k) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        umma_bf16(tmem_base + mt * Cfg::NB * BN, da + 2 * k, db + 2 * k, idesc, acc);   // +32 bytes per K=16 step
+                        if (EPI == EPI_SWIGLU) umma_bf16(tmem_base + (mt * Cfg::NB + 1) * BN, da + 2 * k, db2 + 2 * k, idesc, acc);
+                    }
                 }
                 umma_commit(&empty[s]);     // frees this stage once the MMAs above have read it
             }
@@ -196,8 +204,10 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         mbar_wait(accum, 0, status);
         tc_fence_after();
         const int quarter = warp & 3;
-        const int row = m0 + quarter * 32 + lane;
-        const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int mt = 0; mt < MT; ++mt) {
+        const int row = m0 + mt * GM_BM + quarter * 32 + lane;
+        const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * Cfg::NB * BN);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
             uint32_t v[32];
@@ -235,6 +245,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
 #pragma unroll
                 for (int q = 0; q < 4; ++q) cp[q] = make_uint4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
             }
+        }
         }
         tc_fence_before();
     }
@@ -772,16 +783,16 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
     return MQ_OK;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int MT = 1>
 static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf16* C, const bf16* R, int M, int N, int K, int ldc,
                        unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0) {
     // rows0 > 0: B, B2, B3 hold rows0, rows1 and N - rows0 - rows1 output columns (concatenated along N)
-    using Cfg = GemmCfg<BN, EPI>;
+    using Cfg = GemmCfg<BN, EPI, MT>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm<BN, EPI, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
         if (e != cudaSuccess) return (int)e;
         attr_set[dev] = true;
     }
@@ -804,8 +815,8 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
         rc = get_map(B3, (uint64_t)(N - rows0 - rows1), (uint64_t)K, (uint64_t)K, BN, &mb3);
         if (rc != MQ_OK) return rc;
     }
-    dim3 grid(N / BN, (M + GM_BM - 1) / GM_BM);
-    launch_pdl(k_gemm<BN, EPI>, dim3(grid), dim3(GM_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
+    dim3 grid(N / BN, (M + GM_BM * MT - 1) / (GM_BM * MT));
+    launch_pdl(k_gemm<BN, EPI, MT>, dim3(grid), dim3(GM_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
                                                              C, R, M, N, K, ldc, status);
     return (int)cudaGetLastError();
 }
@@ -1093,12 +1104,16 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     }
     launch_pdl(k_pf_embed, dim3(S), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status);
     int rc;
+    const bool big = S >= 1024;
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
         launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, S);
         // q | k | v in one launch: 32 column tiles from three weight matrices
-        rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
-                                         (const bf16*)w.v_proj, QSZ, KVSZ);
+        // from 1024 rows on, 256-row tiles (two accumulators per CTA) still give 96-128 CTAs
+        rc = big ? launch_gemm<128, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
+                                                  (const bf16*)w.v_proj, QSZ, KVSZ)
+                 : launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
+                                               (const bf16*)w.v_proj, QSZ, KVSZ);
         if (rc) return rc;
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
@@ -1110,7 +1125,8 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
                          : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
         if (rc) return rc;
         launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, S);
-        rc = launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
+        rc = big ? launch_gemm<128, EPI_SWIGLU, 2>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream)
+                 : launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
         if (rc) return rc;
         rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream)
                          : launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream);
