@@ -1110,7 +1110,9 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, S);
         // q | k | v in one launch: 32 column tiles from three weight matrices
         // from 1024 rows on, 256-row tiles (two accumulators per CTA) still give 96-128 CTAs
-        rc = big ? launch_gemm<128, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
+        rc = S >= 2048 ? launch_gemm<256, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
+                                                        (const bf16*)w.v_proj, QSZ, KVSZ)
+           : big ? launch_gemm<128, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                                   (const bf16*)w.v_proj, QSZ, KVSZ)
                  : launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                                (const bf16*)w.v_proj, QSZ, KVSZ);
