@@ -234,6 +234,7 @@ typedef struct MqBatchBuffers {
  * [batch, vocab].  vocab must be a multiple of 128. */
 int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens,
                            int* out_tokens, float* logits_f32, void* stream);
+/* Kernels one step launches on the tile-GEMM path (batch > 64); at most one fewer per layer otherwise. */
 int mq_decode_batch_launch_count(int num_layers);
 
 /* Number of kernels one mq_launch_prefill call launches. */

@@ -359,15 +359,6 @@ __device__ __forceinline__ float sum_splits(const float* part, int ksplit, size_
     return s;
 }
 
-// out[row, col0 + c] = bf16(sum)            (q / k / v projections into the qkv buffer)
-__global__ void __launch_bounds__(256) k_sk_store(const float* __restrict__ part, int ksplit, int M, int N, bf16* __restrict__ out, int ldo) {
-    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
-    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
-    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= (size_t)M * N) return;
-    const int row = (int)(i / N), col = (int)(i % N);
-    out[(size_t)row * ldo + col] = __float2bfloat16_rn(sum_splits(part, ksplit, (size_t)M * N, i));
-}
 
 // h = bf16(h + bf16(sum));  x = rmsnorm(h) * w      one CTA per row (N = 1024), 4 columns per thread
 __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__ part, int ksplit, int M, bf16* __restrict__ h,
@@ -459,11 +450,14 @@ __global__ void __launch_bounds__(256) k_pf_rmsnorm(const bf16* __restrict__ h, 
 __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, const bf16* __restrict__ wq, const bf16* __restrict__ wk,
                                                         const bf16* __restrict__ cos, const bf16* __restrict__ sin, bf16* __restrict__ k_cache,
                                                         bf16* __restrict__ v_cache, int layer, int pos0, int max_seq,
-                                                        const int* __restrict__ pos_rows, size_t seq_stride) {
+                                                        const int* __restrict__ pos_rows, size_t seq_stride,
+                                                        const float* __restrict__ part, int ksplit, int M) {
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     // pos_rows == nullptr: one sequence, row s sits at position pos0 + s.
     // pos_rows != nullptr: row s is sequence s at position pos_rows[s]; its cache starts s * seq_stride elements in.
+    // part != nullptr: the raw q|k|v row is not in qkv yet but in ksplit fp32 partial planes part[ks][M][QKV]
+    // of a K-split GEMM; they are summed in index order and rounded to bf16 here (q is then written to qkv).
     // A warp handles units (q heads 0..15, k heads 16..23, v heads 24..31) blockIdx.y * 8 + warp,
     // then every gridDim.y * 8 further: one CTA per row with gridDim.y = 1, four with 4.
     const int lane = threadIdx.x & 31;
@@ -480,15 +474,34 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
     for (int unit = blockIdx.y * 8 + (threadIdx.x >> 5); unit < NQ + 2 * NKV; unit += gridDim.y * 8) {
         if (unit >= NQ + NKV) {   // V head: raw copy into the cache
             const int g = unit - NQ - NKV;
-            const uint2 u = *reinterpret_cast<const uint2*>(row + QSZ + KVSZ + g * D + 4 * lane);
+            uint2 u;
+            if (part) {
+                const size_t i0 = (size_t)s * QKV + QSZ + KVSZ + g * D + 4 * lane;
+                float f[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) f[e] = sum_splits(part, ksplit, (size_t)M * QKV, i0 + e);
+                u = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+            } else {
+                u = *reinterpret_cast<const uint2*>(row + QSZ + KVSZ + g * D + 4 * lane);
+            }
             *reinterpret_cast<uint2*>(v_cache + ((size_t)(layer * NKV + g) * max_seq + pos) * D + 4 * lane) = u;
             continue;
         }
         const bool is_q = unit < NQ;
         bf16* head = is_q ? row + unit * D : row + QSZ + (unit - NQ) * D;
         const bf16* wn = is_q ? wq : wk;
-        const uint32_t ulo = *reinterpret_cast<const uint32_t*>(head + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
-        const float xl[2] = {bf_lo(ulo), bf_hi(ulo)}, xh[2] = {bf_lo(uhi), bf_hi(uhi)};
+        float xl[2], xh[2];
+        if (part) {
+            const size_t i0 = (size_t)s * QKV + (size_t)(head - row) + 2 * lane;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                xl[e] = rbf(sum_splits(part, ksplit, (size_t)M * QKV, i0 + e));
+                xh[e] = rbf(sum_splits(part, ksplit, (size_t)M * QKV, i0 + 64 + e));
+            }
+        } else {
+            const uint32_t ulo = *reinterpret_cast<const uint32_t*>(head + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
+            xl[0] = bf_lo(ulo); xl[1] = bf_hi(ulo); xh[0] = bf_lo(uhi); xh[1] = bf_hi(uhi);
+        }
         float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
         ss = warp_sum(ss);
         const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
@@ -1119,7 +1132,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         if (rc) return rc;
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
-                                                         model->max_seq_len, nullptr, 0);
+                                                         model->max_seq_len, nullptr, 0, nullptr, 0, 0);
         launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
                                                                                           attn, S, pos0, l, model->max_seq_len);
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
@@ -1141,6 +1154,7 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     return launch_lmhead_only(model, dbuf, out_token, logits, stream);
 }
 
+// kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
 extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
 
 extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens, int* out_tokens,
@@ -1179,10 +1193,10 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
             const int rqkv[3] = {QSZ, KVSZ, KVSZ};
             rc = launch_skinny(wqkv, rqkv, 3, x, H, part, B, H, 4, status, stream);
             if (rc) return rc;
-            launch_pdl(k_sk_store, dim3((B * QKV + 255) / 256), dim3(256), 0, stream, part, 4, B, QKV, qkv, QKV);
+            // sums the four K-split planes, applies QK-norm + RoPE, writes q to qkv and k, v to the caches
             launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                              (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
-                                                             model->max_seq_len, bb->positions, seq_stride);
+                                                             model->max_seq_len, bb->positions, seq_stride, (const float*)part, 4, B);
             launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                              model->max_seq_len, seq_stride);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
@@ -1213,7 +1227,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
         if (rc) return rc;
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
-                                                         model->max_seq_len, bb->positions, seq_stride);
+                                                         model->max_seq_len, bb->positions, seq_stride, nullptr, 0, 0);
         launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                          model->max_seq_len, seq_stride);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
