@@ -888,13 +888,16 @@ namespace mq {
 
 // ---------------------------------------------------------------- batched decode (one new token per sequence)
 // One CTA per (sequence, kv head); the two query heads share the K/V stream.  Each warp owns
-// the 16-position tiles warp, warp + 8, .. of the sequence and streams them through its own
-// three-stage ring of padded rows in shared memory (16-byte cp.async, two tiles in flight per
-// warp, no block barrier inside the loop).  Per tile: scores = K_tile . q on mma.sync (positions
+// the 16-position tiles warp, warp + 12, .. of the sequence and streams them through its own
+// two-stage ring of padded rows in shared memory (16-byte cp.async, the next tile in flight
+// while this one is multiplied, no block barrier inside the loop; twelve warps per SM rather
+// than eight with deeper rings, because the per-tile chain of dependent instructions, not
+// the bytes in flight, bounds a warp; one 256-byte bulk copy per row instead of sixteen
+// cp.async was measured slower: 3.07 vs 2.81 ms per step at batch 64).  Per tile: scores = K_tile . q on mma.sync (positions
 // are M, the two heads two of the eight N columns), softmax of the tile, P rounded to bf16,
 // out += P . V_tile (ldmatrix.trans on V).  About a sixth of the instructions of an fp32-FMA
 // loop over the same bytes, which is what bounded the FMA version at 2.7 TB/s.
-constexpr int BD_THREADS = 256, BD_STAGES = 3, BD_LD = D + 8;
+constexpr int BD_THREADS = 384, BD_STAGES = 2, BD_LD = D + 8;   // 12 warps x 2 stages x 8.5 KB = 209 KB
 constexpr int BD_STAGE_ELEMS = 2 * 16 * BD_LD;                                  // K tile then V tile
 constexpr size_t BD_SMEM = (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS * 2 + 2 * D * 2 + (BD_THREADS / 32) * 32 * 2;
 
@@ -1027,6 +1030,7 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
             *reinterpret_cast<float2*>(s_acc + (warp * 2 + gi) * D + j * 8 + 2 * ti) = make_float2(o[j][0], o[j][1]);
     }
     __syncthreads();
+    if (tid >= 2 * D) return;
     const int hh = tid >> 7, d = tid & 127;
     float M = -1e30f;
 #pragma unroll
