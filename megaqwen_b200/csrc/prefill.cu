@@ -904,12 +904,16 @@ constexpr size_t BD_SMEM = (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEM
 __device__ __forceinline__ void bd_load_tile(bf16* stage, const bf16* kb, const bf16* vb, int tile, int len, int lane) {
     // 16 rows x 16 chunks of 16 bytes for K and the same for V: 16 copies per lane.  Rows past
     // the end of the sequence re-read the last row (their probabilities are zero).
+    // copy i of a lane is chunk (lane & 15) of row 2 * i + (lane >> 4)
+    const int c8 = (lane & 15) * 8, r0 = lane >> 4;
+    bf16* sdst = stage + r0 * BD_LD + c8;
+    const int last = len - 1 - tile * 16 - r0;            // copies with 2 * i > last re-read the last row
+    const size_t gbase = (size_t)(tile * 16 + r0) * D + c8;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int idx = i * 32 + lane, r = idx >> 4, c = idx & 15;
-        const int p = min(tile * 16 + r, len - 1);
-        cp_async16(stage + r * BD_LD + c * 8, kb + (size_t)p * D + c * 8);
-        cp_async16(stage + 16 * BD_LD + r * BD_LD + c * 8, vb + (size_t)p * D + c * 8);
+        const size_t goff = gbase + (size_t)min(2 * i, last) * D;
+        cp_async16(sdst + 2 * i * BD_LD, kb + goff);
+        cp_async16(sdst + (16 + 2 * i) * BD_LD, vb + goff);
     }
 }
 
@@ -947,7 +951,15 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
     float o[16][4];
 #pragma unroll
     for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
-    const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
+    uint32_t qb[D / 16][2];   // B fragments of the two query heads (columns 2..7 are zero)
+    {
+        const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            qb[ks][0] = gi < 2 ? lds32(qaddr + ks * 32) : 0u;
+            qb[ks][1] = gi < 2 ? lds32(qaddr + ks * 32 + 16) : 0u;
+        }
+    }
     bf16* pw = ps + warp * 32;
     int it = 0;
     for (int tile = warp; tile < ntiles; tile += BD_THREADS / 32, ++it) {
@@ -967,9 +979,7 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
         for (int ks = 0; ks < D / 16; ++ks) {
             uint32_t af[4];
             ldsm4(af, kaddr + ks * 32);
-            uint32_t b0 = lds32(qaddr + ks * 32), b1 = lds32(qaddr + ks * 32 + 16);
-            if (gi >= 2) { b0 = 0u; b1 = 0u; }
-            mma16816(c, af, b0, b1);
+            mma16816(c, af, qb[ks][0], qb[ks][1]);
         }
         // lanes with ti == 0 hold head 0 / head 1 of positions gi (c[0], c[1]) and gi + 8 (c[2], c[3])
         const int p_lo = tile * 16 + gi, p_hi = p_lo + 8;
@@ -1007,12 +1017,15 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
             pa[0] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 2 * ti);
             pa[2] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 8 + 2 * ti);
         }
-        const float crg = gi == 0 ? cr0 : cr1;
+        if (cr0 != 1.f || cr1 != 1.f) {   // the same for every lane
+            const float crg = gi == 0 ? cr0 : cr1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { o[j][0] *= crg; o[j][1] *= crg; }
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             uint32_t bv[4];
             ldsm4_t(bv, vaddr + j * 32);
-            o[2 * j][0] *= crg; o[2 * j][1] *= crg; o[2 * j + 1][0] *= crg; o[2 * j + 1][1] *= crg;
             mma16816(o[2 * j], pa, bv[0], bv[1]);
             mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
         }
