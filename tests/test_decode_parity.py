@@ -90,6 +90,16 @@ def test_single_steps_chain_and_graph_agree(tiny):
                 cur = dec.decode_step(cur)
                 out.append(cur)
             return out
+        if mode == "single_eager":      # 141 eager launches per step instead of the one-step graph
+            dec.use_step_graph = False
+            try:
+                out, cur = [], prompt[-1]
+                for _ in range(40):
+                    cur = dec.decode_step(cur)
+                    out.append(cur)
+                return out
+            finally:
+                dec.use_step_graph = True
         if mode == "chain":
             return dec.decode_steps_cuda(prompt[-1], 40).tolist()
         if mode == "graph":
@@ -103,6 +113,7 @@ def test_single_steps_chain_and_graph_agree(tiny):
             dec.use_pdl = True
 
     a = run("single")
+    assert run("single_eager") == a
     assert run("chain") == a
     assert run("graph") == a
     assert run("graph") == a          # replay of the cached graph
