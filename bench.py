@@ -83,6 +83,10 @@ class ClockSampler(threading.Thread):
 from megaqwen_b200.replicas import aggregate_throughput, barrier, dist_env, init_control_plane, max_over_ranks  # noqa: E402
 
 
+NCU_STEP_DRAM_BYTES = 1430.2e6     # measured, see run_ours
+NCU_STEP_CACHE_LEN = 2050
+
+
 def host_threads() -> int:
     """Host cores this process may run on."""
     try:
@@ -311,6 +315,11 @@ def run_ours(args):
     bytes_pass = sum(QWEN3_0_6B.decode_bytes(PROMPT_LEN + i + 1) for i in range(NEW_TOKENS))
     step_s = (tot_dev / 1e3) / (NEW_TOKENS * args.steps)
     achieved = bytes_pass / NEW_TOKENS / step_s / 1e9
+    # DRAM traffic of one step: the ncu capture of all 141 kernels at cache length 2050 (read + write
+    # 1430.2 MB against 1427.3 MB algorithmic, profiles/decode_pdl_chain_ctx2048.md), moved to this
+    # run's mean cache length with the per-position KV bytes (traffic grows in proportion to them)
+    mean_len = PROMPT_LEN + (NEW_TOKENS + 1) / 2
+    traffic = NCU_STEP_DRAM_BYTES + (mean_len - NCU_STEP_CACHE_LEN) * (QWEN3_0_6B.decode_bytes(2) - QWEN3_0_6B.decode_bytes(1))
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": tot_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -322,7 +331,9 @@ def run_ours(args):
                 "prefill_h2d_bytes_per_step": 4 * PROMPT_LEN},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "one decode step (141 chained kernels)",
+                     "traffic": traffic, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum over the 141 kernels of one step at cache length 2050, scaled to the mean cache length of this run",
+                     "algorithmic_bytes": bytes_pass / NEW_TOKENS,
+                     "peak_kind": peak_kind, "kernel": "one decode step (141 chained kernels)",
                      "frac_of_8TBps": achieved / 8000.0, "us_per_token": step_s * 1e6},
         "clocks": clocks,
         "wall_s": wall,
