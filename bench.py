@@ -316,7 +316,7 @@ def run_ours(args):
     step_s = (tot_dev / 1e3) / (NEW_TOKENS * args.steps)
     achieved = bytes_pass / NEW_TOKENS / step_s / 1e9
     # DRAM traffic of one step: the ncu capture of all 141 kernels at cache length 2050 (read + write
-    # 1430.2 MB against 1427.3 MB algorithmic, profiles/decode_pdl_chain_ctx2048.md), moved to this
+    # 1430.2 MB against 1427.3 MB algorithmic; summary under profiles/), moved to this
     # run's mean cache length with the per-position KV bytes (traffic grows in proportion to them)
     mean_len = PROMPT_LEN + (NEW_TOKENS + 1) / 2
     traffic = NCU_STEP_DRAM_BYTES + (mean_len - NCU_STEP_CACHE_LEN) * (QWEN3_0_6B.decode_bytes(2) - QWEN3_0_6B.decode_bytes(1))
