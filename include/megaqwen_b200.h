@@ -234,6 +234,18 @@ typedef struct MqBatchBuffers {
  * [batch, vocab].  vocab must be a multiple of 128. */
 int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens,
                            int* out_tokens, float* logits_f32, void* stream);
+/* Prefill of several sequences in one pass (no reference counterpart: the reference prefills one
+ * sequence at a time).  The prompts are packed row after row: ids[total_rows]; row_seq[r] /
+ * row_pos[r] give the sequence (0..bb->batch-1) and position of packed row r; the causal
+ * attention runs per 64-row query tile: tile t covers rows tile_q0[t]..+63 of sequence
+ * tile_seq[t] (callers list long tiles first); seq_len[b] and seq_row0[b] are the length and
+ * the first packed row of sequence b.  All tables are device int32 arrays.  bb->positions[b]
+ * must hold seq_len[b] - 1 on entry and holds seq_len[b] afterwards; out_tokens[b] is the
+ * token that follows prompt b.  total_rows must not exceed bb->act.max_tokens. */
+int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffers* bb, const int* ids, const int* row_seq,
+                             const int* row_pos, const int* tile_seq, const int* tile_q0, const int* seq_len,
+                             const int* seq_row0, int total_rows, int num_tiles, int* out_tokens, void* stream);
+
 /* Kernels one step launches on the tile-GEMM path (batch > 64); at most one fewer per layer otherwise. */
 int mq_decode_batch_launch_count(int num_layers);
 

@@ -74,6 +74,8 @@ SIGNATURES = {
                                     C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "mq_launch_decode_batch": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers), C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_void_p]),
+    "mq_launch_prefill_packed": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers)] + [C.c_void_p] * 7 +
+                                 [C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "mq_decode_batch_launch_count": (C.c_int, [C.c_int]),
     "mq_prefill_launch_count": (C.c_int, [C.c_int]),
     "mq_launch_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,

@@ -50,7 +50,8 @@ class MegakernelBatchDecoder:
             self.v_cache_ = torch.zeros_like(self.k_cache_)
             self._positions = torch.zeros(B, dtype=i32, device=dev)
             self._logits = torch.empty((B, self.vocab_size_), dtype=bf, device=dev)
-            cap = max(B, self.max_prefill_len_)
+            # room for a ragged batch of prompts packed into one pass (at most 16384 rows, 370 MB)
+            cap = max(B, self.max_prefill_len_, min(B * self.max_prefill_len_, 16384))
             self._act = [torch.empty((cap, w), dtype=bf, device=dev)
                          for w in (_HIDDEN, _HIDDEN, _NQ * _D + 2 * _NKV * _D, _NQ * _D, _INTER)]
             self._pf = MqPrefillBuffers(*[_ptr(t) for t in self._act], cap)
@@ -61,6 +62,7 @@ class MegakernelBatchDecoder:
             self._tok_a = torch.zeros(B, dtype=i32, device=dev)
             self._partials = torch.empty(4 * min(B, 64) * 2 * _INTER, dtype=torch.float32, device=dev)
             self.use_splitk = True
+            self.use_packed_prefill = True
             self._chain = None
             self._graphs = {}
         self.batch_ = 0
@@ -97,23 +99,70 @@ class MegakernelBatchDecoder:
         return self.v_cache_
 
     # ------------------------------------------------------------------ API
+    def _prefill_packed(self, prompts, b0: int, out: torch.Tensor) -> None:
+        """Sequences b0 .. b0+len(prompts)-1 in ONE pass: prompts packed row after row."""
+        lens = torch.tensor([int(p.numel()) for p in prompts], dtype=torch.int64)
+        nb, total = len(prompts), int(lens.sum())
+        row0 = torch.cumsum(lens, 0) - lens
+        row_seq = torch.repeat_interleave(torch.arange(nb), lens)
+        row_pos = torch.arange(total) - row0[row_seq]
+        ntile = (lens + 63) // 64
+        tile_seq = torch.repeat_interleave(torch.arange(nb), ntile)
+        tile_q0 = (torch.arange(int(ntile.sum())) - (torch.cumsum(ntile, 0) - ntile)[tile_seq]) * 64
+        order = torch.argsort(tile_q0, descending=True, stable=True)      # long query tiles first
+        tile_seq, tile_q0 = tile_seq[order], tile_q0[order]
+        tables = torch.cat([torch.cat(prompts).to(torch.int64), row_seq, row_pos, tile_seq, tile_q0, lens, row0]).to(torch.int32)
+        dev_t = tables.to(self.device)
+        offs, acc = [], 0
+        for n in (total, total, total, tile_seq.numel(), tile_seq.numel(), nb, nb):
+            offs.append(_ptr(dev_t) + 4 * acc)
+            acc += n
+        self._positions[b0:b0 + nb].copy_((lens - 1).to(torch.int32))
+        bb = MqBatchBuffers(_ptr(self.k_cache_[b0]), _ptr(self.v_cache_[b0]), _ptr(self._positions) + 4 * b0, _ptr(self._logits),
+                            self._pf, _ptr(self._scalars) + 4, nb, None, 0)
+        rc = self._lib.mq_launch_prefill_packed(C.byref(self._model), C.byref(bb), *offs, total, int(tile_seq.numel()),
+                                                _ptr(out) + 4 * b0, self._stream())
+        _lib.check(rc, "mq_launch_prefill_packed")
+        self.launches += 1 + 8 * self.num_layers_ + 4
+        self._keep = dev_t     # the launch reads the tables asynchronously
+
     def prefill_batch(self, prompts) -> torch.Tensor:
         """Prefill one prompt per sequence (ragged lengths allowed); sequence b
-        takes prompts[b].  Returns the next token of every sequence (cpu int32)."""
+        takes prompts[b].  Returns the next token of every sequence (cpu int32).
+        Consecutive sequences are packed into passes of at most the activation
+        buffers' row capacity; a prompt that fills a pass alone goes through the
+        single-sequence entry point."""
         if len(prompts) == 0 or len(prompts) > self.max_batch_:
             raise RuntimeError(f"prefill_batch: batch must be in 1..{self.max_batch_}")
         out = torch.zeros(len(prompts), dtype=torch.int32, device=self.device)
+        prompts = [torch.as_tensor(p, dtype=torch.int32).reshape(-1).cpu() for p in prompts]
+        for ids in prompts:
+            n = int(ids.numel())
+            if n <= 0:
+                raise RuntimeError("prefill_step: empty input")
+            if n > self.max_prefill_len_:
+                raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
+            if n > self.max_seq_len_:
+                raise RuntimeError("prefill_step would exceed max_seq_len")
+        cap = int(self._pf.max_tokens)
+        if self.use_packed_prefill and len(prompts) > 1:
+            with torch.cuda.device(self.device):
+                b = 0
+                while b < len(prompts):
+                    e, rows = b, 0
+                    while e < len(prompts) and rows + int(prompts[e].numel()) <= cap:
+                        rows += int(prompts[e].numel())
+                        e += 1
+                    self._prefill_packed(prompts[b:e], b, out)
+                    b = e
+            self.batch_ = len(prompts)
+            res = out.cpu()
+            self.check_status()
+            return res
         lens = []
         with torch.cuda.device(self.device):
             for b, ids in enumerate(prompts):
-                ids = torch.as_tensor(ids, dtype=torch.int32).reshape(-1)
                 n = int(ids.numel())
-                if n <= 0:
-                    raise RuntimeError("prefill_step: empty input")
-                if n > self.max_prefill_len_:
-                    raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
-                if n > self.max_seq_len_:
-                    raise RuntimeError("prefill_step would exceed max_seq_len")
                 dev_ids = ids.to(self.device, non_blocking=True)
                 dbuf = MqDecodeBuffers(_ptr(self.k_cache_[b]), _ptr(self.v_cache_[b]), _ptr(self._hidden), None, None, None, None,
                                        _ptr(self._counters), _ptr(self._slot), _ptr(self._scalars) + 4, 0)

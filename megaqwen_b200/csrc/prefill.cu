@@ -451,11 +451,13 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
                                                         const bf16* __restrict__ cos, const bf16* __restrict__ sin, bf16* __restrict__ k_cache,
                                                         bf16* __restrict__ v_cache, int layer, int pos0, int max_seq,
                                                         const int* __restrict__ pos_rows, size_t seq_stride,
-                                                        const float* __restrict__ part, int ksplit, int M) {
+                                                        const float* __restrict__ part, int ksplit, int M,
+                                                        const int* __restrict__ row_seq) {
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     // pos_rows == nullptr: one sequence, row s sits at position pos0 + s.
-    // pos_rows != nullptr: row s is sequence s at position pos_rows[s]; its cache starts s * seq_stride elements in.
+    // pos_rows != nullptr: row s is at position pos_rows[s] of sequence row_seq[s] (sequence s if row_seq is
+    // null), whose cache starts that many times seq_stride elements in.
     // part != nullptr: the raw q|k|v row is not in qkv yet but in ksplit fp32 partial planes part[ks][M][QKV]
     // of a K-split GEMM; they are summed in index order and rounded to bf16 here (q is then written to qkv).
     // A warp handles units (q heads 0..15, k heads 16..23, v heads 24..31) blockIdx.y * 8 + warp,
@@ -463,7 +465,11 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
     const int lane = threadIdx.x & 31;
     const int s = blockIdx.x;
     const int pos = pos_rows ? min(max(pos_rows[s], 0), max_seq - 1) : pos0 + s;
-    if (pos_rows) { k_cache += (size_t)s * seq_stride; v_cache += (size_t)s * seq_stride; }
+    if (pos_rows) {
+        const size_t seq = row_seq ? (size_t)row_seq[s] : (size_t)s;
+        k_cache += seq * seq_stride;
+        v_cache += seq * seq_stride;
+    }
     bf16* row = qkv + (size_t)s * QKV;
     const bf16* cosr = cos + (size_t)pos * D;
     const bf16* sinr = sin + (size_t)pos * D;
@@ -535,6 +541,13 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
 // (16-byte cp.async, the next tile in flight while this one is multiplied).
 constexpr int FA_BQ = 64, FA_BK = 64, FA_LD = D + 8, FA_NG = 2, FA_THREADS = FA_NG * 128;
 constexpr int FA_TILE_ELEMS = FA_BK * FA_LD;                                  // one K or V tile
+struct PackedTiles {          // all null / zero for a single prompt
+    const int* tile_seq;      // [tiles] sequence of query tile t
+    const int* tile_q0;       // [tiles] first query row of the tile inside its sequence
+    const int* seq_len;       // [sequences]
+    const int* seq_row0;      // [sequences] first packed row of the sequence
+    size_t seq_stride;        // elements between the caches of consecutive sequences
+};
 constexpr size_t FA_SMEM = (size_t)(FA_BQ * FA_LD + FA_NG * 2 * 2 * FA_TILE_ELEMS) * 2;
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -566,7 +579,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 
 __global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
                                                                const bf16* __restrict__ v_cache, bf16* __restrict__ out, int S, int pos0,
-                                                               int layer, int max_seq) {
+                                                               int layer, int max_seq, PackedTiles pt) {
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     extern __shared__ __align__(16) uint8_t fa_smem[];
@@ -575,7 +588,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __re
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = warp >> 2, wq = warp & 3, gtid = tid & 127;
     const int head = blockIdx.x, g = head / (NQ / NKV);
-    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * FA_BQ;  // longest query tiles are dispatched first
+    int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * FA_BQ;  // longest query tiles are dispatched first
+    if (pt.tile_seq) {   // several prompts packed row after row: tile blockIdx.y belongs to one of them (the host sorts long tiles first)
+        const int b = pt.tile_seq[blockIdx.y];
+        q0 = pt.tile_q0[blockIdx.y];
+        S = pt.seq_len[b];
+        const size_t row0 = (size_t)pt.seq_row0[b];
+        qkv += row0 * QKV;
+        out += row0 * QSZ;
+        k_cache += (size_t)b * pt.seq_stride;
+        v_cache += (size_t)b * pt.seq_stride;
+    }
     const bf16* kbase = k_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
     const bf16* vbase = v_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
     bf16* gring = ring + (size_t)grp * 4 * FA_TILE_ELEMS;
@@ -882,6 +905,16 @@ __global__ void k_pf_copy_row(const bf16* __restrict__ src, bf16* __restrict__ d
     reinterpret_cast<uint4*>(dst)[threadIdx.x] = reinterpret_cast<const uint4*>(src)[threadIdx.x];
 }
 
+// dst[b] = src[last packed row of sequence b]
+__global__ void k_pf_gather_last(const bf16* __restrict__ src, const int* __restrict__ seq_row0, const int* __restrict__ seq_len,
+                                 bf16* __restrict__ dst) {
+    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
+    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    const int b = blockIdx.x;
+    const size_t row = (size_t)seq_row0[b] + (size_t)seq_len[b] - 1;
+    reinterpret_cast<uint4*>(dst + (size_t)b * H)[threadIdx.x] = reinterpret_cast<const uint4*>(src + row * H)[threadIdx.x];
+}
+
 }  // namespace mq
 
 namespace mq {
@@ -1149,9 +1182,9 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         if (rc) return rc;
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
-                                                         model->max_seq_len, nullptr, 0, nullptr, 0, 0);
+                                                         model->max_seq_len, nullptr, 0, nullptr, 0, 0, nullptr);
         launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
-                                                                                          attn, S, pos0, l, model->max_seq_len);
+                                                                                          attn, S, pos0, l, model->max_seq_len, PackedTiles());
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
         rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream)
                          : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
@@ -1169,6 +1202,73 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     return launch_lmhead_only(model, dbuf, out_token, logits, stream);
+}
+
+// Prompts of several sequences packed row after row (a ragged batch in one pass): the linears
+// see one matrix of total_rows rows, QK-norm/RoPE and the cache writes use the per-row tables,
+// attention the per-tile tables, and the next token of every sequence comes from its last row
+// through the batched LM head.  bb->positions[b] must hold len_b - 1 on entry (the arg-max kernel
+// advances it to len_b).  All tables are device arrays built by the caller.
+extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffers* bb, const int* ids, const int* row_seq,
+                                        const int* row_pos, const int* tile_seq, const int* tile_q0, const int* seq_len,
+                                        const int* seq_row0, int total_rows, int num_tiles, int* out_tokens, void* stream_v) {
+    if (!model || !bb || !ids || !row_seq || !row_pos || !tile_seq || !tile_q0 || !seq_len || !seq_row0 || !out_tokens) return MQ_ERR_BAD_ARG;
+    if (!bb->k_cache || !bb->v_cache || !bb->positions || !bb->logits || !bb->status) return MQ_ERR_BAD_ARG;
+    const MqPrefillBuffers* pb = &bb->act;
+    if (!pb->h || !pb->x || !pb->qkv || !pb->attn || !pb->act) return MQ_ERR_BAD_ARG;
+    const int B = bb->batch, T = total_rows;
+    if (B <= 0 || T < B || num_tiles <= 0) return MQ_ERR_BAD_ARG;
+    if (T > pb->max_tokens) return MQ_ERR_TOO_LONG;
+    if (model->vocab_size % 128 != 0) return MQ_ERR_UNSUPPORTED;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    bf16* h = (bf16*)pb->h; bf16* x = (bf16*)pb->x; bf16* qkv = (bf16*)pb->qkv; bf16* attn = (bf16*)pb->attn; bf16* act = (bf16*)pb->act;
+    unsigned int* status = bb->status;
+    const size_t seq_stride = (size_t)model->num_layers * NKV * model->max_seq_len * D;
+    static bool fa_attr[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !fa_attr[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_pf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        fa_attr[dev] = true;
+    }
+    PackedTiles pt;
+    pt.tile_seq = tile_seq; pt.tile_q0 = tile_q0; pt.seq_len = seq_len; pt.seq_row0 = seq_row0; pt.seq_stride = seq_stride;
+    launch_pdl(k_pf_embed, dim3(T), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status);
+    int rc;
+    const bool big = T >= 1024;
+    for (int l = 0; l < model->num_layers; ++l) {
+        const MqLayerWeights& w = model->layers[l];
+        launch_pdl(k_pf_rmsnorm, dim3((T + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, T);
+        rc = big ? launch_gemm<128, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, T, QKV, H, QKV, status, stream,
+                                                  (const bf16*)w.v_proj, QSZ, KVSZ)
+                 : launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, T, QKV, H, QKV, status, stream,
+                                               (const bf16*)w.v_proj, QSZ, KVSZ);
+        if (rc) return rc;
+        launch_pdl(k_pf_qknorm_rope, dim3(dim3(T, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+                                                         (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
+                                                         model->max_seq_len, row_pos, seq_stride, nullptr, 0, 0, row_seq);
+        launch_pdl(k_pf_attention, dim3(dim3(NQ, num_tiles)), dim3(FA_THREADS), FA_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache,
+                                                                       attn, 0, 0, l, model->max_seq_len, pt);
+        rc = (T <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, T, H, QSZ, H, status, stream)
+                         : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, T, H, QSZ, H, status, stream);
+        if (rc) return rc;
+        launch_pdl(k_pf_rmsnorm, dim3((T + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, T);
+        rc = big ? launch_gemm<128, EPI_SWIGLU, 2>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, T, I, H, I, status, stream)
+                 : launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, T, I, H, I, status, stream);
+        if (rc) return rc;
+        rc = (T <= 1024) ? launch_gemm<64, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, T, H, I, H, status, stream)
+                         : launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, T, H, I, H, status, stream);
+        if (rc) return rc;
+    }
+    // last row of every sequence -> final norm -> LM head -> arg-max (advances positions[b] to len_b)
+    launch_pdl(k_pf_gather_last, dim3(B), dim3(H / 8), 0, stream, h, seq_row0, seq_len, attn);
+    launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, attn, (const bf16*)model->final_norm, x, B);
+    rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
+                                     model->vocab_size, status, stream);
+    if (rc) return rc;
+    launch_pdl(k_bd_argmax_advance, dim3(B), dim3(1024), 0, stream, (const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, (float*)nullptr);
+    return (int)cudaGetLastError();
 }
 
 // kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
@@ -1213,7 +1313,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
             // sums the four K-split planes, applies QK-norm + RoPE, writes q to qkv and k, v to the caches
             launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                              (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
-                                                             model->max_seq_len, bb->positions, seq_stride, (const float*)part, 4, B);
+                                                             model->max_seq_len, bb->positions, seq_stride, (const float*)part, 4, B, nullptr);
             launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                              model->max_seq_len, seq_stride);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
@@ -1244,7 +1344,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
         if (rc) return rc;
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
-                                                         model->max_seq_len, bb->positions, seq_stride, nullptr, 0, 0);
+                                                         model->max_seq_len, bb->positions, seq_stride, nullptr, 0, 0, nullptr);
         launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
                                                          model->max_seq_len, seq_stride);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);

@@ -125,3 +125,36 @@ def test_batch_errors(setup):
         bd.decode_batch(torch.zeros(3, dtype=torch.int32))
     with pytest.raises(RuntimeError, match="exceed max_seq_len"):
         bd.decode_batch_steps(torch.zeros(1, dtype=torch.int32), 1000)
+
+
+def test_packed_and_sequential_prefill_agree(setup):
+    """One packed pass over the ragged prompts writes the same caches and predicts the same
+    tokens as prefilling the sequences one after the other; with a row capacity that only
+    fits some of the prompts the batch is split into several packed passes."""
+    bd, _ = setup
+    prompts = [random_prompt(QWEN3_TINY, n, 6, i) for i, n in enumerate(LENS + [200, 17])]
+
+    def run(packed, cap=None):
+        bd.reset()
+        bd.use_packed_prefill = packed
+        keep = bd._pf.max_tokens
+        if cap:
+            bd._pf.max_tokens = cap
+        try:
+            first = bd.prefill_batch(prompts)
+        finally:
+            bd._pf.max_tokens = keep
+            bd.use_packed_prefill = True
+        n = len(prompts)
+        return first.tolist(), bd.positions().tolist(), bd.get_k_cache()[:n].clone(), bd.get_v_cache()[:n].clone()
+
+    a = run(False)
+    b = run(True)
+    c = run(True, cap=330)       # passes: [3, 40, 129] [300] [64, 200, 17]
+    for other in (b, c):
+        assert other[1] == a[1] == [int(p.numel()) for p in prompts]
+        assert torch.equal(other[2], a[2]) and torch.equal(other[3], a[3])
+        assert other[0] == a[0]
+    nxt = bd.decode_batch(torch.tensor(c[0], dtype=torch.int32))
+    assert nxt.numel() == len(prompts)
+    bd.check_status()
