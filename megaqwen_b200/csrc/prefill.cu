@@ -80,7 +80,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
 constexpr int GM_BM = 128;
 constexpr int GM_BK = 64;
 constexpr int GM_THREADS = 192;    // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..5 epilogue
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };   // PARTIAL: fp32 plane blockIdx.z of a K split
 
 // Every kernel of the prefill and batched-decode chains is launched with programmatic
 // stream serialisation and begins with griddepcontrol.wait + launch_dependents: the next
@@ -139,7 +139,9 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * GM_BM * MT, n0 = blockIdx.x * BN;
-    const int nk = K / GM_BK;
+    // EPI_PARTIAL: gridDim.z CTAs share an output tile, each takes a contiguous range of k-blocks
+    const int kb_first = (int)(((long long)blockIdx.z * (K / GM_BK)) / gridDim.z);
+    const int nk = (int)(((long long)(blockIdx.z + 1) * (K / GM_BK)) / gridDim.z) - kb_first;
     const int tile = blockIdx.x;
     const CUtensorMap* mapB = &tmB;
     int brow0 = n0;
@@ -167,9 +169,9 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
                 mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) tma_load_2d(st + mt * GM_BM * GM_BK * 2, &tmA, kb * GM_BK, m0 + mt * GM_BM, &full[s]);
-                tma_load_2d(st + Cfg::A_BYTES, mapB, kb * GM_BK, brow0, &full[s]);
-                if (EPI == EPI_SWIGLU) tma_load_2d(st + Cfg::A_BYTES + BN * GM_BK * 2, &tmB2, kb * GM_BK, n0, &full[s]);
+                for (int mt = 0; mt < MT; ++mt) tma_load_2d(st + mt * GM_BM * GM_BK * 2, &tmA, (kb_first + kb) * GM_BK, m0 + mt * GM_BM, &full[s]);
+                tma_load_2d(st + Cfg::A_BYTES, mapB, (kb_first + kb) * GM_BK, brow0, &full[s]);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + Cfg::A_BYTES + BN * GM_BK * 2, &tmB2, (kb_first + kb) * GM_BK, n0, &full[s]);
             }
         }
         __syncwarp();
@@ -212,6 +214,15 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         for (int c0 = 0; c0 < BN; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(trow + c0, v);
+            if (EPI == EPI_PARTIAL) {   // raw fp32 accumulators into plane blockIdx.z of C (a float [gridDim.z][M][ldc] array)
+                if (row < M) {
+                    float4* fp = reinterpret_cast<float4*>(reinterpret_cast<float*>(C) + ((size_t)blockIdx.z * M + row) * ldc + n0 + c0);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        fp[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                }
+                continue;
+            }
             uint32_t out[16];
             if (EPI == EPI_SWIGLU) {
                 uint32_t u[32];
@@ -376,6 +387,7 @@ __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__
     const uint2 hu = *reinterpret_cast<const uint2*>(h + base);
     float v[4] = {rbf(bf_lo(hu.x) + rbf(acc.x)), rbf(bf_hi(hu.x) + rbf(acc.y)), rbf(bf_lo(hu.y) + rbf(acc.z)), rbf(bf_hi(hu.y) + rbf(acc.w))};
     *reinterpret_cast<uint2*>(h + base) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+    if (!w) return;   // residual stream only (after the last layer nothing is normalised here)
     float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
     if (lane == 0) s_red[warp] = ss;
     __syncthreads();
@@ -821,7 +833,7 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
 
 template <int BN, int EPI, int MT = 1>
 static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf16* C, const bf16* R, int M, int N, int K, int ldc,
-                       unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0) {
+                       unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0, int ksplit = 1) {
     // rows0 > 0: B, B2, B3 hold rows0, rows1 and N - rows0 - rows1 output columns (concatenated along N)
     using Cfg = GemmCfg<BN, EPI, MT>;
     static bool attr_set[64] = {false};
@@ -851,7 +863,8 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
         rc = get_map(B3, (uint64_t)(N - rows0 - rows1), (uint64_t)K, (uint64_t)K, BN, &mb3);
         if (rc != MQ_OK) return rc;
     }
-    dim3 grid(N / BN, (M + GM_BM * MT - 1) / (GM_BM * MT));
+    if (ksplit < 1 || (ksplit > 1 && EPI != EPI_PARTIAL) || K / GM_BK < ksplit) return MQ_ERR_BAD_ARG;
+    dim3 grid(N / BN, (M + GM_BM * MT - 1) / (GM_BM * MT), ksplit);
     launch_pdl(k_gemm<BN, EPI, MT>, dim3(grid), dim3(GM_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
                                                              C, R, M, N, K, ldc, status);
     return (int)cudaGetLastError();
@@ -1134,6 +1147,7 @@ __global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restri
 
 using namespace mq;
 
+// kernels of one prefill (at most: the split-K path needs one norm kernel fewer per layer after the first)
 extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 8 + 2; }
 
 // C[M,N] = A[M,K] * B[N,K]^T on the tcgen05 path (bf16 in/out, fp32 accumulate);
@@ -1168,9 +1182,16 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
     launch_pdl(k_pf_embed, dim3(S), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status);
     int rc;
     const bool big = S >= 1024;
+    // Between 512 and 1024 rows the N = 1024 projections (O, down) split K over two CTAs per 128 x 128 tile:
+    // 64-wide tiles re-read the A operand sixteen times and are bound by L2 traffic.  The fp32 planes land in
+    // the qkv buffer (free after attention; 2 x S x 1024 floats fill it exactly) and one kernel adds them to the
+    // residual stream and applies the RMSNorm that follows (the next layer's input norm after the down projection).
+    const bool splitk = S >= 512 && S <= 1024;
+    float* part = reinterpret_cast<float*>(qkv);
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
-        launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, S);
+        if (l == 0 || !splitk)
+            launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, S);
         // q | k | v in one launch: 32 column tiles from three weight matrices
         // from 1024 rows on, 256-row tiles (two accumulators per CTA) still give 96-128 CTAs
         rc = S >= 2048 ? launch_gemm<256, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
@@ -1186,16 +1207,31 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
                                                                                           attn, S, pos0, l, model->max_seq_len, PackedTiles());
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
-        rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream)
-                         : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
-        if (rc) return rc;
-        launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, S);
+        if (splitk) {
+            rc = launch_gemm<128, EPI_PARTIAL>(attn, QSZ, (const bf16*)w.o_proj, nullptr, (bf16*)part, nullptr, S, H, QSZ, H, status, stream,
+                                               nullptr, 0, 0, 2);
+            if (rc) return rc;
+            launch_pdl(k_sk_resid_norm, dim3(S), dim3(256), 0, stream, (const float*)part, 2, S, h, (const bf16*)w.post_attn_layernorm, x);
+        } else {
+            rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream)
+                             : launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, S, H, QSZ, H, status, stream);
+            if (rc) return rc;
+            launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, S);
+        }
         rc = big ? launch_gemm<128, EPI_SWIGLU, 2>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream)
                  : launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
         if (rc) return rc;
-        rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream)
-                         : launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream);
-        if (rc) return rc;
+        if (splitk) {
+            rc = launch_gemm<128, EPI_PARTIAL>(act, I, (const bf16*)w.down_proj, nullptr, (bf16*)part, nullptr, S, H, I, H, status, stream,
+                                               nullptr, 0, 0, 2);
+            if (rc) return rc;
+            const bf16* next_norm = l + 1 < model->num_layers ? (const bf16*)model->layers[l + 1].input_layernorm : nullptr;
+            launch_pdl(k_sk_resid_norm, dim3(S), dim3(256), 0, stream, (const float*)part, 2, S, h, next_norm, x);
+        } else {
+            rc = (S <= 1024) ? launch_gemm<64, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream)
+                             : launch_gemm<128, EPI_RESID>(act, I, (const bf16*)w.down_proj, nullptr, h, h, S, H, I, H, status, stream);
+            if (rc) return rc;
+        }
     }
     // last row -> decode hidden buffer, then the decode path's LM head + arg-max
     launch_pdl(k_pf_copy_row, dim3(1), dim3(H / 8), 0, stream, h + (size_t)(S - 1) * H, (bf16*)dbuf->hidden);
