@@ -139,11 +139,9 @@ class MegakernelBatchDecoder:
         for ids in prompts:
             n = int(ids.numel())
             if n <= 0:
-                raise RuntimeError("prefill_step: empty input")
-            if n > self.max_prefill_len_:
-                raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
-            if n > self.max_seq_len_:
-                raise RuntimeError("prefill_step would exceed max_seq_len")
+                raise RuntimeError("Empty input sequence")
+            if n > self.max_prefill_len_ or n > self.max_seq_len_:
+                raise RuntimeError("Prefill sequence length exceeds maximum")
         cap = int(self._pf.max_tokens)
         if self.use_packed_prefill and len(prompts) > 1:
             with torch.cuda.device(self.device):
@@ -213,7 +211,7 @@ class MegakernelBatchDecoder:
                 self._graphs = {}
             ch = self._chain
             ch[0].copy_(first.to(self.device))
-            key = (num_steps, B)
+            key = (num_steps, B, self.use_splitk)     # the partials pointer is baked into the captured launches
             if use_graph:
                 g = self._graphs.get(key)
                 if g is None:

@@ -856,9 +856,15 @@ static size_t slot(int index, size_t need) {
 constexpr int ATT_MAX_CAP = 384;    // positions per CTA: 384 * 520 B + 3 KB of shared memory
 constexpr int ATT_MAX_SPLIT = 64;
 
+constexpr int ATT_ONE_WAVE_SPLIT = 18;   // 8 kv heads x 18 splits = 144 CTAs: the attention grid still fits one CTA per SM
+constexpr int ATT_ONE_WAVE_CAP = 144;    // positions per CTA whose K/V rows fit the smaller shared-memory slot
 static int attn_nsplit(int max_seq) {
     int ns = (max_seq + 127) / 128;
     if (ns < 1) ns = 1;
+    // a cache slightly longer than 18 x 128 positions keeps 18 splits with longer chunks rather
+    // than a grid of more CTAs than SMs
+    if (ns > ATT_ONE_WAVE_SPLIT && (((max_seq + ATT_ONE_WAVE_SPLIT - 1) / ATT_ONE_WAVE_SPLIT + 15) & ~15) <= ATT_ONE_WAVE_CAP)
+        ns = ATT_ONE_WAVE_SPLIT;
     if (ns > ATT_MAX_SPLIT) ns = ATT_MAX_SPLIT;
     return ns;
 }

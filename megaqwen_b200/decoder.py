@@ -99,8 +99,6 @@ class MegakernelDecoder:
             raw = bytes(self._layers)
             self._layers_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
             self._chain_scratch = torch.zeros(self._lib.mq_chain_scratch_bytes(), dtype=torch.uint8, device=dev)
-            # The persistent chain is opt-in: at present the PDL-chained kernels replayed
-            # from a CUDA graph are faster (see profiles/).
             self.persistent_available = self.max_seq_len_ <= self._lib.mq_chain_max_seq_len()
             self.use_persistent = False
             if self.persistent_available:
@@ -216,13 +214,14 @@ class MegakernelDecoder:
         tok = self._single(input_token_id, _ptr(self._logits))
         return tok, self._logits.clone()
 
-    def _chain(self, first_token, num_steps: int, use_graph: bool) -> torch.Tensor:
+    def _chain(self, first_token, num_steps: int, use_graph: bool, what: str = "decode_steps") -> torch.Tensor:
         """Device-resident chain token[i] -> token[i+1]; returns the view of the
         num_steps generated tokens (cuda int32).  No host synchronisation."""
         if num_steps <= 0:
             return torch.empty(0, dtype=torch.int32, device=self.device)
-        if self.position_ + num_steps > self.max_seq_len_:
-            raise RuntimeError("decode_steps would exceed max_seq_len")
+        # the reference's bound (bindings_prefill.cpp:1049-1051, 1092): the last cache row stays unused
+        if self.position_ + num_steps >= self.max_seq_len_:
+            raise RuntimeError(f"{what} would exceed max_seq_len")
         with torch.cuda.device(self.device):
             self._ensure_chain(num_steps)
             tk, ps = self._chain_tokens, self._chain_pos
@@ -251,7 +250,8 @@ class MegakernelDecoder:
             return tk[1:num_steps + 1]
 
     def _replay_graph(self, num_steps: int) -> None:
-        g = self._graphs.get(num_steps)
+        key = (num_steps, self.use_pdl)      # the PDL attribute is baked into the captured launches
+        g = self._graphs.get(key)
         tk, ps = self._chain_tokens, self._chain_pos
         if g is None:
             g = torch.cuda.CUDAGraph()
@@ -266,7 +266,7 @@ class MegakernelDecoder:
                         self._launch(_ptr(tk) + 4 * i, _ptr(tk) + 4 * (i + 1), _ptr(ps) + 4 * i, None, i > 0)
             torch.cuda.current_stream(self.device).wait_stream(s)
             self.launches = launches0
-            self._graphs[num_steps] = g
+            self._graphs[key] = g
         g.replay()
         self.launches += num_steps * (5 * self.num_layers_ + 1)
 
@@ -278,7 +278,7 @@ class MegakernelDecoder:
         decode_steps_cuda_graph, bindings_prefill.cpp:1082-1150)."""
         keep, self.use_persistent = self.use_persistent, False
         try:
-            return self._chain(first_token, num_steps, True).clone()
+            return self._chain(first_token, num_steps, True, "decode_steps_cuda_graph").clone()
         finally:
             self.use_persistent = keep
 
@@ -298,52 +298,79 @@ class MegakernelDecoder:
         self._check_status(int(host[-1]))
         return host[:-1]
 
-    def decode_greedy_cuda(self, first_token, max_new_tokens: int, eos_ids=None, chunk: int = 32):
+    def decode_greedy_cuda(self, first_token, max_new_tokens: int, eos_ids, chunk: int = 32):
         """Greedy loop with tokens kept on the device; the EOS scan and one 4-byte
-        read happen once per chunk (reference: bindings_prefill.cpp:1159-1349).
-        Returns (tokens cuda int32[len], len, stop_reason) with stop_reason 0 =
-        max_new_tokens reached, 1 = EOS found (the EOS token is not included)."""
-        eos = None
-        if eos_ids is not None and len(eos_ids) > 0:
-            eos = torch.as_tensor(eos_ids, dtype=torch.int32).to(self.device)
-        outs, total, cur = [], 0, first_token
+        read happen once per chunk.  Same contract as the reference
+        (bindings_prefill.cpp:1159-1349): the result holds the CONSUMED tokens,
+        i.e. per chunk ``[next_token] + generated[:-1]``, so ``out[0]`` is
+        ``first_token`` and the last token a chunk generated is carried into the
+        next chunk instead of being returned; EOS is searched in
+        ``generated[:-1]`` of each chunk and excluded from the result;
+        ``position()`` advances by whole chunks (the cache rows past an EOS were
+        computed and stay).  Returns (tokens cuda int32[len], len, stop_reason)
+        with stop_reason 0 = max_new_tokens, 1 = EOS."""
+        max_new = int(max_new_tokens)
+        if max_new <= 0:
+            return torch.empty(0, dtype=torch.int32, device=self.device), 0, 0
+        if chunk <= 0:
+            chunk = 32
+        if eos_ids is None or len(eos_ids) == 0:
+            raise RuntimeError("eos_ids must be a non-empty int32 tensor")
+        eos = torch.as_tensor(eos_ids).to(device=self.device, dtype=torch.int32).contiguous()
+        out = torch.empty(max_new, dtype=torch.int32, device=self.device)
         hit = torch.empty(1, dtype=torch.int32, device=self.device)
-        while total < max_new_tokens:
-            n = min(chunk, max_new_tokens - total, self.max_seq_len_ - self.position_)
-            if n <= 0:
-                break
-            toks = self._chain(cur, n, n == chunk).clone()
-            if eos is not None:
-                hit.fill_(n)
-                _lib.check(self._lib.mq_launch_find_first_eos(_ptr(toks), n, _ptr(eos), eos.numel(), _ptr(hit), self._stream()),
-                           "mq_launch_find_first_eos")
+        gen_len, stop_reason, cur = 0, 0, first_token
+        while gen_len < max_new:
+            steps = min(chunk, max_new - gen_len)
+            tail = self._chain(cur, steps, steps == chunk)          # view of tokens[1 .. steps]
+            tokens = self._chain_tokens                             # tokens[0] = consumed token of this chunk
+            out[gen_len:gen_len + steps].copy_(tokens[:steps])
+            stop_pos = -1
+            if steps > 1:
+                hit.fill_(steps - 1)
+                _lib.check(self._lib.mq_launch_find_first_eos(_ptr(tokens) + 4, steps - 1, _ptr(eos), eos.numel(), _ptr(hit),
+                                                              self._stream()), "mq_launch_find_first_eos")
                 self.launches += 1
                 idx = int(hit.item())
-                if idx < n:
-                    outs.append(toks[:idx])
-                    total += idx
-                    self.position_ -= n - (idx + 1)
-                    self.check_status()
-                    return torch.cat(outs), total, 1
-            outs.append(toks)
-            total += n
-            cur = toks[-1:]
+                if idx < steps - 1:
+                    stop_pos = idx + 1          # tokens kept from this chunk; the EOS itself is dropped
+            if stop_pos >= 0:
+                gen_len += stop_pos
+                stop_reason = 1
+                break
+            gen_len += steps
+            cur = tail[steps - 1:steps].clone()
         self.check_status()
-        res = torch.cat(outs) if outs else torch.empty(0, dtype=torch.int32, device=self.device)
-        return res, total, 0
+        return out[:gen_len], gen_len, stop_reason
+
+    def _check_prefill(self, ids: torch.Tensor, pos0: int) -> int:
+        """The reference's checks and texts (bindings_prefill.cpp:731-739); the ASR caller
+        matches on them (megaqwen/qwen3_asr_megakernel.py:767-773)."""
+        n = int(ids.numel())
+        if n > self.max_prefill_len_:
+            raise RuntimeError("Prefill sequence length exceeds maximum")
+        if n == 0:
+            raise RuntimeError("Empty input sequence")
+        if pos0 + n > self.max_seq_len_:
+            raise RuntimeError("Prefill sequence length exceeds maximum (max_seq_len)")
+        return n
 
     def prefill_step(self, input_ids) -> int:
+        """Full-sequence forward from position 0: afterwards ``position() == len(ids)``
+        and the returned token follows the prompt (bindings_prefill.cpp:731-833)."""
         ids = torch.as_tensor(input_ids, dtype=torch.int32).reshape(-1)
-        n = int(ids.numel())
-        if n <= 0:
-            raise RuntimeError("prefill_step: empty input")
-        if n > self.max_prefill_len_:
-            raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
-        if self.position_ + n > self.max_seq_len_:
-            raise RuntimeError("prefill_step would exceed max_seq_len")
+        self._check_prefill(ids, 0)
+        self.position_ = 0
         if self.use_gemm_prefill:
             return self._prefill_gemm(ids)
         return self._prefill_by_decode(ids)
+
+    def prefill_append(self, input_ids) -> int:
+        """Chunked prefill (no reference counterpart): the tokens continue the sequence at
+        ``position()`` and attend over everything cached so far."""
+        ids = torch.as_tensor(input_ids, dtype=torch.int32).reshape(-1)
+        self._check_prefill(ids, self.position_)
+        return self._prefill_gemm(ids)
 
     def _prefill_gemm(self, ids: torch.Tensor, want_logits: bool = False):
         """Full-sequence forward on the tcgen05 GEMM path (mq_launch_prefill)."""
@@ -372,16 +399,12 @@ class MegakernelDecoder:
             return tok, self._logits.clone()
         return tok
 
-    def prefill_step_logits(self, input_ids):
-        """prefill_step that also returns the fp32 logits of the last prompt position."""
+    def prefill_step_logits(self, input_ids, append: bool = False):
+        """prefill_step (or prefill_append) that also returns the fp32 logits of the last prompt position."""
         ids = torch.as_tensor(input_ids, dtype=torch.int32).reshape(-1)
-        n = int(ids.numel())
-        if n <= 0:
-            raise RuntimeError("prefill_step: empty input")
-        if n > self.max_prefill_len_:
-            raise RuntimeError(f"prefill length {n} exceeds max_prefill_len {self.max_prefill_len_}")
-        if self.position_ + n > self.max_seq_len_:
-            raise RuntimeError("prefill_step would exceed max_seq_len")
+        self._check_prefill(ids, self.position_ if append else 0)
+        if not append:
+            self.position_ = 0
         return self._prefill_gemm(ids, want_logits=True)
 
     def _prefill_by_decode(self, ids: torch.Tensor) -> int:

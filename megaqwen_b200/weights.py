@@ -25,9 +25,11 @@ _LAYER_KEYS = ["input_layernorm.weight", "self_attn.q_proj.weight", "self_attn.k
                "mlp.up_proj.weight", "mlp.down_proj.weight"]
 
 
-def load_tensors(model_dir: str, keys) -> dict:
+def load_tensors(model_dir: str, keys, optional=()) -> dict:
     """Read the named tensors from model.safetensors or from the shards listed in
-    model.safetensors.index.json."""
+    model.safetensors.index.json.  A key that the checkpoint does not hold raises
+    KeyError (reference: megaqwen/safetensors_loader.py:50-52) unless it is listed
+    in ``optional``."""
     from safetensors import safe_open
 
     single = os.path.join(model_dir, "model.safetensors")
@@ -39,6 +41,8 @@ def load_tensors(model_dir: str, keys) -> dict:
             for k in keys:
                 if k in names:
                     out[k] = f.get_tensor(k)
+                elif k not in optional:
+                    raise KeyError(f"Missing tensor key in safetensors: {k}")
         return out
     if not os.path.exists(index):
         raise FileNotFoundError(f"no model.safetensors or model.safetensors.index.json in {model_dir}")
@@ -48,6 +52,8 @@ def load_tensors(model_dir: str, keys) -> dict:
     for k in keys:
         if k in weight_map:
             by_file.setdefault(weight_map[k], []).append(k)
+        elif k not in optional:
+            raise KeyError(f"Missing tensor key in safetensors index: {k}")
     for fname, ks in by_file.items():
         with safe_open(os.path.join(model_dir, fname), framework="pt", device="cpu") as f:
             for k in ks:
@@ -85,7 +91,7 @@ def load_qwen3_weights(model_name="Qwen/Qwen3-0.6B", max_seq_len=2048, device="c
     keys = [prefix + "embed_tokens.weight", prefix + "norm.weight", "lm_head.weight"]
     for l in range(spec.num_layers):
         keys += [f"{prefix}layers.{l}.{k}" for k in _LAYER_KEYS]
-    t = load_tensors(model_name, keys)
+    t = load_tensors(model_name, keys, optional=("lm_head.weight",))
     embed = _bf16(t[prefix + "embed_tokens.weight"], device)
     lm_head = embed if "lm_head.weight" not in t or cfg.get("tie_word_embeddings", True) else _bf16(t["lm_head.weight"], device)
     layer_weights = [_bf16(t[f"{prefix}layers.{l}.{k}"], device) for l in range(spec.num_layers) for k in _LAYER_KEYS]

@@ -7,20 +7,22 @@ import torch
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 # Logit tolerances.  The stated target is max-abs 2e-2 per step against the
-# HuggingFace bf16 CPU model.  That model's own self-consistency is coarser than
-# this: feeding the same prompt in one forward or token by token changes its
-# logits by up to ~0.05 (mean ~0.007) on the 28-layer random-init model, because
-# bf16 re-rounding after every op amplifies fp32 summation-order differences
-# (bf16 spacing at |logit| in [2,4) is 0.0156).  The tests therefore assert:
-#   mean-abs  <= LOGIT_MEAN_TOL            (same scale as the oracle's self-noise)
-#   max-abs   <= LOGIT_MAX_TOL             (1.6x the oracle's worst self-noise)
+# HuggingFace bf16 CPU model.  That model's own self-consistency is coarser:
+# feeding the same prompt in one forward or token by token moves its logits by up
+# to 0.047 (mean 0.0070, 97.9 % within 2e-2, 98.4 % arg-max agreement) on the
+# 28-layer random-init model, because bf16 re-rounding after every op amplifies
+# fp32 summation-order differences (bf16 spacing at |logit| in [2,4) is 0.0156);
+# tests/test_hf_self_noise.py measures this on the CPU.  The GPU tests assert:
+#   max-abs   <= LOGIT_MAX_TOL   (largest value seen on the GPU, 0.0405, + 25 %;
+#                                 about the oracle's own worst case)
+#   mean-abs  <= LOGIT_MEAN_TOL  (the oracle's self-noise mean is 0.0070)
 #   fraction of logits within 2e-2 >= LOGIT_FRAC_2E2
 # and that every greedy token equals the oracle's unless the oracle's own
-# top-1/top-2 margin at that step is inside TIE_BAND.
+# top-1/top-2 margin at that step is inside TIE_BAND (two bf16 steps at |x| >= 4).
 LOGIT_TARGET = 2e-2
-LOGIT_MEAN_TOL = 1.2e-2
-LOGIT_MAX_TOL = 8e-2
-LOGIT_FRAC_2E2 = 0.93
+LOGIT_MEAN_TOL = 1.0e-2
+LOGIT_MAX_TOL = 5.1e-2
+LOGIT_FRAC_2E2 = 0.95
 TIE_BAND = 6.25e-2
 
 

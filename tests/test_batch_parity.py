@@ -118,7 +118,7 @@ def test_batch_errors(setup):
     bd.reset()
     with pytest.raises(RuntimeError, match="batch must be"):
         bd.prefill_batch([])
-    with pytest.raises(RuntimeError, match="empty input"):
+    with pytest.raises(RuntimeError, match="Empty input sequence"):
         bd.prefill_batch([torch.zeros(0, dtype=torch.int32)])
     bd.prefill_batch([random_prompt(QWEN3_TINY, 8, 1, 0)])
     with pytest.raises(RuntimeError, match="expected 1 tokens"):

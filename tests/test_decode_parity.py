@@ -170,8 +170,17 @@ def test_errors_and_status(tiny):
     dec.reset()
     with pytest.raises(RuntimeError, match="exceed max_seq_len"):
         dec.decode_steps(1, 5000)
-    with pytest.raises(RuntimeError, match="empty input"):
+    with pytest.raises(RuntimeError, match="Empty input sequence"):
         dec.prefill_step(torch.zeros(0, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="Prefill sequence length exceeds maximum"):
+        dec.prefill_step(torch.zeros(dec.max_prefill_len() + 1, dtype=torch.int32))
+    # the reference's bound: position + steps must stay below max_seq_len
+    with pytest.raises(RuntimeError, match="decode_steps would exceed max_seq_len"):
+        dec.decode_steps(1, 2304)
+    with pytest.raises(RuntimeError, match="decode_steps_cuda_graph would exceed max_seq_len"):
+        dec.decode_steps_cuda_graph(1, 2304)
+    with pytest.raises(RuntimeError, match="eos_ids must be a non-empty int32 tensor"):
+        dec.decode_greedy_cuda(1, 8, [])
     with pytest.raises(RuntimeError, match="token id outside"):
         dec.decode_step(10 ** 6)
     dec.reset()
@@ -185,20 +194,35 @@ def test_errors_and_status(tiny):
 
 
 def test_eos_scan_and_greedy_loop(tiny):
+    """decode_greedy_cuda keeps the reference's contract (bindings_prefill.cpp:1159-1349): the
+    CONSUMED tokens are returned, [first_token] + generated[:-1] per chunk; the EOS is searched in
+    generated[:-1], dropped from the result, and the position advances by whole chunks.  The
+    expected list is the formula of the reference's Python fallback loop
+    (megaqwen/qwen3_asr_megakernel.py:583-600)."""
     dec, _ = tiny
     prompt = random_prompt(QWEN3_TINY, 12, 8, 0).tolist()
-    dec.reset()
-    for t in prompt[:-1]:
-        dec.decode_step(t)
+
+    def feed_prompt():
+        dec.reset()
+        for t in prompt[:-1]:
+            dec.decode_step(t)
+
+    feed_prompt()
     full = dec.decode_steps(prompt[-1], 48).tolist()
-    eos = full[20]
-    first = full.index(eos)
-    dec.reset()
-    for t in prompt[:-1]:
-        dec.decode_step(t)
+    consumed = [prompt[-1]] + full
+    # an EOS whose first occurrence is not the last token a 16-step chunk generates (that one is
+    # carried into the next chunk as its consumed token, where the scan does not look)
+    first = next(full.index(full[k]) for k in range(17, 40) if full.index(full[k]) % 16 != 15)
+    eos = full[first]
+    feed_prompt()
     toks, n, reason = dec.decode_greedy_cuda(prompt[-1], 48, [eos], chunk=16)
-    assert reason == 1 and n == first and toks.tolist() == full[:first]
-    assert dec.position() == len(prompt) - 1 + first + 1
+    assert reason == 1 and n == first + 1 and toks.tolist() == consumed[:first + 1]
+    assert dec.position() == len(prompt) - 1 + 16 * (first // 16 + 1)
+    # no EOS in range: max_new_tokens consumed tokens, the last generated token withheld
+    feed_prompt()
+    toks, n, reason = dec.decode_greedy_cuda(prompt[-1], 20, torch.tensor([QWEN3_TINY.vocab_size + 5]), chunk=16)
+    assert reason == 0 and n == 20 and toks.tolist() == consumed[:20]
+    assert dec.position() == len(prompt) - 1 + 20
 
 
 @pytest.fixture(scope="module")

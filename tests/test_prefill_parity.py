@@ -86,7 +86,8 @@ def test_tiny_prefill_matches_hf_golden_and_decode_only_path(tiny):
     # chunked prefill (two calls) equals one call up to rounding
     dec.reset()
     dec.prefill_step(g["prompt"][:128])
-    tok2, lgc = dec.prefill_step_logits(g["prompt"][128:])
+    tok2, lgc = dec.prefill_step_logits(g["prompt"][128:], append=True)
+    assert dec.position() == int(g["prompt"].numel())
     r = logit_report(lgc.cpu(), lg.cpu())
     assert r["max"] <= 6e-2 and r["mean"] <= 8e-3, r
 
@@ -100,7 +101,7 @@ def full():
 def test_full_prefill_then_decode_matches_hf_golden(full, name):
     dec, _ = full
     g = load_golden(name)
-    n = min(len(g["tokens"]), 64)
+    n = len(g["tokens"])          # every recorded step: 32 for config 3, all 256 for config 2
     dec.reset()
     tok, lg = dec.prefill_step_logits(g["prompt"])
     rows = [lg.cpu()]
