@@ -33,7 +33,7 @@ from megaqwen_b200.synthetic import random_prompt, random_weights  # noqa: E402
 
 PROMPT_LEN = 2048
 NEW_TOKENS = 256
-MAX_SEQ = 2304
+MAX_SEQ = 2320            # position + steps must stay below max_seq_len (the reference's bound)
 METRIC = "decode_tokens_per_s_b1_ctx2048"
 WORKLOAD = "qwen3-0.6b random-init bf16, batch 1, 2048-token random prompt + 256 greedy decode steps"
 
@@ -52,7 +52,12 @@ class ClockSampler(threading.Thread):
 
     def __init__(self, index: int):
         super().__init__(daemon=True)
-        self.index = index
+        # nvidia-smi numbers GPUs physically; with CUDA_VISIBLE_DEVICES set the CUDA ordinal is
+        # another GPU, so the device is named by its UUID
+        try:
+            self.index = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+        except Exception:
+            self.index = str(index)
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop_evt = threading.Event()
 
@@ -83,8 +88,11 @@ class ClockSampler(threading.Thread):
 from megaqwen_b200.replicas import aggregate_throughput, barrier, dist_env, init_control_plane, max_over_ranks  # noqa: E402
 
 
-NCU_STEP_DRAM_BYTES = 1430.2e6     # measured, see run_ours
+# DRAM bytes of one decode step from a recorded ncu capture (dram__bytes_read.sum +
+# dram__bytes_write.sum) at the cache length below; NOT re-measured by this run.
+NCU_STEP_DRAM_BYTES = 1430.2e6
 NCU_STEP_CACHE_LEN = 2050
+NCU_CAPTURE = "per-phase kernels at commit a2e3ddb; the persistent kernel streams a repacked copy of the same bytes"
 
 
 def host_threads() -> int:

@@ -123,40 +123,48 @@ int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf,
                      const int* in_token, int* out_token, const int* position,
                      float* logits, int flags, void* stream);
 
-/* n_steps greedy decode steps in ONE persistent cooperative launch (one CTA per
- * SM): step i consumes the token produced by step i-1 (step 0: *first_token) at
- * position *position0 + i and writes its arg-max token to tokens_out[i].  The
- * device-resident equivalent of the reference's decode_steps_cuda /
- * decode_greedy_cuda chains (csrc/megakernel/bindings_prefill.cpp:1045-1349),
- * which launch one cooperative kernel plus two LM-head kernels per token.
- *   layers_dev  DEVICE copy of the num_layers MqLayerWeights entries
- *   scratch     mq_chain_scratch_bytes() bytes, 256-byte aligned, zeroed ONCE by
- *               the caller before the first call and never touched afterwards
- *               (it carries a phase counter from launch to launch)
- *   status      sticky MQ_STATUS_* word
- *   last_logits optional fp32 [vocab]: bf16-rounded logits of the LAST step
- * model->max_seq_len must not exceed mq_chain_max_seq_len().  Results are
- * identical to n_steps calls of mq_launch_decode. */
-int mq_launch_decode_chain(const MqModel* model, const MqLayerWeights* layers_dev,
-                           void* k_cache, void* v_cache, void* scratch, unsigned int* status,
-                           const int* first_token, const int* position0, int* tokens_out,
-                           int n_steps, float* last_logits, void* stream);
-size_t mq_chain_scratch_bytes(void);
-int mq_chain_max_seq_len(void);
-/* Instrumentation of mq_launch_decode_chain, the counterpart of the reference's
- * per-stage clock64 counters (csrc/megakernel/fused_decode_ldg_common.inl:24-69,
- * debug_ldg_decode_cycles in bindings_prefill.cpp:980-1043).  stage_cycles_dev:
- * NULL (off) or a device array of 16 u64 per CTA that thread 0 of every CTA fills
- * with SM cycles spent waiting for: [0] the hidden vector (QKV phase), [1] q|k|v
- * (attention), [2] attention output, [3] post-attention hidden, [4] MLP
- * activation, [5] weight pieces from the shared-memory ring; [6] the LM-head
- * phase; [7] the whole launch; and computing: [8] QKV rows, [9] attention,
- * [10] O rows, [11] gate/up rows, [12] down rows, [13] the input RMSNorm.  l2_prefetch_ahead: 0/1, whether the producer
- * prefetches the next layer's weight slices into L2 (default 1). */
-int mq_chain_set_debug(unsigned long long* stage_cycles_dev, int l2_prefetch_ahead);
-/* One-time set-up of the current device for mq_launch_decode_chain (done lazily
- * by the first launch otherwise). */
-int mq_chain_init_device(void);
+/* ---- Persistent decode: n_steps greedy steps in ONE cooperative launch (one CTA per SM).
+ * The device-resident equivalent of the reference's cooperative megakernel and of its
+ * decode_steps_cuda / decode_greedy_cuda chains (csrc/megakernel/fused_decode_ldg_kernel.inl:
+ * 43-258, bindings_prefill.cpp:1045-1349), which launch one cooperative kernel plus two LM-head
+ * kernels per token.  The weights are first repacked ONCE into per-CTA byte streams in
+ * consumption order (the reference repacks q|k|v and gate|up for its split backend in the same
+ * spirit, bindings_prefill.cpp:604-621); the HF-layout tensors remain the ones the constructor
+ * takes and the prefill reads.
+ *
+ *   mq_stream_packed_bytes   bytes of the packed copy for this model on the current device
+ *                            (0 if the device is unsupported)
+ *   mq_stream_pack           fills `packed` (256-byte aligned, device memory) from the model
+ *   mq_stream_scratch_bytes  bytes of `scratch`: 256-byte aligned, zeroed ONCE by the caller
+ *                            and never touched afterwards (it carries a phase counter from
+ *                            launch to launch)
+ *   mq_stream_max_context    largest position0 + n_steps a launch accepts (2304 on 148 SMs);
+ *                            longer contexts go through mq_launch_decode
+ *   mq_stream_grid           CTAs per launch (= SMs); mq_stream_stage_count stage slots each
+ *
+ * mq_launch_decode_stream: step i consumes forced_tokens[i] if forced_tokens != NULL, else the
+ * token produced by step i-1 (step 0: *first_token), at position *position0 + i, and writes
+ * its arg-max token to tokens_out[i].  logits: optional fp32, [n_steps][vocab] if logits_all
+ * else [vocab] of the last step (bf16-rounded values).  stage_cycles: optional device array
+ * u64 [grid][num_layers + 1][stages] to which thread 0 of every CTA ADDS the SM cycles it spent
+ * per layer in: 0 wait for the hidden vector, 1 RMSNorm + q|k|v rows, 2 wait for q|k|v,
+ * 3 attention, 4 split merge, 5 wait for the attention output, 6 Wo rows, 7 wait for the
+ * post-attention hidden vector, 8 RMSNorm + gate/up rows, 9 wait for the MLP activation,
+ * 10 Wd rows; in row [num_layers]: 11 wait for the last hidden vector, 12 LM head, 13 wait for
+ * the arg-max keys, 15 cycles spent waiting for weight pages (the counterpart of the
+ * reference's per-stage clock64 counters, fused_decode_ldg_common.inl:24-69).
+ * Results agree with n_steps calls of mq_launch_decode up to fp32 summation order. */
+size_t mq_stream_packed_bytes(const MqModel* model);
+int mq_stream_pack(const MqModel* model, void* packed, size_t packed_bytes, void* stream);
+size_t mq_stream_scratch_bytes(void);
+int mq_stream_max_context(void);
+int mq_stream_grid(void);
+int mq_stream_stage_count(void);
+int mq_launch_decode_stream(const MqModel* model, const void* packed, void* k_cache, void* v_cache,
+                            void* scratch, unsigned int* status, const int* first_token,
+                            const int* position0, const int* forced_tokens, int* tokens_out,
+                            int n_steps, float* logits, int logits_all,
+                            unsigned long long* stage_cycles, void* stream);
 
 /* The same decode step for callers that must not allocate device memory.
  * It has no counterpart in the reference.  Who needs it: a host process that
@@ -296,12 +304,6 @@ int mq_device_info(int* sm_count, int* cc_major, int* cc_minor);
  * explicitly before capturing launches into a CUDA graph.  Returns
  * MQ_ERR_UNSUPPORTED on anything but an sm_100 device. */
 int mq_init_device(void);
-
-/* Benchmark-only switches of mq_launch_decode (results become meaningless):
- * 1 skip the dot products, 2 skip the RMSNorms.  0 restores normal operation.  Used to attribute time per stage; only
- * available when the library is built with -DMQ_DECODE_EXPERIMENTS (otherwise
- * any non-zero value returns MQ_ERR_UNSUPPORTED). */
-int mq_decode_set_experiment(int flags);
 
 /* ABI version of this header. */
 int mq_abi_version(void);

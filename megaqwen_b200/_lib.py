@@ -54,7 +54,6 @@ class MqBatchBuffers(C.Structure):
 # name -> (restype, argtypes); every symbol include/megaqwen_b200.h declares.
 SIGNATURES = {
     "mq_abi_version": (C.c_int, []),
-    "mq_decode_set_experiment": (C.c_int, [C.c_int]),
     "mq_init_device": (C.c_int, []),
     "mq_device_info": (C.c_int, [C.POINTER(C.c_int)] * 3),
     "mq_decode_attn_nsplit": (C.c_int, [C.c_int]),
@@ -64,12 +63,15 @@ SIGNATURES = {
                                    C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "mq_launch_decode_noalloc": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
-    "mq_launch_decode_chain": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
-    "mq_chain_scratch_bytes": (C.c_size_t, []),
-    "mq_chain_max_seq_len": (C.c_int, []),
-    "mq_chain_init_device": (C.c_int, []),
-    "mq_chain_set_debug": (C.c_int, [C.c_void_p, C.c_int]),
+    "mq_stream_packed_bytes": (C.c_size_t, [C.POINTER(MqModel)]),
+    "mq_stream_pack": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "mq_stream_scratch_bytes": (C.c_size_t, []),
+    "mq_stream_max_context": (C.c_int, []),
+    "mq_stream_grid": (C.c_int, []),
+    "mq_stream_stage_count": (C.c_int, []),
+    "mq_launch_decode_stream": (C.c_int, [C.POINTER(MqModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                          C.c_void_p, C.c_void_p]),
     "mq_launch_prefill": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.POINTER(MqPrefillBuffers), C.c_void_p,
                                     C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "mq_launch_decode_batch": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers), C.c_void_p, C.c_void_p, C.c_void_p,

@@ -12,7 +12,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-SOURCES = ["decode.cu", "decode_chain.cu", "prefill.cu", "ops.cu"]
+SOURCES = ["decode.cu", "decode_stream.cu", "prefill.cu", "ops.cu"]
 OUT = os.environ.get("MQ_LIB_OUT") or os.path.join(PKG, "libmegaqwen_b200.so")
 
 

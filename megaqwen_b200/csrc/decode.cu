@@ -954,14 +954,14 @@ int mq::launch_lmhead_only(const MqModel* model, const MqDecodeBuffers* buf, int
     return (int)launch(k_lmhead, dim3(st->sm_count), dim3(LM_THREADS), smem_lmhead(), stream, false, a);
 }
 
-extern "C" int mq_decode_set_experiment(int flags) {
 #ifdef MQ_DECODE_EXPERIMENTS
+// Benchmark builds only (results become meaningless): 1 skip the dot products, 2 skip the
+// RMSNorms, 4 no weight copies.  Not part of the public header.
+extern "C" int mq_decode_set_experiment(int flags) {
     g_decode_exp_flags = flags;
     return MQ_OK;
-#else
-    return flags == 0 ? MQ_OK : MQ_ERR_UNSUPPORTED;
-#endif
 }
+#endif
 
 extern "C" int mq_abi_version(void) { return 1; }
 

@@ -1,0 +1,1249 @@
+// Persistent batch-1 greedy decode for sm_100a: ONE cooperative launch of one CTA per SM
+// runs n_steps decode steps (all layers, LM head, arg-max, next embedding).  It replaces the
+// reference's cooperative megakernel and its device-resident chains
+// (csrc/megakernel/fused_decode_ldg_kernel.inl:43-258, bindings_prefill.cpp:1045-1349).
+//
+// A decode step is HBM-bound (1.19 GB of bf16 weights per token) but is a chain of ~140
+// dependent phases, so the design separates the two:
+//
+//  * Weights never depend on activations.  At load time they are repacked into one
+//    contiguous byte stream per CTA, in exactly the order that CTA consumes them and already
+//    in the register layout of the mma.sync A operand (a "block" = 16 rows x 16 columns =
+//    512 bytes = 16 bytes per lane).  A producer thread per CTA copies its stream page by page
+//    (8 KB, one 1-D TMA bulk copy each, no multicast) into a ring of shared-memory slots and
+//    runs ahead of the consumers by the ring's size, across phase, layer and step boundaries.
+//    The LM head (tied embedding, tiled the same way) is the tail of every step's stream.
+//  * Activations are exchanged between CTAs through small global buffers of 32-bit words that
+//    hold a bf16 value in the high half and a 16-bit phase tag in the low half: a consumer
+//    re-reads its words until the tags match, so data and readiness arrive in one L2 round
+//    trip and there is no flag, fence, grid barrier or kernel boundary on the critical path
+//    (the reference: 225 grid.sync() per token).  fp32 split-KV partials and the arg-max keys
+//    travel as 64-bit words (tag32 | payload32).
+//  * Every GEMV is K-split over the CTA's eight consumer warps, accumulates with
+//    mma.sync.m16n8k16 (bf16 in, fp32 out; the activation vector replicated over the eight
+//    B columns) and is summed across warps in a fixed order: results are bit-reproducible.
+//
+// Work split (planned on the host for the device's SM count): the 4096 q|k|v rows, the 3072
+// gate/up row pairs and the 1024 rows of Wo / Wd are dealt out in groups of 8 rows so that every
+// CTA streams the same number of bytes per layer (13 x 16 KB on 148 SMs); a CTA owns the same
+// rows of Wo and Wd, which keeps the residual stream of those rows in a register.  Attention of
+// kv head g runs on CTAs g, g + 8, ..: one CTA up to 128 cached positions, up to 18 splits of
+// at most 128 positions beyond (context <= 2304), merged by the CTAs of splits 0 and 1.
+//
+// Rounding points are those of the HuggingFace bf16 model, as in decode.cu.  Every wait
+// (mbarrier or tag poll) is bounded; on expiry the sticky status bit is set, later waits give
+// up at once and the kernel drains.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <vector>
+
+#include "mq_device.cuh"
+
+namespace mq {
+
+constexpr int ST_WARPS = 8;                      // consumer warps
+constexpr int ST_CONSUMERS = ST_WARPS * 32;      // 256 threads
+constexpr int ST_THREADS = ST_CONSUMERS + 32;    // + the producer warp
+constexpr uint32_t ST_PAGE = 8192;               // bytes per ring slot
+constexpr int ST_NSLOT = 18;                     // ring slots: 144 KB in flight per SM
+constexpr int ST_KV_CAP = 128;                   // cached positions one CTA attends over
+constexpr int ST_KV_LD = D + 8;                  // K/V rows padded by 16 bytes (conflict-free ldmatrix)
+constexpr int ST_MAX_SPLIT = 18;                 // CTAs per kv head
+constexpr int ST_MAX_TILES = 7;                  // 16-row tiles per GEMV phase and CTA
+constexpr int ST_RED_ROWS = 16 * ST_MAX_TILES;
+constexpr int ST_MIN_GRID = 128;
+constexpr int ST_MAX_GRID = 256;
+constexpr int ST_PART = D + 2;                   // m, l, acc[128]
+constexpr int ST_STAGES = 16;                    // stage counters per (CTA, layer)
+constexpr uint32_t ST_LM_TILE_BYTES = 64 * 512;  // one 16-row tile of the LM head: 64 k-steps
+
+// Per-CTA plan, written by the host when the weights are packed.
+struct StPlan {
+    int a_row0, a_ng;          // rows of [Wq;Wk;Wv]: first row (multiple of 8) and number of 8-row groups
+    int od_row0, od_ng;        // rows of Wo and Wd
+    int gu_row0, gu_np;        // rows of Wg / Wu: first row and number of (8 gate + 8 up) tiles
+    int lm_row0, lm_nt;        // LM head: first vocabulary row and number of 16-row tiles
+    uint32_t off_a, off_o, off_gu, off_d;   // byte offsets of the four GEMV phases in a layer segment
+    uint32_t layer_bytes;      // bytes of one layer segment
+    uint32_t step_bytes;       // num_layers * layer_bytes + lm_nt * 32 KB
+    uint32_t step_pages;       // pages per step (the last one may be short)
+    uint32_t pad_;
+    unsigned long long stream_off;   // byte offset of this CTA's stream in the packed buffer
+    unsigned long long pad2_;
+};
+static_assert(sizeof(StPlan) == 80, "plan layout");
+
+// Scratch (caller-owned, zeroed once): tagged exchange vectors, split-KV partials, arg-max keys
+// and the phase counter that keeps tags unique from launch to launch.
+constexpr size_t SC_XH = 0;                                    // u32 [1024]
+constexpr size_t SC_XQKV = SC_XH + (size_t)H * 4;              // u32 [4096]
+constexpr size_t SC_XATTN = SC_XQKV + (size_t)QKV * 4;         // u32 [2048]
+constexpr size_t SC_XH1 = SC_XATTN + (size_t)QSZ * 4;          // u32 [1024]
+constexpr size_t SC_XACT = SC_XH1 + (size_t)H * 4;             // u32 [3072]
+constexpr size_t SC_XPART = SC_XACT + (size_t)I * 4;           // u64 [8][18][2][130]
+constexpr size_t SC_XLM = SC_XPART + (size_t)NKV * ST_MAX_SPLIT * 2 * ST_PART * 8;   // u64 [2 * ST_MAX_GRID]
+constexpr size_t SC_EPOCH = SC_XLM + (size_t)2 * ST_MAX_GRID * 8;                    // u32 [1]
+constexpr size_t SC_BYTES = SC_EPOCH + 256;
+
+struct StreamArgs {
+    const uint8_t* packed;          // header (plans, norm vectors) + per-CTA streams
+    const StPlan* plans;
+    const bf16* norms;              // [num_layers][input_ln 1024 | post_ln 1024 | q_norm 128 | k_norm 128]
+    const bf16* embed;
+    const bf16* final_norm;
+    const bf16* cos;
+    const bf16* sin;
+    bf16* k_cache;
+    bf16* v_cache;
+    uint8_t* scratch;
+    unsigned int* status;
+    const int* first_token;
+    const int* pos0;
+    const int* forced;              // optional [n_steps]: step i consumes forced[i] instead of the previous arg-max
+    int* tokens_out;                // [n_steps]
+    float* logits;                  // optional fp32: [n_steps][vocab] (logits_all) or [vocab] of the last step
+    unsigned long long* dbg;        // optional [grid][num_layers + 1][ST_STAGES] cycle counters
+    int num_layers;
+    int vocab;
+    int max_seq;
+    int n_steps;
+    int logits_all;
+    int max_split;                  // min(18, grid / 8)
+};
+
+constexpr int NORM_STRIDE = 2 * H + 2 * D;
+
+// ------------------------------------------------------------------ tagged exchange
+__device__ __forceinline__ uint4 ld_relaxed_v4(const uint32_t* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+// v must be exactly representable in bf16
+__device__ __forceinline__ void publish(uint32_t* dst, int idx, float v, uint32_t tag16) {
+    st_relaxed_u32(dst + idx, (__float_as_uint(v) & 0xffff0000u) | tag16);
+}
+__device__ __forceinline__ void publish_u32(unsigned long long* dst, size_t idx, uint32_t payload, uint32_t tag32) {
+    st_relaxed_u64(dst + idx, ((unsigned long long)tag32 << 32) | (unsigned long long)payload);
+}
+
+constexpr long long POLL_LIMIT_CYCLES = 400000000LL;   // about 0.2 s
+
+struct Poller {
+    unsigned int* status;
+    bool aborted;
+    __device__ __forceinline__ void refresh() { aborted = (ld_relaxed_u32(status) & MQ_STATUS_WAIT_TIMEOUT) != 0; }
+    __device__ __forceinline__ void expire() {
+        atomicOr(status, MQ_STATUS_WAIT_TIMEOUT);
+        aborted = true;
+    }
+    static __device__ __forceinline__ bool tags_ok(const uint4& u, uint32_t tag16) {
+        return ((u.x & 0xffffu) == tag16) & ((u.y & 0xffffu) == tag16) & ((u.z & 0xffffu) == tag16) & ((u.w & 0xffffu) == tag16);
+    }
+    // re-read four consecutive tagged words until all carry tag16 (or the kernel is draining)
+    __device__ __noinline__ uint4 spin4(const uint32_t* p, uint32_t tag16) {
+        uint4 v = ld_relaxed_v4(p);
+        if (aborted) return v;
+        const long long t0 = clock64();
+        int it = 0;
+        while (!tags_ok(v, tag16)) {
+            if ((++it & 63) == 0) {
+                refresh();
+                if (aborted) return v;
+                if (clock64() - t0 > POLL_LIMIT_CYCLES) { expire(); return v; }
+            }
+            v = ld_relaxed_v4(p);
+        }
+        return v;
+    }
+    __device__ __noinline__ uint32_t spin64(const unsigned long long* p, uint32_t tag32) {
+        unsigned long long v = ld_relaxed_u64(p);
+        if (aborted) return (uint32_t)v;
+        const long long t0 = clock64();
+        int it = 0;
+        while ((uint32_t)(v >> 32) != tag32) {
+            if ((++it & 63) == 0) {
+                refresh();
+                if (aborted) break;
+                if (clock64() - t0 > POLL_LIMIT_CYCLES) { expire(); break; }
+            }
+            v = ld_relaxed_u64(p);
+        }
+        return (uint32_t)v;
+    }
+    __device__ __forceinline__ uint4 words4(const uint32_t* p, uint32_t tag16) {
+        const uint4 v = ld_relaxed_v4(p);
+        return tags_ok(v, tag16) ? v : spin4(p, tag16);
+    }
+    __device__ __forceinline__ float f32(const unsigned long long* p, uint32_t tag32) {
+        const unsigned long long v = ld_relaxed_u64(p);
+        return __uint_as_float(((uint32_t)(v >> 32) == tag32) ? (uint32_t)v : spin64(p, tag32));
+    }
+};
+
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS) : "memory"); }
+
+__device__ __forceinline__ uint2 tagged_to_bf16x4(const uint4& v) {
+    uint2 o;
+    o.x = (v.x >> 16) | (v.y & 0xffff0000u);
+    o.y = (v.z >> 16) | (v.w & 0xffff0000u);
+    return o;
+}
+
+// Thread t of the 256 consumers gathers words 4 (t + 256 k) .. + 3, k < NCH, of a tagged vector
+// into shared memory as bf16.  All loads are issued before the first tag check.
+template <int NCH>
+__device__ __forceinline__ void poll_vector(Poller& po, const uint32_t* src, uint32_t tag16, bf16* dst, int tid) {
+    uint4 v[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) v[k] = ld_relaxed_v4(src + 4 * (tid + k * ST_CONSUMERS));
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+        if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + 4 * (tid + k * ST_CONSUMERS), tag16);
+        *reinterpret_cast<uint2*>(dst + 4 * (tid + k * ST_CONSUMERS)) = tagged_to_bf16x4(v[k]);
+    }
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t saddr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr));
+    return v;
+}
+
+// ------------------------------------------------------------------ ring cursor of one consumer warp
+// Every warp walks every page of the CTA's stream in order: it waits until the page is full,
+// uses the blocks that belong to it, and arrives on the page's "empty" barrier when it moves
+// on.  A slot is refilled once all eight warps have passed it.
+struct Ring {
+    uint32_t ring_addr;       // shared address of slot 0
+    uint64_t* full;
+    uint64_t* empty;
+    unsigned int* status;
+    uint32_t cur;             // first page this warp has not left yet (global page index)
+    uint32_t ready;           // page known to be full (cur or cur - 1 .. ), ~0 = none
+    unsigned long long wait_cycles;
+    bool timing;
+
+    __device__ __forceinline__ void wait_page(uint32_t pg) {
+        if (pg == ready) return;
+        uint64_t* bar = &full[pg % ST_NSLOT];
+        const uint32_t parity = (pg / ST_NSLOT) & 1u;
+        if (!mbar_try_wait(bar, parity)) {
+            const long long t0 = timing ? clock64() : 0;
+            mbar_wait(bar, parity, status);
+            if (timing) wait_cycles += (unsigned long long)(clock64() - t0);
+        }
+        ready = pg;
+    }
+    __device__ __forceinline__ void advance_to(uint32_t target, int lane) {
+        while (cur < target) {
+            wait_page(cur);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[cur % ST_NSLOT]);
+            ++cur;
+        }
+    }
+    // shared address of the block at byte `voff` of the step whose first page is base_page
+    __device__ __forceinline__ uint32_t block(uint32_t base_page, uint32_t voff, int lane) {
+        const uint32_t pg = base_page + voff / ST_PAGE;
+        advance_to(pg, lane);
+        wait_page(pg);
+        return ring_addr + (pg % ST_NSLOT) * ST_PAGE + (voff % ST_PAGE);
+    }
+};
+
+// ------------------------------------------------------------------ GEMV on the packed stream
+// One phase = `ntf` full tiles (16 rows) and `nh` (0/1) half tile (8 rows) over K = 128 * KSW
+// columns.  Stream layout: [k-step][tile] blocks of 512 bytes for the full tiles, then
+// [k-step] blocks of 256 bytes for the half tile.  Warp w takes k-steps w, w + 8, ..; lanes
+// 0, 4, .., 28 end with row l/4 in c[0] and row l/4 + 8 in c[2], written to red[warp][row].
+template <int KSW, int NT>
+__device__ __forceinline__ void gemv_full(Ring& rg, uint32_t base_page, uint32_t voff, const uint32_t (&xb)[KSW][2], int warp, int lane,
+                                          float* red) {
+    constexpr int NACC = NT == 1 ? 4 : (NT <= 3 ? 2 : 1);
+    float c[NT][NACC][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int q = 0; q < NACC; ++q) { c[t][q][0] = 0.f; c[t][q][1] = 0.f; c[t][q][2] = 0.f; c[t][q][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < KSW; ++j) {
+        const uint32_t ks = (uint32_t)(j * ST_WARPS + warp);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const uint32_t sa = rg.block(base_page, voff + (ks * NT + t) * 512u, lane);
+            const uint4 av = lds128(sa + lane * 16);
+            const uint32_t af[4] = {av.x, av.y, av.z, av.w};
+            mma16816(c[t][j % NACC], af, xb[j][0], xb[j][1]);
+        }
+    }
+    if ((lane & 3) == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            float lo = 0.f, hi = 0.f;
+#pragma unroll
+            for (int q = 0; q < NACC; ++q) { lo += c[t][q][0]; hi += c[t][q][2]; }
+            red[warp * ST_RED_ROWS + t * 16 + (lane >> 2)] = lo;
+            red[warp * ST_RED_ROWS + t * 16 + 8 + (lane >> 2)] = hi;
+        }
+    }
+}
+
+template <int KSW>
+__device__ __forceinline__ void gemv_half(Ring& rg, uint32_t base_page, uint32_t voff, const uint32_t (&xb)[KSW][2], int warp, int lane,
+                                          float* red, int row0) {
+    float c[4][4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
+#pragma unroll
+    for (int j = 0; j < KSW; ++j) {
+        const uint32_t ks = (uint32_t)(j * ST_WARPS + warp);
+        const uint32_t sa = rg.block(base_page, voff + ks * 256u, lane);
+        const uint2 av = lds64(sa + lane * 8);
+        const uint32_t af[4] = {av.x, 0u, av.y, 0u};
+        mma16816(c[j & 3], af, xb[j][0], xb[j][1]);
+    }
+    if ((lane & 3) == 0) red[warp * ST_RED_ROWS + row0 + (lane >> 2)] = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);
+}
+
+template <int KSW>
+__device__ __forceinline__ void gemv_phase(Ring& rg, uint32_t base_page, uint32_t voff, int ntf, int nh, const bf16* xs, float* red,
+                                           int warp, int lane) {
+    // this warp's slices of the activation vector as mma B fragments
+    uint32_t xb[KSW][2];
+    const uint32_t xa = smem_u32(xs) + (uint32_t)(lane & 3) * 4u;
+#pragma unroll
+    for (int j = 0; j < KSW; ++j) {
+        const uint32_t ks = (uint32_t)(j * ST_WARPS + warp);
+        xb[j][0] = lds32(xa + ks * 32u);
+        xb[j][1] = lds32(xa + ks * 32u + 16u);
+    }
+    constexpr uint32_t KS = KSW * ST_WARPS;
+    if (KSW == 8) {
+        switch (ntf) {
+            case 1: gemv_full<KSW, 1>(rg, base_page, voff, xb, warp, lane, red); break;
+            case 2: gemv_full<KSW, 2>(rg, base_page, voff, xb, warp, lane, red); break;
+            case 3: gemv_full<KSW, 3>(rg, base_page, voff, xb, warp, lane, red); break;
+            case 4: gemv_full<KSW, 4>(rg, base_page, voff, xb, warp, lane, red); break;
+            case 5: gemv_full<KSW, 5>(rg, base_page, voff, xb, warp, lane, red); break;
+            case 6: gemv_full<KSW, 6>(rg, base_page, voff, xb, warp, lane, red); break;
+            case 7: gemv_full<KSW, 7>(rg, base_page, voff, xb, warp, lane, red); break;
+            default: break;
+        }
+    } else if (ntf == 1) {
+        gemv_full<KSW, 1>(rg, base_page, voff, xb, warp, lane, red);
+    }
+    const uint32_t half_off = voff + KS * (uint32_t)ntf * 512u;
+    if (nh) gemv_half<KSW>(rg, base_page, half_off, xb, warp, lane, red, ntf * 16);
+    // leave every page that ends inside this phase, so that the producer can refill it while
+    // the CTA waits for the next activation vector
+    rg.advance_to(base_page + (half_off + (nh ? KS * 256u : 0u)) / ST_PAGE, lane);
+}
+
+// per-head RMSNorm + RoPE of a raw head held in shared memory (bf16[128]); lane owns elements
+// 2 lane, 2 lane + 1 of the first half and the same of the second half
+__device__ __forceinline__ void norm_rope_smem(const bf16* raw, const bf16* wn, const bf16* cosr, const bf16* sinr, int lane,
+                                               float (&lo)[2], float (&hi)[2]) {
+    const uint32_t ulo = *reinterpret_cast<const uint32_t*>(raw + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(raw + 64 + 2 * lane);
+    const float xl[2] = {bf_lo(ulo), bf_hi(ulo)}, xh[2] = {bf_lo(uhi), bf_hi(uhi)};
+    float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+    const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
+    const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
+    const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
+    const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
+    const float clo[2] = {bf_lo(cl), bf_hi(cl)}, chi[2] = {bf_lo(chh), bf_hi(chh)};
+    const float slo[2] = {bf_lo(sl), bf_hi(sl)}, shi[2] = {bf_lo(sh), bf_hi(sh)};
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const float nl = rbf(wlo[e] * rbf(xl[e] * r));
+        const float nh = rbf(whi[e] * rbf(xh[e] * r));
+        // x * cos + rotate_half(x) * sin, rotate_half = (-second half, first half)
+        lo[e] = rbf(rbf(nl * clo[e]) + rbf(-nh * slo[e]));
+        hi[e] = rbf(rbf(nh * chi[e]) + rbf(nl * shi[e]));
+    }
+}
+
+// How the cached positions of one kv head are dealt to its CTAs at a given context length.
+struct AttPlan {
+    int n_act, chunk, c0, n, n_cached;
+    bool active, is_last;
+};
+__device__ __forceinline__ AttPlan att_plan(int cta, int pos, int max_split) {
+    AttPlan p;
+    const int len = pos + 1;
+    if (len <= ST_KV_CAP) {
+        p.n_act = 1;
+        p.chunk = ST_KV_CAP;
+    } else {
+        const int want = min(max_split, (len + 63) / 64);
+        p.chunk = (((len + want - 1) / want) + 15) & ~15;
+        p.n_act = (len + p.chunk - 1) / p.chunk;
+    }
+    const int s = cta / NKV;
+    p.active = cta < NKV * max_split && s < p.n_act && p.chunk <= ST_KV_CAP;
+    p.c0 = s * p.chunk;
+    p.n = p.active ? min(len, p.c0 + p.chunk) - p.c0 : 0;
+    p.is_last = p.active && s == p.n_act - 1;
+    p.n_cached = p.is_last ? p.n - 1 : p.n;
+    return p;
+}
+
+__device__ __forceinline__ unsigned long long argmax_key64(float v, int idx) {
+    uint32_t u = __float_as_uint(v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (uint32_t)idx);
+}
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* ring = smem_raw;                                                    // [ST_NSLOT][ST_PAGE]
+    bf16* kt = reinterpret_cast<bf16*>(smem_raw + (size_t)ST_NSLOT * ST_PAGE);   // [ST_KV_CAP][ST_KV_LD]
+    bf16* vt = kt + (size_t)ST_KV_CAP * ST_KV_LD;
+    bf16* xs = vt + (size_t)ST_KV_CAP * ST_KV_LD;                                // [3072] activation vector of a GEMV phase
+    float* red = reinterpret_cast<float*>(xs + I);                               // [8][ST_RED_ROWS] per-warp partial sums
+    float* wacc = reinterpret_cast<float*>(xs);                                  // [8][2][128], attention only (over xs + red)
+    bf16* raw = reinterpret_cast<bf16*>(red + ST_WARPS * ST_RED_ROWS);           // [4][128] raw q(2g) | q(2g+1) | k | v
+    bf16* qs = raw + 4 * D;                                                      // [2][128] normalised, rotated query heads
+    bf16* ps = qs + 2 * D;                                                       // [8][32] probabilities of a warp's tile
+    bf16* cst = ps + ST_WARPS * 32;                                              // q_norm | k_norm | cos[pos] | sin[pos]
+    float* wm = reinterpret_cast<float*>(cst + 4 * D);                           // [8][2]
+    float* wl = wm + 16;                                                         // [8][2]
+    float* ml = wl + 16;                                                         // [2][2]
+    float* ssp = ml + 4;                                                         // [8] partial sums of squares
+    unsigned long long* wbest = reinterpret_cast<unsigned long long*>(ssp + 8 + 4);   // [8] (8-byte aligned: 44 floats before it)
+    uint64_t* full = reinterpret_cast<uint64_t*>(wbest + ST_WARPS);
+    uint64_t* empty = full + ST_NSLOT;
+    int* s_token = reinterpret_cast<int*>(empty + ST_NSLOT);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cta = blockIdx.x, grid = gridDim.x;
+    const int L = a.num_layers;
+    const StPlan pl = a.plans[cta];
+
+    if (tid == 0) {
+        for (int i = 0; i < ST_NSLOT; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], ST_WARPS); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    uint32_t* xh = reinterpret_cast<uint32_t*>(a.scratch + SC_XH);
+    uint32_t* xqkv = reinterpret_cast<uint32_t*>(a.scratch + SC_XQKV);
+    uint32_t* xattn = reinterpret_cast<uint32_t*>(a.scratch + SC_XATTN);
+    uint32_t* xh1 = reinterpret_cast<uint32_t*>(a.scratch + SC_XH1);
+    uint32_t* xact = reinterpret_cast<uint32_t*>(a.scratch + SC_XACT);
+    unsigned long long* xpart = reinterpret_cast<unsigned long long*>(a.scratch + SC_XPART);
+    unsigned long long* xlm = reinterpret_cast<unsigned long long*>(a.scratch + SC_XLM);
+    uint32_t* epoch = reinterpret_cast<uint32_t*>(a.scratch + SC_EPOCH);
+
+    const uint32_t epoch0 = ld_relaxed_u32(epoch);
+    const int pos0 = ld_cg_i32(a.pos0);
+    // every CTA takes the same decision: nothing is launched half-way
+    if (pos0 < 0 || pos0 + a.n_steps > a.max_seq || pos0 + a.n_steps > a.max_split * ST_KV_CAP) {
+        if (cta == 0 && tid == 0) atomicOr(a.status, MQ_STATUS_BAD_POSITION);
+        return;
+    }
+
+    if (warp == ST_WARPS) {
+        // ============================================================ producer
+        if (lane == 0) {
+            const uint8_t* src = a.packed + pl.stream_off;
+            uint32_t gp = 0;
+            bool dead = false;
+            for (int step = 0; step < a.n_steps && !dead; ++step) {
+                for (uint32_t p = 0; p < pl.step_pages; ++p, ++gp) {
+                    const uint32_t slot = gp % ST_NSLOT, fill = gp / ST_NSLOT;
+                    if (fill > 0 && !mbar_wait(&empty[slot], (fill - 1) & 1u, a.status)) { dead = true; break; }
+                    const uint32_t bytes = min(ST_PAGE, pl.step_bytes - p * ST_PAGE);
+                    mbar_expect_tx(&full[slot], bytes);
+                    bulk_g2s(ring + (size_t)slot * ST_PAGE, src + (size_t)p * ST_PAGE, bytes, &full[slot]);
+                }
+            }
+            if (dead) {
+                // the kernel is draining: let the copies still in flight land before the CTA's
+                // shared memory is given back
+                const uint32_t first = gp > (uint32_t)ST_NSLOT ? gp - ST_NSLOT : 0u;
+                for (uint32_t q = first; q < gp; ++q) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(&full[q % ST_NSLOT], (q / ST_NSLOT) & 1u) && clock64() - t0 < 2000000) { }
+                }
+            }
+        }
+        return;
+    }
+
+    // ============================================================== consumers
+    Poller po{a.status, false};
+    po.refresh();
+    const bool timing = a.dbg != nullptr && tid == 0;
+    Ring rg{smem_u32(ring), full, empty, a.status, 0u, 0xffffffffu, 0ull, timing};
+    unsigned long long* dbg = a.dbg ? a.dbg + (size_t)cta * (L + 1) * ST_STAGES : nullptr;
+#define ST_T0() long long t0_ = timing ? clock64() : 0
+#define ST_T1(layer, stage)                                                         \
+    do {                                                                            \
+        if (timing) {                                                               \
+            const long long t1_ = clock64();                                        \
+            dbg[(size_t)(layer) * ST_STAGES + (stage)] += (unsigned long long)(t1_ - t0_); \
+            t0_ = t1_;                                                              \
+        }                                                                           \
+    } while (0)
+
+    auto tag32_of = [&](int step, int layer) { return epoch0 + (uint32_t)(step * (L + 1) + layer) + 1u; };
+    auto tag16_of = [&](int step, int layer) { return ((epoch0 + (uint32_t)(step * (L + 1) + layer)) % 65535u) + 1u; };
+
+    const int g = cta % NKV, s_idx = cta / NKV;     // attention item of this CTA
+    const int n_od = 8 * pl.od_ng, n_a = 8 * pl.a_ng, n_gu = 8 * pl.gu_np;
+
+    // K/V rows [c0, c0 + n_cached) of layer l -> padded shared-memory rows, 16 bytes per copy
+    auto kv_prefetch = [&](int layer, const AttPlan& ap) {
+        if (ap.active && ap.n_cached > 0) {
+            const size_t head_off = ((size_t)(layer * NKV + g) * a.max_seq + ap.c0) * D;
+            const bf16* ksrc = a.k_cache + head_off;
+            const bf16* vsrc = a.v_cache + head_off;
+            for (int i = tid; i < ap.n_cached * 16; i += ST_CONSUMERS) {
+                const int r = i >> 4, c = i & 15;
+                cp_async16(kt + (size_t)r * ST_KV_LD + c * 8, ksrc + (size_t)r * D + c * 8);
+                cp_async16(vt + (size_t)r * ST_KV_LD + c * 8, vsrc + (size_t)r * D + c * 8);
+            }
+        }
+        cp_async_commit();
+    };
+
+    int token = a.forced ? ld_cg_i32(a.forced) : ld_cg_i32(a.first_token);
+    kv_prefetch(0, att_plan(cta, pos0, a.max_split));
+
+    for (int step = 0; step < a.n_steps; ++step) {
+        const int pos = pos0 + step;
+        const AttPlan ap = att_plan(cta, pos, a.max_split);
+        const uint32_t base_page = (uint32_t)step * pl.step_pages;
+        if (cta == 0 && tid == 0 && (token < 0 || token >= a.vocab)) atomicOr(a.status, MQ_STATUS_BAD_TOKEN);
+        token = min(max(token, 0), a.vocab - 1);
+        const bf16* erow = a.embed + (size_t)token * H;
+        float resid = 0.f;                               // residual stream of row od_row0 + tid (tid < n_od)
+        if (tid < n_od) resid = bf2f(erow[pl.od_row0 + tid]);
+
+        for (int l = 0; l < L; ++l) {
+            const uint32_t t16 = tag16_of(step, l), t32 = tag32_of(step, l);
+            const bf16* nrm = a.norms + (size_t)l * NORM_STRIDE;
+            const uint32_t lbase = (uint32_t)l * pl.layer_bytes;
+            ST_T0();
+
+            // ---------------- phase A: RMSNorm + rows of [Wq;Wk;Wv]
+            if (n_a > 0) {
+                const uint2 wv = __ldg(reinterpret_cast<const uint2*>(nrm + 4 * tid));      // input_layernorm
+                float v0, v1, v2, v3;
+                if (l == 0) {
+                    const uint2 u = __ldg(reinterpret_cast<const uint2*>(erow + 4 * tid));
+                    v0 = bf_lo(u.x); v1 = bf_hi(u.x); v2 = bf_lo(u.y); v3 = bf_hi(u.y);
+                } else {
+                    const uint4 u = po.words4(xh + 4 * tid, tag16_of(step, l - 1));
+                    v0 = bf_hi(u.x); v1 = bf_hi(u.y); v2 = bf_hi(u.z); v3 = bf_hi(u.w);
+                }
+                ST_T1(l, 0);
+                const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
+                if (lane == 0) ssp[warp] = part;
+                consumer_bar();
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < ST_WARPS; ++i) ss += ssp[i];
+                const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+                uint2 o;
+                o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
+                o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
+                *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                consumer_bar();
+                gemv_phase<8>(rg, base_page, lbase + pl.off_a, pl.a_ng >> 1, pl.a_ng & 1, xs, red, warp, lane);
+                consumer_bar();
+                if (tid < n_a) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ST_WARPS; ++w) s += red[w * ST_RED_ROWS + tid];
+                    publish(xqkv, pl.a_row0 + tid, rbf(s), t16);
+                }
+                ST_T1(l, 1);
+            }
+
+            // ---------------- phase B: attention item (g, split) of this CTA
+            if (ap.active) {
+                const int n = ap.n;
+                const size_t head_off = ((size_t)(l * NKV + g) * a.max_seq) * D;
+                // q_norm | k_norm | cos[pos] | sin[pos] do not depend on the hop: fetch them first
+                if (tid >= 128 && tid < 192) {
+                    const int v = (tid - 128) >> 4, c = tid & 15;
+                    const bf16* src = v == 0 ? nrm + 2 * H : v == 1 ? nrm + 2 * H + D
+                                    : v == 2 ? a.cos + (size_t)pos * D : a.sin + (size_t)pos * D;
+                    *reinterpret_cast<uint4*>(cst + v * D + c * 8) = __ldg(reinterpret_cast<const uint4*>(src + c * 8));
+                }
+                // raw q(2g), q(2g+1) for every split; k(g), v(g) for the split that owns the new position
+                if (tid < 64) {
+                    const uint4 v = po.words4(xqkv + 2 * g * D + 4 * tid, t16);
+                    *reinterpret_cast<uint2*>(raw + 4 * tid) = tagged_to_bf16x4(v);
+                } else if (tid < 128 && ap.is_last) {
+                    const int c = tid - 64;                                   // 0..31 k, 32..63 v
+                    const int base = c < 32 ? QSZ + g * D + 4 * c : QSZ + KVSZ + g * D + 4 * (c - 32);
+                    const uint4 v = po.words4(xqkv + base, t16);
+                    *reinterpret_cast<uint2*>(raw + 2 * D + 4 * c) = tagged_to_bf16x4(v);
+                }
+                ST_T1(l, 2);
+                cp_async_wait_all();
+                consumer_bar();
+                if (warp < 2) {
+                    float lo[2], hi[2];
+                    norm_rope_smem(raw + warp * D, cst, cst + 2 * D, cst + 3 * D, lane, lo, hi);
+                    *reinterpret_cast<uint32_t*>(qs + warp * D + 2 * lane) = pack_bf16x2(lo[0], lo[1]);
+                    *reinterpret_cast<uint32_t*>(qs + warp * D + 64 + 2 * lane) = pack_bf16x2(hi[0], hi[1]);
+                } else if (warp == 2 && ap.is_last) {
+                    float lo[2], hi[2];
+                    norm_rope_smem(raw + 2 * D, cst + D, cst + 2 * D, cst + 3 * D, lane, lo, hi);
+                    const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
+                    bf16* krow = kt + (size_t)(n - 1) * ST_KV_LD;
+                    *reinterpret_cast<uint32_t*>(krow + 2 * lane) = plo;
+                    *reinterpret_cast<uint32_t*>(krow + 64 + 2 * lane) = phi;
+                    bf16* gk = a.k_cache + head_off + (size_t)pos * D;
+                    *reinterpret_cast<uint32_t*>(gk + 2 * lane) = plo;
+                    *reinterpret_cast<uint32_t*>(gk + 64 + 2 * lane) = phi;
+                } else if (warp == 3 && ap.is_last) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(raw + 3 * D + 4 * lane);
+                    *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * ST_KV_LD + 4 * lane) = u;
+                    *reinterpret_cast<uint2*>(a.v_cache + head_off + (size_t)pos * D + 4 * lane) = u;
+                } else if (warp >= 4) {
+                    // rows between n and the end of the last 16-position tile are multiplied by p = 0
+                    const int n16 = (n + 15) & ~15;
+                    for (int i = (warp - 4) * 32 + lane; i < (n16 - n) * 16; i += 128)
+                        *reinterpret_cast<uint4*>(vt + (size_t)(n + (i >> 4)) * ST_KV_LD + (i & 15) * 8) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                consumer_bar();
+                // a warp takes 16-position tiles warp, warp + 8, ..: scores = K_tile . q on the tensor
+                // cores (positions are the M dimension, the two heads two of the eight N columns),
+                // softmax of the tile, probabilities to bf16, out += P . V_tile
+                {
+                    const int gi = lane >> 2, ti = lane & 3;
+                    const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+                    float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+                    float o[16][4];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
+                    const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
+                    bf16* pw = ps + warp * 32;
+                    for (int tile = warp; tile * 16 < n; tile += ST_WARPS) {
+                        const uint32_t rowoff = (uint32_t)(((tile * 16 + (lane & 15)) * ST_KV_LD + (lane >> 4) * 8) * 2);
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int ks = 0; ks < D / 16; ++ks) {
+                            uint32_t af[4];
+                            ldsm4(af, smem_u32(kt) + rowoff + ks * 32);
+                            uint32_t b0 = lds32(qaddr + ks * 32), b1 = lds32(qaddr + ks * 32 + 16);
+                            if (gi >= 2) { b0 = 0u; b1 = 0u; }
+                            mma16816(c, af, b0, b1);
+                        }
+                        const int p_lo = tile * 16 + gi, p_hi = p_lo + 8;
+                        const bool own = ti == 0;
+                        const float s00 = (own && p_lo < n) ? c[0] * scale : -1e30f, s01 = (own && p_lo < n) ? c[1] * scale : -1e30f;
+                        const float s10 = (own && p_hi < n) ? c[2] * scale : -1e30f, s11 = (own && p_hi < n) ? c[3] * scale : -1e30f;
+                        float t0 = fmaxf(s00, s10), t1 = fmaxf(s01, s11);
+#pragma unroll
+                        for (int off = 4; off < 32; off <<= 1) {
+                            t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, off));
+                            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, off));
+                        }
+                        t0 = __shfl_sync(0xffffffffu, t0, 0);
+                        t1 = __shfl_sync(0xffffffffu, t1, 0);
+                        const float mn0 = fmaxf(m0, t0), mn1 = fmaxf(m1, t1);
+                        const float cr0 = expf(m0 - mn0), cr1 = expf(m1 - mn1);
+                        m0 = mn0; m1 = mn1;
+                        const float e00 = (own && p_lo < n) ? expf(s00 - m0) : 0.f, e01 = (own && p_lo < n) ? expf(s01 - m1) : 0.f;
+                        const float e10 = (own && p_hi < n) ? expf(s10 - m0) : 0.f, e11 = (own && p_hi < n) ? expf(s11 - m1) : 0.f;
+                        float u0 = e00 + e10, u1 = e01 + e11;
+#pragma unroll
+                        for (int off = 4; off < 32; off <<= 1) {
+                            u0 += __shfl_xor_sync(0xffffffffu, u0, off);
+                            u1 += __shfl_xor_sync(0xffffffffu, u1, off);
+                        }
+                        l0 = l0 * cr0 + __shfl_sync(0xffffffffu, u0, 0);
+                        l1 = l1 * cr1 + __shfl_sync(0xffffffffu, u1, 0);
+                        if (own) {
+                            pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
+                            pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+                        }
+                        __syncwarp();
+                        uint32_t pa[4] = {0u, 0u, 0u, 0u};      // A = P: row gi is head gi (rows 2..15 are zero)
+                        if (gi < 2) {
+                            pa[0] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 2 * ti);
+                            pa[2] = *reinterpret_cast<const uint32_t*>(pw + gi * 16 + 8 + 2 * ti);
+                        }
+                        const float crg = gi == 0 ? cr0 : cr1;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            uint32_t bv[4];
+                            ldsm4_t(bv, smem_u32(vt) + rowoff + j * 32);
+                            o[2 * j][0] *= crg; o[2 * j][1] *= crg; o[2 * j + 1][0] *= crg; o[2 * j + 1][1] *= crg;
+                            mma16816(o[2 * j], pa, bv[0], bv[1]);
+                            mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
+                        }
+                        __syncwarp();
+                    }
+                    if (lane == 0) { wm[warp * 2] = m0; wm[warp * 2 + 1] = m1; wl[warp * 2] = l0; wl[warp * 2 + 1] = l1; }
+                    if (gi < 2) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            *reinterpret_cast<float2*>(wacc + (warp * 2 + gi) * D + j * 8 + 2 * ti) = make_float2(o[j][0], o[j][1]);
+                    }
+                }
+                consumer_bar();
+                const int hh = tid >> 7, d = tid & 127;
+                float acc = 0.f;
+                {
+                    float M = -1e30f;
+#pragma unroll
+                    for (int w8 = 0; w8 < ST_WARPS; ++w8) M = fmaxf(M, wm[w8 * 2 + hh]);
+                    float lsum = 0.f;
+#pragma unroll
+                    for (int w8 = 0; w8 < ST_WARPS; ++w8) {
+                        const float f = expf(wm[w8 * 2 + hh] - M);
+                        lsum = fmaf(wl[w8 * 2 + hh], f, lsum);
+                        acc = fmaf(wacc[(w8 * 2 + hh) * D + d], f, acc);
+                    }
+                    if (d == 0) { ml[hh * 2] = M; ml[hh * 2 + 1] = lsum; }
+                }
+                consumer_bar();        // (M, l) published; every read of kt / vt / wacc of this layer is done
+                const int qhead = 2 * g + hh;
+                if (ap.n_act == 1) {
+                    publish(xattn, qhead * D + d, rbf(acc / ml[hh * 2 + 1]), t16);
+                    ST_T1(l, 3);
+                } else {
+                    // split-KV: publish the partial; the CTAs of splits 0 and 1 merge head 0 and head 1
+                    const size_t pbase = (((size_t)g * ST_MAX_SPLIT + s_idx) * 2 + hh) * ST_PART;
+                    publish_u32(xpart, pbase + 2 + d, __float_as_uint(acc), t32);
+                    if (d == 0) {
+                        publish_u32(xpart, pbase, __float_as_uint(ml[hh * 2]), t32);
+                        publish_u32(xpart, pbase + 1, __float_as_uint(ml[hh * 2 + 1]), t32);
+                    }
+                    ST_T1(l, 3);
+                    if (s_idx < 2 && tid < D) {
+                        const int mh = s_idx;                             // the head this CTA merges
+                        const unsigned long long* hb = xpart + ((size_t)g * ST_MAX_SPLIT * 2 + mh) * ST_PART;
+                        constexpr size_t SPLIT_STRIDE = 2 * ST_PART;
+                        // (m, l) of split `lane` (n_act <= 18 < 32): one round trip for the warp
+                        float mj = -INFINITY, lj = 0.f;
+                        if (lane < ap.n_act) {
+                            mj = po.f32(hb + (size_t)lane * SPLIT_STRIDE, t32);
+                            lj = po.f32(hb + (size_t)lane * SPLIT_STRIDE + 1, t32);
+                        }
+                        const float M = warp_max(mj);
+                        const float fj = (lane < ap.n_act) ? expf(mj - M) : 0.f;
+                        const float den = warp_sum(lj * fj);
+                        // acc[d] of every split: all loads are issued before the first tag check
+                        unsigned long long rawv[ST_MAX_SPLIT];
+#pragma unroll
+                        for (int j = 0; j < ST_MAX_SPLIT; ++j)
+                            if (j < ap.n_act) rawv[j] = ld_relaxed_u64(hb + (size_t)j * SPLIT_STRIDE + 2 + tid);
+                        float num = 0.f;
+#pragma unroll
+                        for (int j = 0; j < ST_MAX_SPLIT; ++j) {
+                            const float f = __shfl_sync(0xffffffffu, fj, j);
+                            if (j < ap.n_act) {
+                                float v = __uint_as_float((uint32_t)rawv[j]);
+                                if ((uint32_t)(rawv[j] >> 32) != t32) v = po.f32(hb + (size_t)j * SPLIT_STRIDE + 2 + tid, t32);
+                                num = fmaf(v, f, num);
+                            }
+                        }
+                        publish(xattn, (2 * g + mh) * D + tid, rbf(num / den), t16);
+                    }
+                    ST_T1(l, 4);
+                }
+                if (ap.is_last) __threadfence();   // the new K/V rows are read by other CTAs in later steps
+            }
+            // K/V rows of the next attention phase (their positions were written by earlier steps)
+            if (l + 1 < L) kv_prefetch(l + 1, ap);
+            else if (step + 1 < a.n_steps) kv_prefetch(0, att_plan(cta, pos + 1, a.max_split));
+
+            // ---------------- phase C: rows of Wo + residual
+            if (n_od > 0) {
+                poll_vector<2>(po, xattn, t16, xs, tid);
+                ST_T1(l, 5);
+                consumer_bar();
+                gemv_phase<16>(rg, base_page, lbase + pl.off_o, pl.od_ng >> 1, pl.od_ng & 1, xs, red, warp, lane);
+                consumer_bar();
+                if (tid < n_od) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ST_WARPS; ++w) s += red[w * ST_RED_ROWS + tid];
+                    resid = rbf(resid + rbf(s));
+                    publish(xh1, pl.od_row0 + tid, resid, t16);
+                }
+                ST_T1(l, 6);
+            }
+
+            // ---------------- phase D: RMSNorm + gate / up rows + SiLU * up
+            if (n_gu > 0) {
+                const uint2 wv = __ldg(reinterpret_cast<const uint2*>(nrm + H + 4 * tid));   // post_attention_layernorm
+                const uint4 u = po.words4(xh1 + 4 * tid, t16);
+                const float v0 = bf_hi(u.x), v1 = bf_hi(u.y), v2 = bf_hi(u.z), v3 = bf_hi(u.w);
+                ST_T1(l, 7);
+                const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
+                if (lane == 0) ssp[warp] = part;
+                consumer_bar();
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < ST_WARPS; ++i) ss += ssp[i];
+                const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+                uint2 o;
+                o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
+                o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
+                *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                consumer_bar();
+                gemv_phase<8>(rg, base_page, lbase + pl.off_gu, pl.gu_np, 0, xs, red, warp, lane);
+                consumer_bar();
+                if (tid < n_gu) {
+                    const int t = tid >> 3, i = tid & 7;
+                    float gs = 0.f, us = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ST_WARPS; ++w) {
+                        gs += red[w * ST_RED_ROWS + t * 16 + i];
+                        us += red[w * ST_RED_ROWS + t * 16 + 8 + i];
+                    }
+                    const float act = rbf(silu_f32(rbf(gs)));
+                    publish(xact, pl.gu_row0 + tid, rbf(act * rbf(us)), t16);
+                }
+                ST_T1(l, 8);
+            }
+
+            // ---------------- phase E: rows of Wd + residual
+            if (n_od > 0) {
+                poll_vector<3>(po, xact, t16, xs, tid);
+                ST_T1(l, 9);
+                consumer_bar();
+                gemv_phase<24>(rg, base_page, lbase + pl.off_d, pl.od_ng >> 1, pl.od_ng & 1, xs, red, warp, lane);
+                consumer_bar();
+                if (tid < n_od) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int w = 0; w < ST_WARPS; ++w) s += red[w * ST_RED_ROWS + tid];
+                    resid = rbf(resid + rbf(s));
+                    publish(xh, pl.od_row0 + tid, resid, t16);
+                }
+                ST_T1(l, 10);
+            }
+        }
+
+        // ---------------- final RMSNorm + LM head tiles + arg-max
+        {
+            ST_T0();
+            const uint32_t t32 = tag32_of(step, L);
+            const uint2 wv = __ldg(reinterpret_cast<const uint2*>(a.final_norm + 4 * tid));
+            const uint4 u = po.words4(xh + 4 * tid, tag16_of(step, L - 1));
+            const float v0 = bf_hi(u.x), v1 = bf_hi(u.y), v2 = bf_hi(u.z), v3 = bf_hi(u.w);
+            ST_T1(L, 11);
+            const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
+            if (lane == 0) ssp[warp] = part;
+            consumer_bar();
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < ST_WARPS; ++i) ss += ssp[i];
+            const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+            uint2 o;
+            o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
+            o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
+            *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+            consumer_bar();
+
+            float* lg = nullptr;
+            if (a.logits && (a.logits_all || step == a.n_steps - 1)) lg = a.logits + (a.logits_all ? (size_t)step * a.vocab : 0);
+            const uint32_t lm_off = (uint32_t)L * pl.layer_bytes;
+            const uint32_t xa = smem_u32(xs) + (uint32_t)(lane & 3) * 4u;
+            unsigned long long best = 0ull;
+            for (int j = warp; j < pl.lm_nt; j += ST_WARPS) {
+                float c[4][4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
+                const uint32_t toff = lm_off + (uint32_t)j * ST_LM_TILE_BYTES;
+#pragma unroll 8
+                for (int ks = 0; ks < 64; ++ks) {
+                    const uint32_t sa = rg.block(base_page, toff + (uint32_t)ks * 512u, lane);
+                    const uint4 av = lds128(sa + lane * 16);
+                    const uint32_t af[4] = {av.x, av.y, av.z, av.w};
+                    mma16816(c[ks & 3], af, lds32(xa + ks * 32u), lds32(xa + ks * 32u + 16u));
+                }
+                if ((lane & 3) == 0) {
+                    const float lo = rbf((c[0][0] + c[1][0]) + (c[2][0] + c[3][0]));
+                    const float hi = rbf((c[0][2] + c[1][2]) + (c[2][2] + c[3][2]));
+                    const int r0 = pl.lm_row0 + j * 16 + (lane >> 2), r1 = r0 + 8;
+                    if (r0 < a.vocab) {
+                        if (lg) lg[r0] = lo;
+                        const unsigned long long k = argmax_key64(lo, r0);
+                        best = k > best ? k : best;
+                    }
+                    if (r1 < a.vocab) {
+                        if (lg) lg[r1] = hi;
+                        const unsigned long long k = argmax_key64(hi, r1);
+                        best = k > best ? k : best;
+                    }
+                }
+            }
+            rg.advance_to((uint32_t)(step + 1) * pl.step_pages, lane);     // leave the step's last pages
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
+                best = other > best ? other : best;
+            }
+            if (lane == 0) wbest[warp] = best;
+            consumer_bar();
+            if (tid == 0) {
+                unsigned long long k = 0ull;
+                for (int i = 0; i < ST_WARPS; ++i) k = wbest[i] > k ? wbest[i] : k;
+                publish_u32(xlm, 2 * (size_t)cta, (uint32_t)(k >> 32), t32);
+                publish_u32(xlm, 2 * (size_t)cta + 1, (uint32_t)k, t32);
+            }
+            ST_T1(L, 12);
+            // every CTA reduces the keys of all CTAs itself: no extra hop for the token
+            unsigned long long k = 0ull;
+            if (tid < grid) {
+                const uint32_t hi = __float_as_uint(po.f32(xlm + 2 * (size_t)tid, t32));
+                const uint32_t lo = __float_as_uint(po.f32(xlm + 2 * (size_t)tid + 1, t32));
+                k = ((unsigned long long)hi << 32) | lo;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, k, off);
+                k = other > k ? other : k;
+            }
+            consumer_bar();                    // wbest of this step has been read by thread 0
+            if (lane == 0) wbest[warp] = k;
+            consumer_bar();
+            if (tid == 0) {
+                unsigned long long kk = 0ull;
+                for (int i = 0; i < ST_WARPS; ++i) kk = wbest[i] > kk ? wbest[i] : kk;
+                const int next = (int)(0xffffffffu - (uint32_t)(kk & 0xffffffffull));
+                *s_token = next;
+                if (cta == 0) a.tokens_out[step] = next;
+            }
+            consumer_bar();
+            token = *s_token;
+            if (a.forced && step + 1 < a.n_steps) token = ld_cg_i32(a.forced + step + 1);
+            ST_T1(L, 13);
+        }
+    }
+    if (timing) dbg[(size_t)L * ST_STAGES + 15] += rg.wait_cycles;
+    if (cta == 0 && tid == 0) st_relaxed_u32(epoch, epoch0 + (uint32_t)(a.n_steps * (L + 1)));
+#undef ST_T0
+#undef ST_T1
+}
+
+// ------------------------------------------------------------------ weight packing
+// Writes CTA `blockIdx.x`'s segment of one layer: every 32-bit word of the segment is two
+// adjacent bf16 of one weight row, placed where the mma A fragment of its (tile, k-step) block
+// expects them: lane = 4 (row % 8) + (col % 8) / 2; register a0 (rows 0-7, cols 0-7),
+// a1 (rows 8-15, cols 0-7), a2 (rows 0-7, cols 8-15), a3 (rows 8-15, cols 8-15).
+__device__ __forceinline__ uint32_t pack_word(const bf16* W, int ld, int row, int col) {
+    return *reinterpret_cast<const uint32_t*>(W + (size_t)row * ld + col);
+}
+
+// row of tile-row i (0..15) of tile t in a phase -> (matrix, row index)
+struct RowSrc { const bf16* W; int row; };
+
+__global__ void k_pack_layer(const StPlan* plans, MqLayerWeights w, uint8_t* packed, int layer) {
+    const StPlan pl = plans[blockIdx.x];
+    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + (size_t)layer * pl.layer_bytes);
+    const uint32_t nwords = pl.layer_bytes / 4;
+    for (uint32_t wd = blockIdx.y * blockDim.x + threadIdx.x; wd < nwords; wd += gridDim.y * blockDim.x) {
+        const uint32_t off = wd * 4;
+        // which phase
+        int phase;
+        uint32_t poff;
+        if (off >= pl.off_d) { phase = 3; poff = off - pl.off_d; }
+        else if (off >= pl.off_gu) { phase = 2; poff = off - pl.off_gu; }
+        else if (off >= pl.off_o) { phase = 1; poff = off - pl.off_o; }
+        else { phase = 0; poff = off - pl.off_a; }
+        const int K = phase == 1 ? QSZ : phase == 3 ? I : H;
+        const uint32_t KS = (uint32_t)K / 16;
+        const int ng = phase == 0 ? pl.a_ng : phase == 2 ? 2 * pl.gu_np : pl.od_ng;   // 8-row groups
+        const int ntf = ng >> 1, nh = ng & 1;
+        const uint32_t full_bytes = KS * (uint32_t)ntf * 512u;
+        uint32_t value = 0u;
+        int trow = -1, tile = 0, col = 0;      // row within the tile (0..15), tile, first column
+        if (poff < full_bytes) {
+            const uint32_t blk = poff / 512u, inb = poff % 512u;
+            const uint32_t ks = blk / (uint32_t)ntf;
+            tile = (int)(blk % (uint32_t)ntf);
+            const int ln = (int)(inb / 16u), reg = (int)((inb % 16u) / 4u);
+            trow = (ln >> 2) + ((reg & 1) ? 8 : 0);
+            col = (int)ks * 16 + 2 * (ln & 3) + ((reg & 2) ? 8 : 0);
+        } else if (nh && poff < full_bytes + KS * 256u) {
+            const uint32_t p2 = poff - full_bytes;
+            const uint32_t ks = p2 / 256u, inb = p2 % 256u;
+            tile = ntf;
+            const int ln = (int)(inb / 8u), reg = (int)((inb % 8u) / 4u);
+            trow = ln >> 2;
+            col = (int)ks * 16 + 2 * (ln & 3) + (reg ? 8 : 0);
+        }
+        if (trow >= 0) {
+            const bf16* W;
+            int row;
+            if (phase == 0) {
+                const int r = pl.a_row0 + tile * 16 + trow;
+                if (r < QSZ) { W = (const bf16*)w.q_proj; row = r; }
+                else if (r < QSZ + KVSZ) { W = (const bf16*)w.k_proj; row = r - QSZ; }
+                else { W = (const bf16*)w.v_proj; row = r - QSZ - KVSZ; }
+            } else if (phase == 2) {
+                W = trow < 8 ? (const bf16*)w.gate_proj : (const bf16*)w.up_proj;
+                row = pl.gu_row0 + tile * 8 + (trow & 7);
+            } else {
+                W = phase == 1 ? (const bf16*)w.o_proj : (const bf16*)w.down_proj;
+                row = pl.od_row0 + tile * 16 + trow;
+            }
+            value = pack_word(W, K, row, col);
+        }
+        dst[wd] = value;       // padding between phases is zero
+    }
+}
+
+__global__ void k_pack_lm(const StPlan* plans, const bf16* lm_head, uint8_t* packed, int num_layers, int vocab) {
+    const StPlan pl = plans[blockIdx.x];
+    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + (size_t)num_layers * pl.layer_bytes);
+    const uint32_t nwords = (uint32_t)pl.lm_nt * (ST_LM_TILE_BYTES / 4);
+    for (uint32_t wd = blockIdx.y * blockDim.x + threadIdx.x; wd < nwords; wd += gridDim.y * blockDim.x) {
+        const uint32_t off = wd * 4;
+        const uint32_t tile = off / ST_LM_TILE_BYTES, intile = off % ST_LM_TILE_BYTES;
+        const uint32_t ks = intile / 512u, inb = intile % 512u;
+        const int ln = (int)(inb / 16u), reg = (int)((inb % 16u) / 4u);
+        const int row = pl.lm_row0 + (int)tile * 16 + (ln >> 2) + ((reg & 1) ? 8 : 0);
+        const int col = (int)ks * 16 + 2 * (ln & 3) + ((reg & 2) ? 8 : 0);
+        dst[wd] = row < vocab ? pack_word(lm_head, H, row, col) : 0u;
+    }
+}
+
+__global__ void k_pack_norms(MqLayerWeights w, bf16* dst) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < H) { dst[i] = ((const bf16*)w.input_layernorm)[i]; dst[H + i] = ((const bf16*)w.post_attn_layernorm)[i]; }
+    if (i < D) { dst[2 * H + i] = ((const bf16*)w.q_norm)[i]; dst[2 * H + D + i] = ((const bf16*)w.k_norm)[i]; }
+}
+
+// ------------------------------------------------------------------ host side
+static size_t st_smem_bytes() {
+    return (size_t)ST_NSLOT * ST_PAGE + (size_t)2 * ST_KV_CAP * ST_KV_LD * 2 + (size_t)I * 2 + (size_t)ST_WARPS * ST_RED_ROWS * 4 +
+           (4 * D + 2 * D + ST_WARPS * 32 + 4 * D) * 2 + (16 + 16 + 4 + 8 + 4) * 4 + ST_WARPS * 8 + 2 * ST_NSLOT * 8 + 16;
+}
+
+constexpr size_t ST_HDR_PLANS = 0;
+static size_t st_hdr_norms() { return ((size_t)ST_MAX_GRID * sizeof(StPlan) + 255) & ~(size_t)255; }
+static size_t st_hdr_bytes(int num_layers) {
+    return (st_hdr_norms() + (size_t)num_layers * NORM_STRIDE * 2 + ST_PAGE - 1) / ST_PAGE * ST_PAGE;
+}
+
+// Deals the rows out so that every CTA streams (almost) the same number of bytes per layer.
+// Units of 8 rows x 1024 columns (16 KB): a q|k|v group 1, a gate/up pair 2, a Wo group 2, a Wd
+// group 3; 1920 units in all.  CTAs 0..127 own one Wo/Wd group each (the same rows, so that the
+// residual of those rows stays in a register); gate/up pairs go one at a time to the CTA with
+// the most room left, q|k|v groups fill what remains.
+static int st_make_plans(int grid, int num_layers, int vocab, std::vector<StPlan>& plans, size_t* total_bytes) {
+    if (grid < ST_MIN_GRID || grid > ST_MAX_GRID) return MQ_ERR_UNSUPPORTED;
+    const int n_od = H / 8, n_a = QKV / 8, n_gu = I / 8;
+    plans.assign(grid, StPlan{});
+    std::vector<int> room(grid), pairs(grid, 0), od(grid, 0), ag(grid, 0);
+    const int total_units = n_a + 2 * n_gu + 5 * n_od;
+    const int target = (total_units + grid - 1) / grid;
+    for (int c = 0; c < grid; ++c) {
+        od[c] = c < n_od ? 1 : 0;
+        room[c] = target - 5 * od[c];
+    }
+    for (int p = 0; p < n_gu; ++p) {
+        int bestc = 0;
+        for (int c = 1; c < grid; ++c)
+            if (room[c] > room[bestc]) bestc = c;
+        if (room[bestc] < 2 || pairs[bestc] >= ST_MAX_TILES) return MQ_ERR_UNSUPPORTED;
+        pairs[bestc] += 1;
+        room[bestc] -= 2;
+    }
+    int left = n_a;
+    for (int c = 0; c < grid && left > 0; ++c) {
+        const int take = room[c] < left ? room[c] : left;
+        ag[c] = take > 0 ? take : 0;
+        left -= ag[c];
+    }
+    if (left > 0) return MQ_ERR_UNSUPPORTED;
+    const int lm_tiles = (vocab + 15) / 16;
+    int a_next = 0, od_next = 0, gu_next = 0, lm_next = 0;
+    size_t off = st_hdr_bytes(num_layers);
+    for (int c = 0; c < grid; ++c) {
+        StPlan& p = plans[c];
+        p.a_row0 = 8 * a_next; p.a_ng = ag[c]; a_next += ag[c];
+        p.od_row0 = 8 * od_next; p.od_ng = od[c]; od_next += od[c];
+        p.gu_row0 = 8 * gu_next; p.gu_np = pairs[c]; gu_next += pairs[c];
+        p.lm_nt = lm_tiles / grid + (c < lm_tiles % grid ? 1 : 0);
+        p.lm_row0 = 16 * lm_next; lm_next += p.lm_nt;
+        if (p.a_ng > 2 * ST_MAX_TILES || p.od_ng > 2) return MQ_ERR_UNSUPPORTED;
+        auto phase_bytes = [](int K, int ng) { return (uint32_t)(K / 16) * (uint32_t)((ng >> 1) * 512 + (ng & 1) * 256); };
+        auto up512 = [](uint32_t v) { return (v + 511u) & ~511u; };
+        p.off_a = 0;
+        p.off_o = up512(p.off_a + phase_bytes(H, p.a_ng));
+        p.off_gu = up512(p.off_o + phase_bytes(QSZ, p.od_ng));
+        p.off_d = up512(p.off_gu + phase_bytes(H, 2 * p.gu_np));
+        p.layer_bytes = up512(p.off_d + phase_bytes(I, p.od_ng));
+        p.step_bytes = (uint32_t)num_layers * p.layer_bytes + (uint32_t)p.lm_nt * ST_LM_TILE_BYTES;
+        p.step_pages = (p.step_bytes + ST_PAGE - 1) / ST_PAGE;
+        p.stream_off = off;
+        off += (size_t)p.step_pages * ST_PAGE;
+    }
+    if (a_next != n_a || od_next != n_od || gu_next != n_gu || lm_next != lm_tiles) return MQ_ERR_UNSUPPORTED;
+    *total_bytes = off;
+    return MQ_OK;
+}
+
+struct StDevice {
+    bool ready = false;
+    int sm_count = 0;
+};
+static StDevice g_st_dev[64];
+
+static int st_ensure_device(StDevice** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return MQ_ERR_UNSUPPORTED;
+    StDevice& st = g_st_dev[dev];
+    if (!st.ready) {
+        cudaDeviceProp p;
+        e = cudaGetDeviceProperties(&p, dev);
+        if (e != cudaSuccess) return (int)e;
+        if (p.major != 10 || p.multiProcessorCount < ST_MIN_GRID || p.multiProcessorCount > ST_MAX_GRID || !p.cooperativeLaunch)
+            return MQ_ERR_UNSUPPORTED;
+        st.sm_count = p.multiProcessorCount;
+        e = cudaFuncSetAttribute(k_decode_stream, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)st_smem_bytes());
+        if (e != cudaSuccess) return (int)e;
+        int per_sm = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_decode_stream, ST_THREADS, st_smem_bytes());
+        if (e != cudaSuccess) return (int)e;
+        if (per_sm < 1) return MQ_ERR_UNSUPPORTED;
+        st.ready = true;
+    }
+    *out = &st;
+    return MQ_OK;
+}
+
+}  // namespace mq
+
+using namespace mq;
+
+extern "C" size_t mq_stream_scratch_bytes(void) { return SC_BYTES; }
+
+extern "C" int mq_stream_max_context(void) {
+    StDevice* st = nullptr;
+    if (st_ensure_device(&st) != MQ_OK) return 0;
+    const int ms = st->sm_count / NKV < ST_MAX_SPLIT ? st->sm_count / NKV : ST_MAX_SPLIT;
+    return ms * ST_KV_CAP;
+}
+
+extern "C" int mq_stream_stage_count(void) { return ST_STAGES; }
+
+extern "C" int mq_stream_grid(void) {
+    StDevice* st = nullptr;
+    if (st_ensure_device(&st) != MQ_OK) return 0;
+    return st->sm_count;
+}
+
+extern "C" size_t mq_stream_packed_bytes(const MqModel* model) {
+    if (!model || model->num_layers <= 0 || model->vocab_size <= 0) return 0;
+    StDevice* st = nullptr;
+    if (st_ensure_device(&st) != MQ_OK) return 0;
+    std::vector<StPlan> plans;
+    size_t total = 0;
+    if (st_make_plans(st->sm_count, model->num_layers, model->vocab_size, plans, &total) != MQ_OK) return 0;
+    return total;
+}
+
+extern "C" int mq_stream_pack(const MqModel* model, void* packed, size_t packed_bytes, void* stream_v) {
+    if (!model || !packed || !model->layers || !model->lm_head) return MQ_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(packed) & 255u) != 0) return MQ_ERR_ALIGNMENT;
+    StDevice* st = nullptr;
+    int rc = st_ensure_device(&st);
+    if (rc != MQ_OK) return rc;
+    std::vector<StPlan> plans;
+    size_t total = 0;
+    rc = st_make_plans(st->sm_count, model->num_layers, model->vocab_size, plans, &total);
+    if (rc != MQ_OK) return rc;
+    if (packed_bytes < total) return MQ_ERR_BAD_ARG;
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    uint8_t* base = static_cast<uint8_t*>(packed);
+    cudaError_t e = cudaMemcpyAsync(base + ST_HDR_PLANS, plans.data(), plans.size() * sizeof(StPlan), cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(stream);      // `plans` is a host temporary
+    if (e != cudaSuccess) return (int)e;
+    const StPlan* dplans = reinterpret_cast<const StPlan*>(base + ST_HDR_PLANS);
+    bf16* norms = reinterpret_cast<bf16*>(base + st_hdr_norms());
+    for (int l = 0; l < model->num_layers; ++l) {
+        k_pack_norms<<<(H + 255) / 256, 256, 0, stream>>>(model->layers[l], norms + (size_t)l * NORM_STRIDE);
+        k_pack_layer<<<dim3(st->sm_count, 8), 256, 0, stream>>>(dplans, model->layers[l], base, l);
+    }
+    k_pack_lm<<<dim3(st->sm_count, 32), 256, 0, stream>>>(dplans, (const bf16*)model->lm_head, base, model->num_layers, model->vocab_size);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int mq_launch_decode_stream(const MqModel* model, const void* packed, void* k_cache, void* v_cache, void* scratch,
+                                       unsigned int* status, const int* first_token, const int* position0,
+                                       const int* forced_tokens, int* tokens_out, int n_steps, float* logits, int logits_all,
+                                       unsigned long long* stage_cycles, void* stream_v) {
+    if (!model || !packed || !k_cache || !v_cache || !scratch || !status || !position0 || !tokens_out) return MQ_ERR_BAD_ARG;
+    if (!first_token && !forced_tokens) return MQ_ERR_BAD_ARG;
+    if (!model->embed || !model->final_norm || !model->cos_table || !model->sin_table) return MQ_ERR_BAD_ARG;
+    if (model->num_layers <= 0 || model->vocab_size <= 0 || model->max_seq_len <= 0 || n_steps <= 0) return MQ_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(packed) & 255u) || (reinterpret_cast<uintptr_t>(scratch) & 255u) ||
+        (reinterpret_cast<uintptr_t>(k_cache) & 15u) || (reinterpret_cast<uintptr_t>(v_cache) & 15u))
+        return MQ_ERR_ALIGNMENT;
+    StDevice* st = nullptr;
+    int rc = st_ensure_device(&st);
+    if (rc != MQ_OK) return rc;
+    const uint8_t* base = static_cast<const uint8_t*>(packed);
+    StreamArgs a;
+    a.packed = base;
+    a.plans = reinterpret_cast<const StPlan*>(base + ST_HDR_PLANS);
+    a.norms = reinterpret_cast<const bf16*>(base + st_hdr_norms());
+    a.embed = (const bf16*)model->embed;
+    a.final_norm = (const bf16*)model->final_norm;
+    a.cos = (const bf16*)model->cos_table;
+    a.sin = (const bf16*)model->sin_table;
+    a.k_cache = (bf16*)k_cache;
+    a.v_cache = (bf16*)v_cache;
+    a.scratch = static_cast<uint8_t*>(scratch);
+    a.status = status;
+    a.first_token = first_token;
+    a.pos0 = position0;
+    a.forced = forced_tokens;
+    a.tokens_out = tokens_out;
+    a.logits = logits;
+    a.dbg = stage_cycles;
+    a.num_layers = model->num_layers;
+    a.vocab = model->vocab_size;
+    a.max_seq = model->max_seq_len;
+    a.n_steps = n_steps;
+    a.logits_all = logits_all;
+    a.max_split = st->sm_count / NKV < ST_MAX_SPLIT ? st->sm_count / NKV : ST_MAX_SPLIT;
+    void* params[] = {&a};
+    return (int)cudaLaunchCooperativeKernel((const void*)k_decode_stream, dim3(st->sm_count), dim3(ST_THREADS), params,
+                                            st_smem_bytes(), (cudaStream_t)stream_v);
+}

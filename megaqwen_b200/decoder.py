@@ -95,14 +95,13 @@ class MegakernelDecoder:
             self._pf = None            # prefill activation buffers, allocated at the first prefill
             self._pf_tensors = None
             self.use_gemm_prefill = True
-            # persistent decode chain: device copy of the layer table + its scratch
-            raw = bytes(self._layers)
-            self._layers_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
-            self._chain_scratch = torch.zeros(self._lib.mq_chain_scratch_bytes(), dtype=torch.uint8, device=dev)
-            self.persistent_available = self.max_seq_len_ <= self._lib.mq_chain_max_seq_len()
-            self.use_persistent = False
-            if self.persistent_available:
-                _lib.check(self._lib.mq_chain_init_device(), "mq_chain_init_device")
+            # Persistent decode (mq_launch_decode_stream): the weights repacked into per-CTA streams
+            # (built at the first use) and the scratch that carries its phase counter.
+            self._stream_packed = None
+            self._stream_scratch = torch.zeros(self._lib.mq_stream_scratch_bytes(), dtype=torch.uint8, device=dev)
+            self._stream_max_context = self._lib.mq_stream_max_context()
+            self.persistent_available = self._stream_max_context > 0
+            self.use_persistent = self.persistent_available
             self._chain_cap = 0
             self._chain_tokens = None
             self._chain_pos = None
@@ -229,14 +228,8 @@ class MegakernelDecoder:
                 tk[0:1].copy_(first_token.reshape(1).to(torch.int32), non_blocking=True)
             else:
                 tk[0:1].fill_(int(first_token))
-            if self.use_persistent and use_graph is not False:
-                self._pos_dev.fill_(self.position_)
-                rc = self._lib.mq_launch_decode_chain(
-                    C.byref(self._model), _ptr(self._layers_dev), _ptr(self.k_cache_), _ptr(self.v_cache_),
-                    _ptr(self._chain_scratch), _ptr(self._scalars) + 4, _ptr(tk), _ptr(self._pos_dev), _ptr(tk) + 4,
-                    num_steps, None, self._stream())
-                _lib.check(rc, "mq_launch_decode_chain")
-                self.launches += 1
+            if self.use_persistent and use_graph and self.position_ + num_steps <= self._stream_max_context:
+                self._launch_stream(_ptr(tk), None, _ptr(tk) + 4, num_steps, None, False, None)
                 self.position_ += num_steps
                 return tk[1:num_steps + 1]
             _lib.check(self._lib.mq_launch_fill_iota(_ptr(ps), self.position_, num_steps, self._stream()), "mq_launch_fill_iota")
@@ -282,15 +275,73 @@ class MegakernelDecoder:
         finally:
             self.use_persistent = keep
 
-    def decode_steps_cuda_persistent(self, first_token, num_steps: int) -> torch.Tensor:
-        """All steps in one persistent cooperative launch."""
+    def _ensure_stream_pack(self) -> None:
+        if self._stream_packed is None:
+            nbytes = self._lib.mq_stream_packed_bytes(C.byref(self._model))
+            if nbytes == 0:
+                raise RuntimeError("persistent decode is not available on this device")
+            self._stream_packed = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            _lib.check(self._lib.mq_stream_pack(C.byref(self._model), _ptr(self._stream_packed), nbytes, self._stream()),
+                       "mq_stream_pack")
+            self.launches += 2 * self.num_layers_ + 1
+
+    def _launch_stream(self, first_ptr, forced_ptr, out_ptr, num_steps, logits_ptr, logits_all, cycles_ptr) -> None:
+        """num_steps steps in one cooperative launch starting at position_ (not advanced here)."""
+        self._ensure_stream_pack()
+        self._pos_dev.fill_(self.position_)
+        rc = self._lib.mq_launch_decode_stream(
+            C.byref(self._model), _ptr(self._stream_packed), _ptr(self.k_cache_), _ptr(self.v_cache_),
+            _ptr(self._stream_scratch), _ptr(self._scalars) + 4, first_ptr, _ptr(self._pos_dev), forced_ptr, out_ptr,
+            num_steps, logits_ptr, 1 if logits_all else 0, cycles_ptr, self._stream())
+        _lib.check(rc, "mq_launch_decode_stream")
+        self.launches += 1
+
+    def _check_stream(self, num_steps: int, what: str) -> None:
         if not self.persistent_available:
-            raise RuntimeError("persistent decode chain unavailable for this max_seq_len")
+            raise RuntimeError("persistent decode is not available on this device")
+        if self.position_ + num_steps >= self.max_seq_len_:
+            raise RuntimeError(f"{what} would exceed max_seq_len")
+        if self.position_ + num_steps > self._stream_max_context:
+            raise RuntimeError(f"{what}: context beyond {self._stream_max_context} positions goes through decode_steps_cuda_graph")
+
+    def decode_steps_cuda_persistent(self, first_token, num_steps: int) -> torch.Tensor:
+        """All steps in one persistent cooperative launch (mq_launch_decode_stream)."""
+        if num_steps <= 0:
+            return torch.empty(0, dtype=torch.int32, device=self.device)
+        self._check_stream(num_steps, "decode_steps")
         keep, self.use_persistent = self.use_persistent, True
         try:
             return self._chain(first_token, num_steps, True).clone()
         finally:
             self.use_persistent = keep
+
+    def decode_forced_logits(self, tokens):
+        """Teacher-forced steps in one persistent launch: step i consumes tokens[i].  Returns
+        (predicted tokens cuda int32 [n], logits cuda fp32 [n, vocab]); used by the parity tests."""
+        forced = torch.as_tensor(tokens, dtype=torch.int32).reshape(-1).to(self.device)
+        n = int(forced.numel())
+        self._check_stream(n, "decode_steps")
+        with torch.cuda.device(self.device):
+            out = torch.empty(n, dtype=torch.int32, device=self.device)
+            logits = torch.empty((n, self.vocab_size_), dtype=torch.float32, device=self.device)
+            self._launch_stream(None, _ptr(forced), _ptr(out), n, _ptr(logits), True, None)
+            self.position_ += n
+        self.check_status()
+        return out, logits
+
+    def debug_decode_cycles(self, input_token_id: int) -> torch.Tensor:
+        """One decode step with the per-stage cycle counters on (reference:
+        debug_ldg_decode_cycles, bindings_prefill.cpp:980-1043).  Returns a CUDA int64 tensor
+        [CTAs, num_layers + 1, stages]; the stage list is in include/megaqwen_b200.h."""
+        self._check_stream(1, "decode_steps")
+        with torch.cuda.device(self.device):
+            cycles = torch.zeros((self._lib.mq_stream_grid(), self.num_layers_ + 1, self._lib.mq_stream_stage_count()),
+                                 dtype=torch.int64, device=self.device)
+            self._in_token.fill_(int(input_token_id))
+            self._launch_stream(_ptr(self._in_token), None, _ptr(self._scalars), 1, None, False, _ptr(cycles))
+            self.position_ += 1
+        self.check_status()
+        return cycles
 
     def decode_steps(self, first_token_id: int, num_steps: int) -> torch.Tensor:
         out = self._chain(first_token_id, num_steps, True)
