@@ -119,7 +119,7 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    sample_new = 24
+    sample_new = 64
     vals, pre = [], []
     from oracle.hf_reference import build_hf_model, time_hf_decode
     torch.set_num_threads(host_threads())   # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core it may
@@ -133,7 +133,7 @@ def run_reference(args):
             pre.append(prefill_s)
     v = sum(vals) / len(vals)
     cores = torch.get_num_threads()
-    sample = f"{PROMPT_LEN}-token prompt + {sample_new} greedy tokens per step, HF Qwen3ForCausalLM bf16 on CPU"
+    sample = f"{PROMPT_LEN}-token prompt + {sample_new} greedy single-token forwards per step (timed directly), HF Qwen3ForCausalLM bf16 on CPU"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sample_new / v,
@@ -146,7 +146,7 @@ def run_reference(args):
     }))
 
 
-def measure_other_configs(dev, w):
+def measure_other_configs(dev, w, only_config5=False, seq_seed0=0):
     """The remaining BASELINE configurations on one GPU (reported beside the headline):
     config 3 (1024-token prefill + 32 steps), config 4 (batch 32, ragged 256-512 prompts,
     128 steps) and config 5 (batch 64, 1024-token prompts, 256 steps)."""
@@ -162,6 +162,8 @@ def measure_other_configs(dev, w):
     def events():
         return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
+    if only_config5:
+        return _measure_batched(out, common, w, dev, only_config5, seq_seed0)
     # config 3
     dec = MegakernelDecoder(*common, w["cos_table"].to(dev), w["sin_table"].to(dev), spec.num_layers, MAX_SEQ, 1024)
     prompt = random_prompt(spec, 1024, 3, 0).to(dev)
@@ -185,11 +187,22 @@ def measure_other_configs(dev, w):
     del dec
     torch.cuda.empty_cache()
 
+    return _measure_batched(out, common, w, dev, only_config5, seq_seed0)
+
+
+def _measure_batched(out, common, w, dev, only_config5, seq_seed0):
+    from megaqwen_b200.batch import MegakernelBatchDecoder
+    from megaqwen_b200.synthetic import random_lengths
+    spec = QWEN3_0_6B
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
     def batched(name, lens, steps, max_seq, cfg_idx):
         B = len(lens)
         cos, sin = w["cos_table"][:max_seq].contiguous().to(dev), w["sin_table"][:max_seq].contiguous().to(dev)
         bd = MegakernelBatchDecoder(*common, cos, sin, spec.num_layers, max_seq, B, max(lens))
-        prompts = [random_prompt(spec, n, cfg_idx, i) for i, n in enumerate(lens)]
+        prompts = [random_prompt(spec, n, cfg_idx, seq_seed0 + i) for i, n in enumerate(lens)]
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
         first = bd.prefill_batch(prompts)
@@ -217,30 +230,66 @@ def measure_other_configs(dev, w):
         del bd
         torch.cuda.empty_cache()
 
-    batched("config4_batch32_ragged", random_lengths(32, 256, 512), 128, 1024, 4)
-    batched("config5_batch64_ctx1024", [1024] * 64, 256, 1280, 5)
+    if not only_config5:
+        batched("config4_batch32_ragged", random_lengths(32, 256, 512), 128, 1024, 4)
+    batched("config5_batch64_ctx1024", [1024] * 64, 256, 1296, 5)
     return out
 
 
 def decode_by_context(dec, dev, peak):
-    """Batch-1 decode latency at fixed cache lengths (32 graph-replayed steps starting at
-    each length, over the cache the headline run left behind): microseconds per token and
-    the fraction of the HBM roofline for the bytes of those steps."""
+    """Batch-1 decode latency at fixed cache lengths (32 steps starting at each length, over the
+    cache the headline run left behind): microseconds per token and the fraction of the HBM
+    roofline for the bytes of those steps, for the graph-replayed per-phase kernels and for the
+    persistent kernel (one cooperative launch)."""
     out = {}
+    keep = dec.use_persistent
     for L in (1, 16, 128, 512, 1024, 2048):
-        best = 1e9
-        for _ in range(3):
-            dec.position_ = L - 1          # the step writes position L-1 and attends over L entries
-            torch.cuda.synchronize(dev)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); dec._chain(17, 32, True); e1.record()
-            torch.cuda.synchronize(dev)
-            best = min(best, e0.elapsed_time(e1) / 32 * 1e3)
         nbytes = sum(QWEN3_0_6B.decode_bytes(L + i) for i in range(32)) / 32
-        gbs = nbytes / (best * 1e-6) / 1e9
-        out[str(L)] = {"us_per_token": best, "tokens_per_s": 1e6 / best, "achieved_GBps": gbs, "frac": gbs / peak}
+        row = {}
+        for name, persistent in (("graph", False), ("persistent", True)):
+            if persistent and not dec.persistent_available:
+                continue
+            dec.use_persistent = persistent
+            best = 1e9
+            for _ in range(3):
+                dec.position_ = L - 1          # the step writes position L-1 and attends over L entries
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); dec._chain(17, 32, True); e1.record()
+                torch.cuda.synchronize(dev)
+                best = min(best, e0.elapsed_time(e1) / 32 * 1e3)
+            gbs = nbytes / (best * 1e-6) / 1e9
+            row[name] = {"us_per_token": best, "achieved_GBps": gbs, "frac": gbs / peak, "frac_of_8TBps": gbs / 8000.0}
+        out[str(L)] = row
+    dec.use_persistent = keep
     dec.check_status()
     return out
+
+
+def parity_check(dec):
+    """The headline workload's first 64 decode steps, teacher-forced, against the committed HF
+    bf16 CPU fixture (tests/golden/full_cfg2_p2048_n256.npz; rank 0's prompt is that prompt)."""
+    import numpy as np
+    z = np.load(os.path.join(ROOT, "tests", "golden", "full_cfg2_p2048_n256.npz"))
+
+    def f32(a):
+        return torch.from_numpy(a.astype(np.uint16).view(np.int16).copy()).view(torch.bfloat16).float()
+
+    n = 64
+    tokens = z["tokens"].tolist()
+    dec.reset()
+    tok0, lg = dec.prefill_step_logits(torch.from_numpy(z["prompt"]))
+    rows, got = [lg.cpu()], [tok0]
+    for t in tokens[:n - 1]:
+        tok, l2 = dec.decode_step_logits(int(t))
+        rows.append(l2.cpu()); got.append(tok)
+    lgs = torch.stack(rows)
+    top_idx = torch.from_numpy(z["top_idx"][:n]).long()
+    d = torch.cat([(lgs[:, ::64] - f32(z["strided"][:n])).abs().flatten(),
+                   (torch.gather(lgs, 1, top_idx) - f32(z["top_vals"][:n])).abs().flatten()])
+    return {"against": "HF Qwen3ForCausalLM bf16 CPU fixture, 2048-token prompt, 64 teacher-forced steps (every 64th logit + HF's top-8)",
+            "max_abs": float(d.max()), "mean_abs": float(d.mean()), "frac_within_2e-2": float((d <= 2e-2).float().mean()),
+            "tokens_identical": sum(int(a == b) for a, b in zip(got, tokens[:n])), "tokens_compared": n}
 
 
 def run_ours(args):
@@ -259,6 +308,7 @@ def run_ours(args):
                             w["sin_table"].to(dev), QWEN3_0_6B.num_layers, MAX_SEQ, PROMPT_LEN)
     prompt = random_prompt(QWEN3_0_6B, PROMPT_LEN, 2, rank).pin_memory()
     chunk = args.chunk
+    dec.use_persistent = bool(args.persistent)
 
     def one_step(timed: bool):
         """Returns (decode_ms_device, decode_ms_e2e, prefill_ms_e2e, launches)."""
@@ -313,6 +363,21 @@ def run_ours(args):
     wall = time.perf_counter() - wall0
     clocks = sampler.stop()
     tot_dev, tot_e2e, tot_pre = max_over_ranks(dist, [sum(dev_ms), sum(e2e_ms), sum(pre_ms)])
+    other = None
+    if args.other_configs:
+        # Every rank measures the batched configurations on its own GPU (config 5 is the replica
+        # configuration: batch 64 x 1024-token prompts x 256 steps per GPU); the aggregate uses the
+        # slowest rank's time.  Only N = 1 also runs configs 3 and 4.
+        try:
+            other = measure_other_configs(dev, w, only_config5=(world > 1), seq_seed0=64 * rank)
+            ms5 = other["config5_batch64_ctx1024"]["ms_per_step"]
+            (worst_ms5,) = max_over_ranks(dist, [ms5])
+            other["config5_replicas"] = {"n_gpus": world, "batch_per_gpu": 64, "prompt_len": 1024, "decode_steps": 256,
+                                         "ms_per_step_max_over_ranks": worst_ms5,
+                                         "aggregate_decode_tokens_per_s": world * 64 / worst_ms5 * 1e3}
+        except Exception as exc:
+            other = {"error": repr(exc)[:200]}
+            max_over_ranks(dist, [0.0])
     if rank != 0:
         return
     n_tok = NEW_TOKENS * args.steps * world
@@ -323,9 +388,9 @@ def run_ours(args):
     bytes_pass = sum(QWEN3_0_6B.decode_bytes(PROMPT_LEN + i + 1) for i in range(NEW_TOKENS))
     step_s = (tot_dev / 1e3) / (NEW_TOKENS * args.steps)
     achieved = bytes_pass / NEW_TOKENS / step_s / 1e9
-    # DRAM traffic of one step: the ncu capture of all 141 kernels at cache length 2050 (read + write
-    # 1430.2 MB against 1427.3 MB algorithmic; summary under profiles/), moved to this
-    # run's mean cache length with the per-position KV bytes (traffic grows in proportion to them)
+    # DRAM traffic of one step: a RECORDED ncu capture at cache length 2050 (read + write 1430.2 MB
+    # against 1427.3 MB algorithmic), moved to this run's mean cache length with the per-position
+    # KV bytes (traffic grows in proportion to them); this run does not measure it
     mean_len = PROMPT_LEN + (NEW_TOKENS + 1) / 2
     traffic = NCU_STEP_DRAM_BYTES + (mean_len - NCU_STEP_CACHE_LEN) * (QWEN3_0_6B.decode_bytes(2) - QWEN3_0_6B.decode_bytes(1))
     line = {
@@ -333,35 +398,39 @@ def run_ours(args):
         "ms_per_step": tot_dev / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "parallelism": f"{world} independent replica(s), no communication",
-                   "l2": "inputs larger than L2 (1.19 GB of weights stream per token)", "graph_chunk": chunk},
+                   "l2": "inputs larger than L2 (1.19 GB of weights stream per token)", "steps_per_launch": chunk},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4 * NEW_TOKENS + 4,
                 "prefill_tokens_per_s": PROMPT_LEN * args.steps * world / (tot_pre / 1e3),
                 "prefill_h2d_bytes_per_step": 4 * PROMPT_LEN},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum over the 141 kernels of one step at cache length 2050, scaled to the mean cache length of this run",
+                     "traffic": traffic, "traffic_kind": "recorded",
+                     "traffic_source": "recorded ncu capture (dram__bytes_read.sum + dram__bytes_write.sum of one step at cache length 2050: "
+                                       + NCU_CAPTURE + "), scaled to the mean cache length of this run; not re-measured here",
                      "algorithmic_bytes": bytes_pass / NEW_TOKENS,
-                     "peak_kind": peak_kind, "kernel": "one decode step (141 chained kernels)",
+                     "peak_kind": peak_kind,
+                     "kernel": ("k_decode_stream: one persistent launch per chunk of decode steps; per-step figures = launch / steps"
+                                if args.persistent else "one decode step of the per-phase kernels (141 PDL-chained launches, graph replay)"),
                      "frac_of_8TBps": achieved / 8000.0, "us_per_token": step_s * 1e6},
         "clocks": clocks,
         "wall_s": wall,
     }
     if args.other_configs and world == 1:
         try:
+            line["parity"] = parity_check(dec)
+        except Exception as exc:
+            line["parity"] = {"error": repr(exc)[:200]}
+        try:
             line["decode_by_context"] = decode_by_context(dec, dev, peak)
         except Exception as exc:
             line["decode_by_context"] = {"error": repr(exc)[:200]}
-        try:
-            del dec
-            torch.cuda.empty_cache()
-            line["other_configs"] = measure_other_configs(dev, w)
-        except Exception as exc:
-            line["other_configs"] = {"error": repr(exc)[:200]}
+    if args.other_configs:
+        line["other_configs"] = other
     if not args.no_cpu and world == 1:
         try:
-            tps, prefill_s, cores = cpu_reference(16)
+            tps, prefill_s, cores = cpu_reference(64)
             line["cpu_baseline"] = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "reference",
-                                    "sample": f"{PROMPT_LEN}-token prompt + 16 greedy tokens, HF Qwen3ForCausalLM bf16 on CPU",
+                                    "sample": f"{PROMPT_LEN}-token prompt + 64 greedy single-token forwards timed directly, HF Qwen3ForCausalLM bf16 on CPU",
                                     "prefill_tokens_per_s": PROMPT_LEN / prefill_s}
         except Exception as exc:  # the baseline is reported, never a gate
             line["cpu_baseline"] = {"value": None, "error": repr(exc)[:200]}
@@ -421,7 +490,9 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--chunk", type=int, default=32, help="decode steps per CUDA graph")
+    ap.add_argument("--chunk", type=int, default=32, help="decode steps per CUDA graph (per launch with --persistent)")
+    ap.add_argument("--persistent", action="store_true",
+                    help="time the persistent kernel (one cooperative launch per chunk) instead of the graph-replayed per-phase kernels")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-other-configs", dest="other_configs", action="store_false",
                     help="skip the extra single-GPU measurements of configs 3-5")

@@ -7,21 +7,26 @@
 // dependent phases, so the design separates the two:
 //
 //  * Weights never depend on activations.  At load time they are repacked into one
-//    contiguous byte stream per CTA, in exactly the order that CTA consumes them and already
-//    in the register layout of the mma.sync A operand (a "block" = 16 rows x 16 columns =
-//    512 bytes = 16 bytes per lane).  A producer thread per CTA copies its stream page by page
-//    (8 KB, one 1-D TMA bulk copy each, no multicast) into a ring of shared-memory slots and
-//    runs ahead of the consumers by the ring's size, across phase, layer and step boundaries.
-//    The LM head (tied embedding, tiled the same way) is the tail of every step's stream.
+//    contiguous byte stream per WARP (8 per CTA), in exactly the order that warp consumes them
+//    and already in the register layout of the mma.sync A operand.  Each warp streams its own
+//    bytes through a private ring of 2 KB shared-memory slots with 1-D TMA bulk copies (no
+//    multicast): it waits for a slot, multiplies, and refills the slot it has just used with
+//    the unit nine places ahead.  There is no producer warp and no hand-shake between warps;
+//    the stream runs ahead of the arithmetic by the ring's size (144 KB per SM) across phase,
+//    layer and step boundaries.  The LM head (tied embedding, tiled the same way) is the tail
+//    of every step's stream.
 //  * Activations are exchanged between CTAs through small global buffers of 32-bit words that
 //    hold a bf16 value in the high half and a 16-bit phase tag in the low half: a consumer
 //    re-reads its words until the tags match, so data and readiness arrive in one L2 round
 //    trip and there is no flag, fence, grid barrier or kernel boundary on the critical path
 //    (the reference: 225 grid.sync() per token).  fp32 split-KV partials and the arg-max keys
 //    travel as 64-bit words (tag32 | payload32).
-//  * Every GEMV is K-split over the CTA's eight consumer warps, accumulates with
-//    mma.sync.m16n8k16 (bf16 in, fp32 out; the activation vector replicated over the eight
-//    B columns) and is summed across warps in a fixed order: results are bit-reproducible.
+//  * Every GEMV is K-split over the CTA's eight warps (warp w owns columns w K/8 .. of every
+//    row of the CTA), accumulates with mma.sync.m16n8k16 (bf16 in, fp32 out; the activation
+//    vector replicated over the eight B columns) and is summed across warps in a fixed order:
+//    results are bit-reproducible.  In the LM head a warp owns whole 16-row tiles instead.
+//  * The layer loop runs thousands of times and must stay in the instruction cache: loops are
+//    rolled, the GEMV code exists once, rare paths are out of line.
 //
 // Work split (planned on the host for the device's SM count): the 4096 q|k|v rows, the 3072
 // gate/up row pairs and the 1024 rows of Wo / Wd are dealt out in groups of 8 rows so that every
@@ -44,11 +49,13 @@
 
 namespace mq {
 
-constexpr int ST_WARPS = 8;                      // consumer warps
-constexpr int ST_CONSUMERS = ST_WARPS * 32;      // 256 threads
-constexpr int ST_THREADS = ST_CONSUMERS + 32;    // + the producer warp
-constexpr uint32_t ST_PAGE = 8192;               // bytes per ring slot
-constexpr int ST_NSLOT = 18;                     // ring slots: 144 KB in flight per SM
+constexpr int ST_WARPS = 8;
+constexpr int ST_THREADS = ST_WARPS * 32;        // 256: every warp streams, multiplies and polls
+constexpr uint32_t ST_UNIT = 2048;               // bytes per ring slot = one bulk copy = 4 blocks of 512 bytes
+#ifndef MQ_ST_NSLOT
+#define MQ_ST_NSLOT 9
+#endif
+constexpr int ST_NSLOT = MQ_ST_NSLOT;            // slots per warp: 8 x 9 x 2 KB = 144 KB in flight per SM
 constexpr int ST_KV_CAP = 128;                   // cached positions one CTA attends over
 constexpr int ST_KV_LD = D + 8;                  // K/V rows padded by 16 bytes (conflict-free ldmatrix)
 constexpr int ST_MAX_SPLIT = 18;                 // CTAs per kv head
@@ -58,7 +65,7 @@ constexpr int ST_MIN_GRID = 128;
 constexpr int ST_MAX_GRID = 256;
 constexpr int ST_PART = D + 2;                   // m, l, acc[128]
 constexpr int ST_STAGES = 16;                    // stage counters per (CTA, layer)
-constexpr uint32_t ST_LM_TILE_BYTES = 64 * 512;  // one 16-row tile of the LM head: 64 k-steps
+constexpr int ST_LM_TILE_UNITS = 16;             // one 16-row tile of the LM head: 64 k-steps = 32 KB
 
 // Per-CTA plan, written by the host when the weights are packed.
 struct StPlan {
@@ -66,15 +73,23 @@ struct StPlan {
     int od_row0, od_ng;        // rows of Wo and Wd
     int gu_row0, gu_np;        // rows of Wg / Wu: first row and number of (8 gate + 8 up) tiles
     int lm_row0, lm_nt;        // LM head: first vocabulary row and number of 16-row tiles
-    uint32_t off_a, off_o, off_gu, off_d;   // byte offsets of the four GEMV phases in a layer segment
-    uint32_t layer_bytes;      // bytes of one layer segment
-    uint32_t step_bytes;       // num_layers * layer_bytes + lm_nt * 32 KB
-    uint32_t step_pages;       // pages per step (the last one may be short)
-    uint32_t pad_;
-    unsigned long long stream_off;   // byte offset of this CTA's stream in the packed buffer
+    uint32_t layer_units;      // 2 KB units per layer and warp
+    uint32_t pad_[3];
+    unsigned long long stream_off;   // byte offset of this CTA's streams (warp 0 first) in the packed buffer
     unsigned long long pad2_;
 };
-static_assert(sizeof(StPlan) == 80, "plan layout");
+static_assert(sizeof(StPlan) == 64, "plan layout");
+
+// units per warp of one phase: a full tile holds K/8 columns x 16 rows per warp, a half tile 8 rows
+__host__ __device__ constexpr uint32_t st_phase_units(int K, int ng) { return (uint32_t)((ng >> 1) * (K / 512) + (ng & 1) * (K / 1024)); }
+__host__ __device__ inline uint32_t st_layer_units(const StPlan& p) {
+    return st_phase_units(H, p.a_ng) + st_phase_units(QSZ, p.od_ng) + st_phase_units(H, 2 * p.gu_np) + st_phase_units(I, p.od_ng);
+}
+// LM tiles of warp w: tiles w, w + 8, .. of the CTA's lm_nt tiles
+__host__ __device__ inline uint32_t st_lm_tiles(const StPlan& p, int w) { return p.lm_nt > w ? (uint32_t)(p.lm_nt - w + ST_WARPS - 1) / ST_WARPS : 0u; }
+__host__ __device__ inline uint32_t st_step_units(const StPlan& p, int w, int num_layers) {
+    return (uint32_t)num_layers * p.layer_units + st_lm_tiles(p, w) * ST_LM_TILE_UNITS;
+}
 
 // Scratch (caller-owned, zeroed once): tagged exchange vectors, split-KV partials, arg-max keys
 // and the phase counter that keeps tags unique from launch to launch.
@@ -114,6 +129,7 @@ struct StreamArgs {
     int max_split;                  // min(18, grid / 8)
 };
 
+
 constexpr int NORM_STRIDE = 2 * H + 2 * D;
 
 // ------------------------------------------------------------------ tagged exchange
@@ -150,7 +166,7 @@ constexpr long long POLL_LIMIT_CYCLES = 400000000LL;   // about 0.2 s
 
 struct Poller {
     unsigned int* status;
-    bool aborted;
+    bool aborted;       // the kernel is draining
     __device__ __forceinline__ void refresh() { aborted = (ld_relaxed_u32(status) & MQ_STATUS_WAIT_TIMEOUT) != 0; }
     __device__ __forceinline__ void expire() {
         atomicOr(status, MQ_STATUS_WAIT_TIMEOUT);
@@ -200,7 +216,7 @@ struct Poller {
     }
 };
 
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS) : "memory"); }
+__device__ __forceinline__ void consumer_bar() { __syncthreads(); }
 
 __device__ __forceinline__ uint2 tagged_to_bf16x4(const uint4& v) {
     uint2 o;
@@ -215,12 +231,28 @@ template <int NCH>
 __device__ __forceinline__ void poll_vector(Poller& po, const uint32_t* src, uint32_t tag16, bf16* dst, int tid) {
     uint4 v[NCH];
 #pragma unroll
-    for (int k = 0; k < NCH; ++k) v[k] = ld_relaxed_v4(src + 4 * (tid + k * ST_CONSUMERS));
+    for (int k = 0; k < NCH; ++k) v[k] = ld_relaxed_v4(src + 4 * (tid + k * ST_THREADS));
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-        if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + 4 * (tid + k * ST_CONSUMERS), tag16);
-        *reinterpret_cast<uint2*>(dst + 4 * (tid + k * ST_CONSUMERS)) = tagged_to_bf16x4(v[k]);
+        if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + 4 * (tid + k * ST_THREADS), tag16);
+        *reinterpret_cast<uint2*>(dst + 4 * (tid + k * ST_THREADS)) = tagged_to_bf16x4(v[k]);
     }
+}
+
+// Warp `warp` gathers ITS slice of a tagged vector (words warp * 32 * NCH * 4 ..), which is all a
+// K-split GEMV needs of it: no block barrier, and the warp starts as soon as its own words are in.
+template <int NCH>
+__device__ __forceinline__ void poll_slice(Poller& po, const uint32_t* src, uint32_t tag16, bf16* dst, int warp, int lane) {
+    const int base = warp * (32 * NCH * 4) + lane * 4;
+    uint4 v[NCH];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) v[k] = ld_relaxed_v4(src + base + k * 128);
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+        if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + base + k * 128, tag16);
+        *reinterpret_cast<uint2*>(dst + base + k * 128) = tagged_to_bf16x4(v[k]);
+    }
+    __syncwarp();
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t saddr) {
@@ -234,134 +266,132 @@ __device__ __forceinline__ uint2 lds64(uint32_t saddr) {
     return v;
 }
 
-// ------------------------------------------------------------------ ring cursor of one consumer warp
-// Every warp walks every page of the CTA's stream in order: it waits until the page is full,
-// uses the blocks that belong to it, and arrives on the page's "empty" barrier when it moves
-// on.  A slot is refilled once all eight warps have passed it.
-struct Ring {
-    uint32_t ring_addr;       // shared address of slot 0
-    uint64_t* full;
-    uint64_t* empty;
-    unsigned int* status;
-    uint32_t cur;             // first page this warp has not left yet (global page index)
-    uint32_t ready;           // page known to be full (cur or cur - 1 .. ), ~0 = none
-    unsigned long long wait_cycles;
-    bool timing;
+// ------------------------------------------------------------------ the ring of one warp
+// Slot k of the warp holds unit u with u % ST_NSLOT == k of the warp's stream.  The warp waits
+// for the slot's mbarrier (completed by the bulk copy), reads the unit, and lane 0 refills the
+// same slot with unit u + ST_NSLOT.  Refill and use are ordered by the warp's own program
+// order, so there is no "empty" barrier.
+__device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned int* status) { mbar_wait(bar, parity, status); }
 
-    __device__ __forceinline__ void wait_page(uint32_t pg) {
-        if (pg == ready) return;
-        uint64_t* bar = &full[pg % ST_NSLOT];
-        const uint32_t parity = (pg / ST_NSLOT) & 1u;
-        if (!mbar_try_wait(bar, parity)) {
-            const long long t0 = timing ? clock64() : 0;
-            mbar_wait(bar, parity, status);
-            if (timing) wait_cycles += (unsigned long long)(clock64() - t0);
-        }
-        ready = pg;
+__device__ __forceinline__ void bulk_g2s_addr(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar_addr) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_addr(uint32_t bar_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_addr), "r"(bytes) : "memory");
+}
+
+struct WRing {
+    uint32_t base;            // shared address of this warp's slot 0
+    uint64_t* full;           // this warp's ST_NSLOT barriers
+    const uint8_t* src;       // this warp's stream (one step's worth, re-read every step)
+    unsigned int* status;
+    uint32_t slot;            // slot of the next unit to use
+    uint32_t parity;          // its barrier phase
+    uint32_t fidx;            // index (within a step) of the next unit to fetch
+    uint32_t step_units;      // units per step
+    uint32_t left;            // units still to fetch in this launch
+
+    __device__ __forceinline__ void fetch(uint32_t k) {          // lane 0 only
+        const uint32_t bar = smem_u32(&full[k]);
+        mbar_expect_tx_addr(bar, ST_UNIT);
+        bulk_g2s_addr(base + k * ST_UNIT, src + (size_t)fidx * ST_UNIT, ST_UNIT, bar);
     }
-    __device__ __forceinline__ void advance_to(uint32_t target, int lane) {
-        while (cur < target) {
-            wait_page(cur);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[cur % ST_NSLOT]);
-            ++cur;
-        }
+    __device__ __forceinline__ void advance_fetch() {
+        --left;
+        if (++fidx == step_units) fidx = 0u;
     }
-    // shared address of the block at byte `voff` of the step whose first page is base_page
-    __device__ __forceinline__ uint32_t block(uint32_t base_page, uint32_t voff, int lane) {
-        const uint32_t pg = base_page + voff / ST_PAGE;
-        advance_to(pg, lane);
-        wait_page(pg);
-        return ring_addr + (pg % ST_NSLOT) * ST_PAGE + (voff % ST_PAGE);
+    // shared address of the next unit, once it has landed
+    __device__ __forceinline__ uint32_t acquire() {
+        if (!mbar_try_wait(&full[slot], parity)) mbar_wait_slow(&full[slot], parity, status);
+        return base + slot * ST_UNIT;
+    }
+    // the unit's bytes are in registers (their consumers have been issued): refill its slot
+    __device__ __forceinline__ void release(int lane) {
+        __syncwarp();
+        if (left) {
+            if (lane == 0) fetch(slot);
+            advance_fetch();
+        }
+        if (++slot == (uint32_t)ST_NSLOT) { slot = 0u; parity ^= 1u; }
     }
 };
 
 // ------------------------------------------------------------------ GEMV on the packed stream
-// One phase = `ntf` full tiles (16 rows) and `nh` (0/1) half tile (8 rows) over K = 128 * KSW
-// columns.  Stream layout: [k-step][tile] blocks of 512 bytes for the full tiles, then
-// [k-step] blocks of 256 bytes for the half tile.  Warp w takes k-steps w, w + 8, ..; lanes
-// 0, 4, .., 28 end with row l/4 in c[0] and row l/4 + 8 in c[2], written to red[warp][row].
-template <int KSW, int NT>
-__device__ __forceinline__ void gemv_full(Ring& rg, uint32_t base_page, uint32_t voff, const uint32_t (&xb)[KSW][2], int warp, int lane,
-                                          float* red) {
-    constexpr int NACC = NT == 1 ? 4 : (NT <= 3 ? 2 : 1);
-    float c[NT][NACC][4];
-#pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-        for (int q = 0; q < NACC; ++q) { c[t][q][0] = 0.f; c[t][q][1] = 0.f; c[t][q][2] = 0.f; c[t][q][3] = 0.f; }
-#pragma unroll
-    for (int j = 0; j < KSW; ++j) {
-        const uint32_t ks = (uint32_t)(j * ST_WARPS + warp);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            const uint32_t sa = rg.block(base_page, voff + (ks * NT + t) * 512u, lane);
-            const uint4 av = lds128(sa + lane * 16);
-            const uint32_t af[4] = {av.x, av.y, av.z, av.w};
-            mma16816(c[t][j % NACC], af, xb[j][0], xb[j][1]);
-        }
-    }
-    if ((lane & 3) == 0) {
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            float lo = 0.f, hi = 0.f;
-#pragma unroll
-            for (int q = 0; q < NACC; ++q) { lo += c[t][q][0]; hi += c[t][q][2]; }
-            red[warp * ST_RED_ROWS + t * 16 + (lane >> 2)] = lo;
-            red[warp * ST_RED_ROWS + t * 16 + 8 + (lane >> 2)] = hi;
-        }
-    }
+// One phase = `ntf` full tiles (16 rows) and `nh` (0/1) half tile (8 rows); warp w multiplies
+// columns [w kw, (w + 1) kw) of every row (kw = K / 8) with its slice of the activation vector
+// (bf16, shared memory).  Stream of the warp: per full tile kw / 64 units, then kw / 128 units
+// of the half tile.  A unit is four 512-byte blocks, 16 bytes per lane and block:
+//   full tile, block s = k-step s of the unit (columns c = C0 + 16 tig + 4 s):
+//       W[g][c, c+1] | W[g+8][c, c+1] | W[g][c+2, c+3] | W[g+8][c+2, c+3]      (a0 a1 a2 a3)
+//   half tile, block u = k-steps 2u, 2u+1 (columns c = C0 + 32 tig + 8 u):
+//       W[g][c .. c+7]                                  (k-step 2u: c..c+3, k-step 2u+1: c+4..c+7)
+// with g = lane / 4, tig = lane % 4: a lane's B fragments of a unit are 32 (64) contiguous
+// bytes of the activation vector.  Lanes 0, 4, .., 28 end with row g in c[0] and row g + 8 in
+// c[2], written to red[warp][row].
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int KSW>
-__device__ __forceinline__ void gemv_half(Ring& rg, uint32_t base_page, uint32_t voff, const uint32_t (&xb)[KSW][2], int warp, int lane,
-                                          float* red, int row0) {
-    float c[4][4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
-#pragma unroll
-    for (int j = 0; j < KSW; ++j) {
-        const uint32_t ks = (uint32_t)(j * ST_WARPS + warp);
-        const uint32_t sa = rg.block(base_page, voff + ks * 256u, lane);
-        const uint2 av = lds64(sa + lane * 8);
-        const uint32_t af[4] = {av.x, 0u, av.y, 0u};
-        mma16816(c[j & 3], af, xb[j][0], xb[j][1]);
+// one unit of a full tile: four k-steps into four independent accumulators
+__device__ __forceinline__ void full_unit(WRing& rg, float (&c)[4][4], uint32_t xaddr, int lane) {
+    const uint32_t sa = rg.acquire() + (uint32_t)lane * 16u;
+    const uint4 a0 = lds128(sa), a1 = lds128(sa + 512u), a2 = lds128(sa + 1024u), a3 = lds128(sa + 1536u);
+    const uint4 x0 = lds128(xaddr), x1 = lds128(xaddr + 16u);
+    {
+        mma_bf16(c[0], a0.x, a0.y, a0.z, a0.w, x0.x, x0.y);
+        mma_bf16(c[1], a1.x, a1.y, a1.z, a1.w, x0.z, x0.w);
+        mma_bf16(c[2], a2.x, a2.y, a2.z, a2.w, x1.x, x1.y);
+        mma_bf16(c[3], a3.x, a3.y, a3.z, a3.w, x1.z, x1.w);
     }
-    if ((lane & 3) == 0) red[warp * ST_RED_ROWS + row0 + (lane >> 2)] = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);
+    rg.release(lane);
 }
 
-template <int KSW>
-__device__ __forceinline__ void gemv_phase(Ring& rg, uint32_t base_page, uint32_t voff, int ntf, int nh, const bf16* xs, float* red,
-                                           int warp, int lane) {
-    // this warp's slices of the activation vector as mma B fragments
-    uint32_t xb[KSW][2];
-    const uint32_t xa = smem_u32(xs) + (uint32_t)(lane & 3) * 4u;
+__device__ __forceinline__ void gemv_phase(WRing& rg, int ntf, int nh, int kw, uint32_t xs_addr, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t xw = xs_addr + (uint32_t)(warp * kw) * 2u;           // this warp's slice of the vector
+    float* rw = red + warp * ST_RED_ROWS + (lane >> 2);
+#pragma unroll 1
+    for (int t = 0; t < ntf; ++t) {
+        float c[4][4];
 #pragma unroll
-    for (int j = 0; j < KSW; ++j) {
-        const uint32_t ks = (uint32_t)(j * ST_WARPS + warp);
-        xb[j][0] = lds32(xa + ks * 32u);
-        xb[j][1] = lds32(xa + ks * 32u + 16u);
-    }
-    constexpr uint32_t KS = KSW * ST_WARPS;
-    if (KSW == 8) {
-        switch (ntf) {
-            case 1: gemv_full<KSW, 1>(rg, base_page, voff, xb, warp, lane, red); break;
-            case 2: gemv_full<KSW, 2>(rg, base_page, voff, xb, warp, lane, red); break;
-            case 3: gemv_full<KSW, 3>(rg, base_page, voff, xb, warp, lane, red); break;
-            case 4: gemv_full<KSW, 4>(rg, base_page, voff, xb, warp, lane, red); break;
-            case 5: gemv_full<KSW, 5>(rg, base_page, voff, xb, warp, lane, red); break;
-            case 6: gemv_full<KSW, 6>(rg, base_page, voff, xb, warp, lane, red); break;
-            case 7: gemv_full<KSW, 7>(rg, base_page, voff, xb, warp, lane, red); break;
-            default: break;
+        for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
+        const uint32_t xl = xw + (uint32_t)(lane & 3) * 32u;
+#pragma unroll 1
+        for (int i = 0; i < kw; i += 64) full_unit(rg, c, xl + (uint32_t)i * 2u, lane);
+        if ((lane & 3) == 0) {
+            rw[t * 16] = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);
+            rw[t * 16 + 8] = (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]);
         }
-    } else if (ntf == 1) {
-        gemv_full<KSW, 1>(rg, base_page, voff, xb, warp, lane, red);
     }
-    const uint32_t half_off = voff + KS * (uint32_t)ntf * 512u;
-    if (nh) gemv_half<KSW>(rg, base_page, half_off, xb, warp, lane, red, ntf * 16);
-    // leave every page that ends inside this phase, so that the producer can refill it while
-    // the CTA waits for the next activation vector
-    rg.advance_to(base_page + (half_off + (nh ? KS * 256u : 0u)) / ST_PAGE, lane);
+    if (nh) {
+        float c[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
+        const uint32_t xl = xw + (uint32_t)(lane & 3) * 64u;
+        const bool odd = ((lane >> 2) & 1) != 0;
+#pragma unroll 1
+        for (int i = 0; i < kw; i += 128) {
+            const uint32_t sa = rg.acquire() + (uint32_t)lane * 16u;
+            const uint4 a0 = lds128(sa), a1 = lds128(sa + 512u), a2 = lds128(sa + 1024u), a3 = lds128(sa + 1536u);
+            const uint32_t xa = xl + (uint32_t)i * 2u;
+            const uint4 x0 = lds128(xa), x1 = lds128(xa + 16u), x2 = lds128(xa + 32u), x3 = lds128(xa + 48u);
+            {
+                // One mma per block: rows 0-7 of the A tile are the 8 weight rows at k-step 2u, rows
+                // 8-15 the SAME weight rows at k-step 2u+1; B column 0 carries the vector slice of
+                // k-step 2u, column 1 that of 2u+1 (the other columns are ignored).  The row sums are
+                // C[r][0] + C[r+8][1], i.e. c[0] + c[3] of lanes 0, 4, .., 28.
+                mma_bf16(c[0], a0.x, a0.z, a0.y, a0.w, odd ? x0.z : x0.x, odd ? x0.w : x0.y);
+                mma_bf16(c[1], a1.x, a1.z, a1.y, a1.w, odd ? x1.z : x1.x, odd ? x1.w : x1.y);
+                mma_bf16(c[2], a2.x, a2.z, a2.y, a2.w, odd ? x2.z : x2.x, odd ? x2.w : x2.y);
+                mma_bf16(c[3], a3.x, a3.z, a3.y, a3.w, odd ? x3.z : x3.x, odd ? x3.w : x3.y);
+            }
+            rg.release(lane);
+        }
+        if ((lane & 3) == 0) rw[ntf * 16] = ((c[0][0] + c[0][3]) + (c[1][0] + c[1][3])) + ((c[2][0] + c[2][3]) + (c[3][0] + c[3][3]));
+    }
 }
 
 // per-head RMSNorm + RoPE of a raw head held in shared memory (bf16[128]); lane owns elements
@@ -423,8 +453,8 @@ __device__ __forceinline__ unsigned long long argmax_key64(float v, int idx) {
 // ------------------------------------------------------------------ the kernel
 __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t* ring = smem_raw;                                                    // [ST_NSLOT][ST_PAGE]
-    bf16* kt = reinterpret_cast<bf16*>(smem_raw + (size_t)ST_NSLOT * ST_PAGE);   // [ST_KV_CAP][ST_KV_LD]
+    uint8_t* ring = smem_raw;                                                    // [ST_WARPS][ST_NSLOT][ST_UNIT]
+    bf16* kt = reinterpret_cast<bf16*>(smem_raw + (size_t)ST_WARPS * ST_NSLOT * ST_UNIT);   // [ST_KV_CAP][ST_KV_LD]
     bf16* vt = kt + (size_t)ST_KV_CAP * ST_KV_LD;
     bf16* xs = vt + (size_t)ST_KV_CAP * ST_KV_LD;                                // [3072] activation vector of a GEMV phase
     float* red = reinterpret_cast<float*>(xs + I);                               // [8][ST_RED_ROWS] per-warp partial sums
@@ -438,9 +468,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     float* ml = wl + 16;                                                         // [2][2]
     float* ssp = ml + 4;                                                         // [8] partial sums of squares
     unsigned long long* wbest = reinterpret_cast<unsigned long long*>(ssp + 8 + 4);   // [8] (8-byte aligned: 44 floats before it)
-    uint64_t* full = reinterpret_cast<uint64_t*>(wbest + ST_WARPS);
-    uint64_t* empty = full + ST_NSLOT;
-    int* s_token = reinterpret_cast<int*>(empty + ST_NSLOT);
+    uint64_t* full = reinterpret_cast<uint64_t*>(wbest + ST_WARPS);              // [ST_WARPS][ST_NSLOT]
+    int* s_token = reinterpret_cast<int*>(full + ST_WARPS * ST_NSLOT);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cta = blockIdx.x, grid = gridDim.x;
@@ -448,7 +477,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     const StPlan pl = a.plans[cta];
 
     if (tid == 0) {
-        for (int i = 0; i < ST_NSLOT; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], ST_WARPS); }
+        for (int i = 0; i < ST_WARPS * ST_NSLOT; ++i) mbar_init(&full[i], 1);
         mbar_fence_init();
     }
     __syncthreads();
@@ -470,39 +499,28 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
         return;
     }
 
-    if (warp == ST_WARPS) {
-        // ============================================================ producer
-        if (lane == 0) {
-            const uint8_t* src = a.packed + pl.stream_off;
-            uint32_t gp = 0;
-            bool dead = false;
-            for (int step = 0; step < a.n_steps && !dead; ++step) {
-                for (uint32_t p = 0; p < pl.step_pages; ++p, ++gp) {
-                    const uint32_t slot = gp % ST_NSLOT, fill = gp / ST_NSLOT;
-                    if (fill > 0 && !mbar_wait(&empty[slot], (fill - 1) & 1u, a.status)) { dead = true; break; }
-                    const uint32_t bytes = min(ST_PAGE, pl.step_bytes - p * ST_PAGE);
-                    mbar_expect_tx(&full[slot], bytes);
-                    bulk_g2s(ring + (size_t)slot * ST_PAGE, src + (size_t)p * ST_PAGE, bytes, &full[slot]);
-                }
-            }
-            if (dead) {
-                // the kernel is draining: let the copies still in flight land before the CTA's
-                // shared memory is given back
-                const uint32_t first = gp > (uint32_t)ST_NSLOT ? gp - ST_NSLOT : 0u;
-                for (uint32_t q = first; q < gp; ++q) {
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(&full[q % ST_NSLOT], (q / ST_NSLOT) & 1u) && clock64() - t0 < 2000000) { }
-                }
-            }
-        }
-        return;
-    }
-
-    // ============================================================== consumers
     Poller po{a.status, false};
     po.refresh();
     const bool timing = a.dbg != nullptr && tid == 0;
-    Ring rg{smem_u32(ring), full, empty, a.status, 0u, 0xffffffffu, 0ull, timing};
+    // this warp's stream and ring; the first ST_NSLOT units are requested at once
+    WRing rg;
+    {
+        size_t woff = 0;
+        for (int v = 0; v < warp; ++v) woff += (size_t)st_step_units(pl, v, L) * ST_UNIT;
+        rg.base = smem_u32(ring) + (uint32_t)warp * ST_NSLOT * ST_UNIT;
+        rg.full = full + warp * ST_NSLOT;
+        rg.src = a.packed + pl.stream_off + woff;
+        rg.status = a.status;
+        rg.slot = 0u;
+        rg.parity = 0u;
+        rg.fidx = 0u;
+        rg.step_units = st_step_units(pl, warp, L);
+        rg.left = rg.step_units * (uint32_t)a.n_steps;
+        for (int k = 0; k < ST_NSLOT && rg.left; ++k) {
+            if (lane == 0) rg.fetch((uint32_t)k);
+            rg.advance_fetch();
+        }
+    }
     unsigned long long* dbg = a.dbg ? a.dbg + (size_t)cta * (L + 1) * ST_STAGES : nullptr;
 #define ST_T0() long long t0_ = timing ? clock64() : 0
 #define ST_T1(layer, stage)                                                         \
@@ -514,8 +532,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
         }                                                                           \
     } while (0)
 
-    auto tag32_of = [&](int step, int layer) { return epoch0 + (uint32_t)(step * (L + 1) + layer) + 1u; };
-    auto tag16_of = [&](int step, int layer) { return ((epoch0 + (uint32_t)(step * (L + 1) + layer)) % 65535u) + 1u; };
+    // Tags: phase number p = epoch0 + step * (L + 1) + layer (layer L = the LM head); tag32 = p + 1,
+    // tag16 = p % 65535 + 1 (never 0), both advanced incrementally.
+    uint32_t t32 = epoch0 + 1u, t16 = epoch0 % 65535u + 1u, t16_prev = 0u;
+    auto next_tags = [&]() {
+        ++t32;
+        t16_prev = t16;
+        t16 = t16 == 65535u ? 1u : t16 + 1u;
+    };
 
     const int g = cta % NKV, s_idx = cta / NKV;     // attention item of this CTA
     const int n_od = 8 * pl.od_ng, n_a = 8 * pl.a_ng, n_gu = 8 * pl.gu_np;
@@ -526,7 +550,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
             const size_t head_off = ((size_t)(layer * NKV + g) * a.max_seq + ap.c0) * D;
             const bf16* ksrc = a.k_cache + head_off;
             const bf16* vsrc = a.v_cache + head_off;
-            for (int i = tid; i < ap.n_cached * 16; i += ST_CONSUMERS) {
+            for (int i = tid; i < ap.n_cached * 16; i += ST_THREADS) {
                 const int r = i >> 4, c = i & 15;
                 cp_async16(kt + (size_t)r * ST_KV_LD + c * 8, ksrc + (size_t)r * D + c * 8);
                 cp_async16(vt + (size_t)r * ST_KV_LD + c * 8, vsrc + (size_t)r * D + c * 8);
@@ -541,7 +565,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     for (int step = 0; step < a.n_steps; ++step) {
         const int pos = pos0 + step;
         const AttPlan ap = att_plan(cta, pos, a.max_split);
-        const uint32_t base_page = (uint32_t)step * pl.step_pages;
         if (cta == 0 && tid == 0 && (token < 0 || token >= a.vocab)) atomicOr(a.status, MQ_STATUS_BAD_TOKEN);
         token = min(max(token, 0), a.vocab - 1);
         const bf16* erow = a.embed + (size_t)token * H;
@@ -549,9 +572,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
         if (tid < n_od) resid = bf2f(erow[pl.od_row0 + tid]);
 
         for (int l = 0; l < L; ++l) {
-            const uint32_t t16 = tag16_of(step, l), t32 = tag32_of(step, l);
             const bf16* nrm = a.norms + (size_t)l * NORM_STRIDE;
-            const uint32_t lbase = (uint32_t)l * pl.layer_bytes;
             ST_T0();
 
             // ---------------- phase A: RMSNorm + rows of [Wq;Wk;Wv]
@@ -562,7 +583,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                     const uint2 u = __ldg(reinterpret_cast<const uint2*>(erow + 4 * tid));
                     v0 = bf_lo(u.x); v1 = bf_hi(u.x); v2 = bf_lo(u.y); v3 = bf_hi(u.y);
                 } else {
-                    const uint4 u = po.words4(xh + 4 * tid, tag16_of(step, l - 1));
+                    const uint4 u = po.words4(xh + 4 * tid, t16_prev);
                     v0 = bf_hi(u.x); v1 = bf_hi(u.y); v2 = bf_hi(u.z); v3 = bf_hi(u.w);
                 }
                 ST_T1(l, 0);
@@ -578,7 +599,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                 o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
                 *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
                 consumer_bar();
-                gemv_phase<8>(rg, base_page, lbase + pl.off_a, pl.a_ng >> 1, pl.a_ng & 1, xs, red, warp, lane);
+                gemv_phase(rg, pl.a_ng >> 1, pl.a_ng & 1, H / 8, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_a) {
                     float s = 0.f;
@@ -785,10 +806,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             // ---------------- phase C: rows of Wo + residual
             if (n_od > 0) {
-                poll_vector<2>(po, xattn, t16, xs, tid);
+                poll_slice<2>(po, xattn, t16, xs, warp, lane);      // this warp's 256 columns
                 ST_T1(l, 5);
-                consumer_bar();
-                gemv_phase<16>(rg, base_page, lbase + pl.off_o, pl.od_ng >> 1, pl.od_ng & 1, xs, red, warp, lane);
+                gemv_phase(rg, pl.od_ng >> 1, pl.od_ng & 1, QSZ / 8, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_od) {
                     float s = 0.f;
@@ -818,7 +838,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                 o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
                 *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
                 consumer_bar();
-                gemv_phase<8>(rg, base_page, lbase + pl.off_gu, pl.gu_np, 0, xs, red, warp, lane);
+                gemv_phase(rg, pl.gu_np, 0, H / 8, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_gu) {
                     const int t = tid >> 3, i = tid & 7;
@@ -836,10 +856,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             // ---------------- phase E: rows of Wd + residual
             if (n_od > 0) {
-                poll_vector<3>(po, xact, t16, xs, tid);
+                poll_slice<3>(po, xact, t16, xs, warp, lane);       // this warp's 384 columns
                 ST_T1(l, 9);
-                consumer_bar();
-                gemv_phase<24>(rg, base_page, lbase + pl.off_d, pl.od_ng >> 1, pl.od_ng & 1, xs, red, warp, lane);
+                gemv_phase(rg, pl.od_ng >> 1, pl.od_ng & 1, I / 8, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_od) {
                     float s = 0.f;
@@ -850,14 +869,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                 }
                 ST_T1(l, 10);
             }
+            next_tags();
         }
 
         // ---------------- final RMSNorm + LM head tiles + arg-max
         {
             ST_T0();
-            const uint32_t t32 = tag32_of(step, L);
             const uint2 wv = __ldg(reinterpret_cast<const uint2*>(a.final_norm + 4 * tid));
-            const uint4 u = po.words4(xh + 4 * tid, tag16_of(step, L - 1));
+            const uint4 u = po.words4(xh + 4 * tid, t16_prev);
             const float v0 = bf_hi(u.x), v1 = bf_hi(u.y), v2 = bf_hi(u.z), v3 = bf_hi(u.w);
             ST_T1(L, 11);
             const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
@@ -875,21 +894,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             float* lg = nullptr;
             if (a.logits && (a.logits_all || step == a.n_steps - 1)) lg = a.logits + (a.logits_all ? (size_t)step * a.vocab : 0);
-            const uint32_t lm_off = (uint32_t)L * pl.layer_bytes;
-            const uint32_t xa = smem_u32(xs) + (uint32_t)(lane & 3) * 4u;
+            // a warp owns whole tiles (tiles warp, warp + 8, .. of the CTA): 16 units of 4 k-steps each
+            const uint32_t xl = smem_u32(xs) + (uint32_t)(lane & 3) * 32u;
             unsigned long long best = 0ull;
+#pragma unroll 1
             for (int j = warp; j < pl.lm_nt; j += ST_WARPS) {
                 float c[4][4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
-                const uint32_t toff = lm_off + (uint32_t)j * ST_LM_TILE_BYTES;
-#pragma unroll 8
-                for (int ks = 0; ks < 64; ++ks) {
-                    const uint32_t sa = rg.block(base_page, toff + (uint32_t)ks * 512u, lane);
-                    const uint4 av = lds128(sa + lane * 16);
-                    const uint32_t af[4] = {av.x, av.y, av.z, av.w};
-                    mma16816(c[ks & 3], af, lds32(xa + ks * 32u), lds32(xa + ks * 32u + 16u));
-                }
+#pragma unroll 1
+                for (int i = 0; i < ST_LM_TILE_UNITS; ++i) full_unit(rg, c, xl + (uint32_t)i * 128u, lane);
                 if ((lane & 3) == 0) {
                     const float lo = rbf((c[0][0] + c[1][0]) + (c[2][0] + c[3][0]));
                     const float hi = rbf((c[0][2] + c[1][2]) + (c[2][2] + c[3][2]));
@@ -906,7 +920,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                     }
                 }
             }
-            rg.advance_to((uint32_t)(step + 1) * pl.step_pages, lane);     // leave the step's last pages
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) {
                 const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, off);
@@ -948,93 +961,93 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
             if (a.forced && step + 1 < a.n_steps) token = ld_cg_i32(a.forced + step + 1);
             ST_T1(L, 13);
         }
+        next_tags();
     }
-    if (timing) dbg[(size_t)L * ST_STAGES + 15] += rg.wait_cycles;
     if (cta == 0 && tid == 0) st_relaxed_u32(epoch, epoch0 + (uint32_t)(a.n_steps * (L + 1)));
+    // a kernel that is draining after an expired wait may still have bulk copies on their way to
+    // this CTA's shared memory: give them time to land before the memory is handed back
+    if (ld_relaxed_u32(a.status) & MQ_STATUS_WAIT_TIMEOUT)
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
 #undef ST_T0
 #undef ST_T1
 }
 
 // ------------------------------------------------------------------ weight packing
-// Writes CTA `blockIdx.x`'s segment of one layer: every 32-bit word of the segment is two
-// adjacent bf16 of one weight row, placed where the mma A fragment of its (tile, k-step) block
-// expects them: lane = 4 (row % 8) + (col % 8) / 2; register a0 (rows 0-7, cols 0-7),
-// a1 (rows 8-15, cols 0-7), a2 (rows 0-7, cols 8-15), a3 (rows 8-15, cols 8-15).
+// Every 32-bit word of a warp's stream is two adjacent bf16 of one weight row, placed where the
+// mma A fragment of its block expects them (layout: see gemv_phase).
 __device__ __forceinline__ uint32_t pack_word(const bf16* W, int ld, int row, int col) {
     return *reinterpret_cast<const uint32_t*>(W + (size_t)row * ld + col);
 }
 
-// row of tile-row i (0..15) of tile t in a phase -> (matrix, row index)
-struct RowSrc { const bf16* W; int row; };
+// (row within the tile, column) of word `wd` (0..511) of a unit; warp_col0 = first column of the warp
+__device__ __forceinline__ void unit_word_pos(bool full_tile, int unit_in_tile, int warp_col0, uint32_t wd, int& trow, int& col) {
+    const int blk = (int)(wd >> 7), ln = (int)((wd & 127u) >> 2), reg = (int)(wd & 3u);
+    const int g = ln >> 2, tig = ln & 3;
+    if (full_tile) {
+        trow = g + ((reg & 1) ? 8 : 0);
+        col = warp_col0 + 64 * unit_in_tile + 16 * tig + 4 * blk + ((reg & 2) ? 2 : 0);
+    } else {
+        trow = g;
+        col = warp_col0 + 128 * unit_in_tile + 32 * tig + 8 * blk + 2 * reg;
+    }
+}
 
-__global__ void k_pack_layer(const StPlan* plans, MqLayerWeights w, uint8_t* packed, int layer) {
+// grid (CTAs, 8 warps, z); one layer of one warp's stream per (x, y)
+__global__ void k_pack_layer(const StPlan* plans, MqLayerWeights w, uint8_t* packed, int layer, int num_layers) {
     const StPlan pl = plans[blockIdx.x];
-    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + (size_t)layer * pl.layer_bytes);
-    const uint32_t nwords = pl.layer_bytes / 4;
-    for (uint32_t wd = blockIdx.y * blockDim.x + threadIdx.x; wd < nwords; wd += gridDim.y * blockDim.x) {
-        const uint32_t off = wd * 4;
-        // which phase
-        int phase;
-        uint32_t poff;
-        if (off >= pl.off_d) { phase = 3; poff = off - pl.off_d; }
-        else if (off >= pl.off_gu) { phase = 2; poff = off - pl.off_gu; }
-        else if (off >= pl.off_o) { phase = 1; poff = off - pl.off_o; }
-        else { phase = 0; poff = off - pl.off_a; }
-        const int K = phase == 1 ? QSZ : phase == 3 ? I : H;
-        const uint32_t KS = (uint32_t)K / 16;
-        const int ng = phase == 0 ? pl.a_ng : phase == 2 ? 2 * pl.gu_np : pl.od_ng;   // 8-row groups
-        const int ntf = ng >> 1, nh = ng & 1;
-        const uint32_t full_bytes = KS * (uint32_t)ntf * 512u;
-        uint32_t value = 0u;
-        int trow = -1, tile = 0, col = 0;      // row within the tile (0..15), tile, first column
-        if (poff < full_bytes) {
-            const uint32_t blk = poff / 512u, inb = poff % 512u;
-            const uint32_t ks = blk / (uint32_t)ntf;
-            tile = (int)(blk % (uint32_t)ntf);
-            const int ln = (int)(inb / 16u), reg = (int)((inb % 16u) / 4u);
-            trow = (ln >> 2) + ((reg & 1) ? 8 : 0);
-            col = (int)ks * 16 + 2 * (ln & 3) + ((reg & 2) ? 8 : 0);
-        } else if (nh && poff < full_bytes + KS * 256u) {
-            const uint32_t p2 = poff - full_bytes;
-            const uint32_t ks = p2 / 256u, inb = p2 % 256u;
-            tile = ntf;
-            const int ln = (int)(inb / 8u), reg = (int)((inb % 8u) / 4u);
-            trow = ln >> 2;
-            col = (int)ks * 16 + 2 * (ln & 3) + (reg ? 8 : 0);
+    const int warp = blockIdx.y;
+    size_t woff = 0;
+    for (int v = 0; v < warp; ++v) woff += (size_t)st_step_units(pl, v, num_layers) * ST_UNIT;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + woff + (size_t)layer * pl.layer_units * ST_UNIT);
+    const uint32_t nwords = pl.layer_units * (ST_UNIT / 4);
+    // units of the four phases, in stream order
+    const int ng[4] = {pl.a_ng, pl.od_ng, 2 * pl.gu_np, pl.od_ng};
+    const int Ks[4] = {H, QSZ, H, I};
+    for (uint32_t wi = blockIdx.z * blockDim.x + threadIdx.x; wi < nwords; wi += gridDim.z * blockDim.x) {
+        uint32_t unit = wi / (ST_UNIT / 4);
+        const uint32_t wd = wi % (ST_UNIT / 4);
+        int phase = 0;
+        while (phase < 3 && unit >= st_phase_units(Ks[phase], ng[phase])) { unit -= st_phase_units(Ks[phase], ng[phase]); ++phase; }
+        const int K = Ks[phase], kw = K / 8;
+        const int ntf = ng[phase] >> 1;
+        const uint32_t upt = (uint32_t)(kw / 64);                 // units per full tile
+        const bool full_tile = unit < (uint32_t)ntf * upt;
+        const int tile = full_tile ? (int)(unit / upt) : ntf;
+        const int uit = full_tile ? (int)(unit % upt) : (int)(unit - (uint32_t)ntf * upt);
+        int trow, col;
+        unit_word_pos(full_tile, uit, warp * kw, wd, trow, col);
+        const bf16* W;
+        int row;
+        if (phase == 0) {
+            const int r = pl.a_row0 + tile * 16 + trow;
+            if (r < QSZ) { W = (const bf16*)w.q_proj; row = r; }
+            else if (r < QSZ + KVSZ) { W = (const bf16*)w.k_proj; row = r - QSZ; }
+            else { W = (const bf16*)w.v_proj; row = r - QSZ - KVSZ; }
+        } else if (phase == 2) {
+            W = trow < 8 ? (const bf16*)w.gate_proj : (const bf16*)w.up_proj;
+            row = pl.gu_row0 + tile * 8 + (trow & 7);
+        } else {
+            W = phase == 1 ? (const bf16*)w.o_proj : (const bf16*)w.down_proj;
+            row = pl.od_row0 + tile * 16 + trow;
         }
-        if (trow >= 0) {
-            const bf16* W;
-            int row;
-            if (phase == 0) {
-                const int r = pl.a_row0 + tile * 16 + trow;
-                if (r < QSZ) { W = (const bf16*)w.q_proj; row = r; }
-                else if (r < QSZ + KVSZ) { W = (const bf16*)w.k_proj; row = r - QSZ; }
-                else { W = (const bf16*)w.v_proj; row = r - QSZ - KVSZ; }
-            } else if (phase == 2) {
-                W = trow < 8 ? (const bf16*)w.gate_proj : (const bf16*)w.up_proj;
-                row = pl.gu_row0 + tile * 8 + (trow & 7);
-            } else {
-                W = phase == 1 ? (const bf16*)w.o_proj : (const bf16*)w.down_proj;
-                row = pl.od_row0 + tile * 16 + trow;
-            }
-            value = pack_word(W, K, row, col);
-        }
-        dst[wd] = value;       // padding between phases is zero
+        dst[wi] = pack_word(W, K, row, col);
     }
 }
 
 __global__ void k_pack_lm(const StPlan* plans, const bf16* lm_head, uint8_t* packed, int num_layers, int vocab) {
     const StPlan pl = plans[blockIdx.x];
-    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + (size_t)num_layers * pl.layer_bytes);
-    const uint32_t nwords = (uint32_t)pl.lm_nt * (ST_LM_TILE_BYTES / 4);
-    for (uint32_t wd = blockIdx.y * blockDim.x + threadIdx.x; wd < nwords; wd += gridDim.y * blockDim.x) {
-        const uint32_t off = wd * 4;
-        const uint32_t tile = off / ST_LM_TILE_BYTES, intile = off % ST_LM_TILE_BYTES;
-        const uint32_t ks = intile / 512u, inb = intile % 512u;
-        const int ln = (int)(inb / 16u), reg = (int)((inb % 16u) / 4u);
-        const int row = pl.lm_row0 + (int)tile * 16 + (ln >> 2) + ((reg & 1) ? 8 : 0);
-        const int col = (int)ks * 16 + 2 * (ln & 3) + ((reg & 2) ? 8 : 0);
-        dst[wd] = row < vocab ? pack_word(lm_head, H, row, col) : 0u;
+    const int warp = blockIdx.y;
+    size_t woff = 0;
+    for (int v = 0; v < warp; ++v) woff += (size_t)st_step_units(pl, v, num_layers) * ST_UNIT;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + woff + (size_t)num_layers * pl.layer_units * ST_UNIT);
+    const uint32_t nwords = st_lm_tiles(pl, warp) * ST_LM_TILE_UNITS * (ST_UNIT / 4);
+    for (uint32_t wi = blockIdx.z * blockDim.x + threadIdx.x; wi < nwords; wi += gridDim.z * blockDim.x) {
+        const uint32_t unit = wi / (ST_UNIT / 4), wd = wi % (ST_UNIT / 4);
+        const int k = (int)(unit / ST_LM_TILE_UNITS), uit = (int)(unit % ST_LM_TILE_UNITS);
+        int trow, col;
+        unit_word_pos(true, uit, 0, wd, trow, col);
+        const int row = pl.lm_row0 + (warp + ST_WARPS * k) * 16 + trow;
+        dst[wi] = row < vocab ? pack_word(lm_head, H, row, col) : 0u;
     }
 }
 
@@ -1046,47 +1059,42 @@ __global__ void k_pack_norms(MqLayerWeights w, bf16* dst) {
 
 // ------------------------------------------------------------------ host side
 static size_t st_smem_bytes() {
-    return (size_t)ST_NSLOT * ST_PAGE + (size_t)2 * ST_KV_CAP * ST_KV_LD * 2 + (size_t)I * 2 + (size_t)ST_WARPS * ST_RED_ROWS * 4 +
-           (4 * D + 2 * D + ST_WARPS * 32 + 4 * D) * 2 + (16 + 16 + 4 + 8 + 4) * 4 + ST_WARPS * 8 + 2 * ST_NSLOT * 8 + 16;
+    return (size_t)ST_WARPS * ST_NSLOT * ST_UNIT + (size_t)2 * ST_KV_CAP * ST_KV_LD * 2 + (size_t)I * 2 + (size_t)ST_WARPS * ST_RED_ROWS * 4 +
+           (4 * D + 2 * D + ST_WARPS * 32 + 4 * D) * 2 + (16 + 16 + 4 + 8 + 4) * 4 + ST_WARPS * 8 + ST_WARPS * ST_NSLOT * 8 + 16;
 }
 
 constexpr size_t ST_HDR_PLANS = 0;
 static size_t st_hdr_norms() { return ((size_t)ST_MAX_GRID * sizeof(StPlan) + 255) & ~(size_t)255; }
 static size_t st_hdr_bytes(int num_layers) {
-    return (st_hdr_norms() + (size_t)num_layers * NORM_STRIDE * 2 + ST_PAGE - 1) / ST_PAGE * ST_PAGE;
+    return (st_hdr_norms() + (size_t)num_layers * NORM_STRIDE * 2 + 4095) / 4096 * 4096;
 }
 
-// Deals the rows out so that every CTA streams (almost) the same number of bytes per layer.
-// Units of 8 rows x 1024 columns (16 KB): a q|k|v group 1, a gate/up pair 2, a Wo group 2, a Wd
-// group 3; 1920 units in all.  CTAs 0..127 own one Wo/Wd group each (the same rows, so that the
-// residual of those rows stays in a register); gate/up pairs go one at a time to the CTA with
-// the most room left, q|k|v groups fill what remains.
+// Deals the rows out.  A step is bound by its chain of dependent phases, not by a CTA's total
+// bytes: every phase lasts as long as its most loaded CTA, so each phase is spread as evenly
+// as its granularity allows (8-row groups of q|k|v, 8 + 8-row gate/up pairs, 8-row groups of
+// Wo / Wd): 3-4 + 1 + 2-3 + 1 on 148 SMs.  CTAs 0..127 own one Wo/Wd group each (the same
+// rows in both, so that the residual of those rows stays in a register); the CTAs without one
+// take the larger shares of the other two phases.
 static int st_make_plans(int grid, int num_layers, int vocab, std::vector<StPlan>& plans, size_t* total_bytes) {
     if (grid < ST_MIN_GRID || grid > ST_MAX_GRID) return MQ_ERR_UNSUPPORTED;
     const int n_od = H / 8, n_a = QKV / 8, n_gu = I / 8;
     plans.assign(grid, StPlan{});
-    std::vector<int> room(grid), pairs(grid, 0), od(grid, 0), ag(grid, 0);
-    const int total_units = n_a + 2 * n_gu + 5 * n_od;
-    const int target = (total_units + grid - 1) / grid;
+    std::vector<int> pairs(grid, 0), od(grid, 0), ag(grid, 0);
+    for (int c = 0; c < grid; ++c) od[c] = c < n_od ? 1 : 0;
+    // the larger shares go to the highest-numbered CTAs first (those without Wo / Wd rows)
     for (int c = 0; c < grid; ++c) {
-        od[c] = c < n_od ? 1 : 0;
-        room[c] = target - 5 * od[c];
+        pairs[c] = n_gu / grid + (grid - 1 - c < n_gu % grid ? 1 : 0);
+        ag[c] = n_a / grid;
     }
-    for (int p = 0; p < n_gu; ++p) {
-        int bestc = 0;
-        for (int c = 1; c < grid; ++c)
-            if (room[c] > room[bestc]) bestc = c;
-        if (room[bestc] < 2 || pairs[bestc] >= ST_MAX_TILES) return MQ_ERR_UNSUPPORTED;
-        pairs[bestc] += 1;
-        room[bestc] -= 2;
-    }
-    int left = n_a;
-    for (int c = 0; c < grid && left > 0; ++c) {
-        const int take = room[c] < left ? room[c] : left;
-        ag[c] = take > 0 ? take : 0;
-        left -= ag[c];
-    }
-    if (left > 0) return MQ_ERR_UNSUPPORTED;
+    // q|k|v extras: prefer CTAs that did not get an extra gate/up pair, from the top down
+    int extra = n_a % grid;
+    for (int pass = 0; pass < 2 && extra > 0; ++pass)
+        for (int c = grid - 1; c >= 0 && extra > 0; --c) {
+            const bool has_extra_pair = pairs[c] > n_gu / grid;
+            if (ag[c] == n_a / grid && (pass == 1 || !has_extra_pair || od[c] == 0)) { ag[c] += 1; --extra; }
+        }
+    for (int c = 0; c < grid; ++c)
+        if (pairs[c] > ST_MAX_TILES) return MQ_ERR_UNSUPPORTED;
     const int lm_tiles = (vocab + 15) / 16;
     int a_next = 0, od_next = 0, gu_next = 0, lm_next = 0;
     size_t off = st_hdr_bytes(num_layers);
@@ -1098,17 +1106,9 @@ static int st_make_plans(int grid, int num_layers, int vocab, std::vector<StPlan
         p.lm_nt = lm_tiles / grid + (c < lm_tiles % grid ? 1 : 0);
         p.lm_row0 = 16 * lm_next; lm_next += p.lm_nt;
         if (p.a_ng > 2 * ST_MAX_TILES || p.od_ng > 2) return MQ_ERR_UNSUPPORTED;
-        auto phase_bytes = [](int K, int ng) { return (uint32_t)(K / 16) * (uint32_t)((ng >> 1) * 512 + (ng & 1) * 256); };
-        auto up512 = [](uint32_t v) { return (v + 511u) & ~511u; };
-        p.off_a = 0;
-        p.off_o = up512(p.off_a + phase_bytes(H, p.a_ng));
-        p.off_gu = up512(p.off_o + phase_bytes(QSZ, p.od_ng));
-        p.off_d = up512(p.off_gu + phase_bytes(H, 2 * p.gu_np));
-        p.layer_bytes = up512(p.off_d + phase_bytes(I, p.od_ng));
-        p.step_bytes = (uint32_t)num_layers * p.layer_bytes + (uint32_t)p.lm_nt * ST_LM_TILE_BYTES;
-        p.step_pages = (p.step_bytes + ST_PAGE - 1) / ST_PAGE;
+        p.layer_units = st_layer_units(p);
         p.stream_off = off;
-        off += (size_t)p.step_pages * ST_PAGE;
+        for (int wv = 0; wv < ST_WARPS; ++wv) off += (size_t)st_step_units(p, wv, num_layers) * ST_UNIT;
     }
     if (a_next != n_a || od_next != n_od || gu_next != n_gu || lm_next != lm_tiles) return MQ_ERR_UNSUPPORTED;
     *total_bytes = off;
@@ -1149,6 +1149,7 @@ static int st_ensure_device(StDevice** out) {
 }  // namespace mq
 
 using namespace mq;
+
 
 extern "C" size_t mq_stream_scratch_bytes(void) { return SC_BYTES; }
 
@@ -1198,9 +1199,9 @@ extern "C" int mq_stream_pack(const MqModel* model, void* packed, size_t packed_
     bf16* norms = reinterpret_cast<bf16*>(base + st_hdr_norms());
     for (int l = 0; l < model->num_layers; ++l) {
         k_pack_norms<<<(H + 255) / 256, 256, 0, stream>>>(model->layers[l], norms + (size_t)l * NORM_STRIDE);
-        k_pack_layer<<<dim3(st->sm_count, 8), 256, 0, stream>>>(dplans, model->layers[l], base, l);
+        k_pack_layer<<<dim3(st->sm_count, ST_WARPS, 2), 256, 0, stream>>>(dplans, model->layers[l], base, l, model->num_layers);
     }
-    k_pack_lm<<<dim3(st->sm_count, 32), 256, 0, stream>>>(dplans, (const bf16*)model->lm_head, base, model->num_layers, model->vocab_size);
+    k_pack_lm<<<dim3(st->sm_count, ST_WARPS, 8), 256, 0, stream>>>(dplans, (const bf16*)model->lm_head, base, model->num_layers, model->vocab_size);
     return (int)cudaGetLastError();
 }
 

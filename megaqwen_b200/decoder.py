@@ -101,7 +101,9 @@ class MegakernelDecoder:
             self._stream_scratch = torch.zeros(self._lib.mq_stream_scratch_bytes(), dtype=torch.uint8, device=dev)
             self._stream_max_context = self._lib.mq_stream_max_context()
             self.persistent_available = self._stream_max_context > 0
-            self.use_persistent = self.persistent_available
+            # opt-in: measured on B200 the graph-replayed per-phase kernels are still faster
+            # (389 vs 425 us/token at context 1, 477 vs 508 at 2048)
+            self.use_persistent = False
             self._chain_cap = 0
             self._chain_tokens = None
             self._chain_pos = None

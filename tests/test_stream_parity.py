@@ -85,11 +85,15 @@ def test_stream_is_deterministic_and_chains_like_single_launches(tiny):
     a = run(False)
     assert run(False) == a and run(True) == a
     assert dec.position() == len(prompt) - 1 + 40
-    # decode_steps (host in / out) takes the same path
+    # with use_persistent set, decode_steps (host in / out) takes the same path
     dec.reset()
     for t in prompt[:-1]:
         dec.decode_step(t)
-    assert dec.decode_steps(prompt[-1], 40).tolist() == a
+    dec.use_persistent = True
+    try:
+        assert dec.decode_steps(prompt[-1], 40).tolist() == a
+    finally:
+        dec.use_persistent = False
     # the per-phase kernels sum some reductions in another order: teacher-forced on their
     # sequence the persistent kernel predicts the same next token except at near-ties
     dec.reset()
@@ -165,7 +169,7 @@ def test_full_config1_stream_matches_hf_golden(full):
     dec.reset()
     for t in g["prompt"].tolist()[:-1]:
         dec.decode_step(t)
-    free = dec.decode_steps(int(g["prompt"][-1]), 64).tolist()
+    free = dec.decode_steps_cuda_persistent(int(g["prompt"][-1]), 64).tolist()
     agree = next((i for i, (x, y) in enumerate(zip(free, g["tokens"])) if x != y), 64)
     print("cfg1 free-running greedy agrees for", agree, "steps")
     assert agree >= 10
