@@ -217,6 +217,15 @@ typedef struct MqPrefillBuffers {
 int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pbuf,
                       const int* ids, int seq_len, int pos0, int* out_token, float* logits, void* stream);
 
+/* The same forward with rows audio_start .. audio_start + audio_len - 1 of the embedded prompt
+ * replaced by externally computed embeddings audio_embeds [audio_len, 1024] bf16 (device,
+ * 16-byte aligned) before the first layer: the hook the reference's speech front-end uses
+ * (prefill_asr, csrc/megakernel/bindings_prefill.cpp:835-955; patch kernel
+ * fused_prefill_kernels.inl:28-45).  The token ids of the replaced rows are ignored. */
+int mq_launch_prefill_asr(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pbuf,
+                          const int* ids, int seq_len, int pos0, const void* audio_embeds, int audio_start,
+                          int audio_len, int* out_token, float* logits, void* stream);
+
 /* State and scratch of a batch of independent sequences (no counterpart in the
  * reference, which is batch-1 only).  Sequence b owns the cache slice
  * [b][num_layers, 8, max_seq_len, 128]; a prefill of sequence b is an

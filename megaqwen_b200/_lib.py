@@ -74,6 +74,8 @@ SIGNATURES = {
                                           C.c_void_p, C.c_void_p]),
     "mq_launch_prefill": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.POINTER(MqPrefillBuffers), C.c_void_p,
                                     C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "mq_launch_prefill_asr": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.POINTER(MqPrefillBuffers), C.c_void_p,
+                                        C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "mq_launch_decode_batch": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers), C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_void_p]),
     "mq_launch_prefill_packed": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers)] + [C.c_void_p] * 7 +

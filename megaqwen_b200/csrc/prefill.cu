@@ -65,6 +65,32 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes
 // (64 elements) under the 128-byte swizzle: 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
@@ -415,11 +441,19 @@ __global__ void __launch_bounds__(256) k_sk_swiglu(const float* __restrict__ par
 
 // ---------------------------------------------------------------- row-wise kernels
 // h[s,:] = embed[ids[s],:]      (reference: prefill_embed_kernel, fused_prefill_kernels.inl:3-20)
+// Rows audio_start .. audio_start + audio_len - 1 take externally computed embeddings instead
+// (reference: prefill_patch_audio_kernel, fused_prefill_kernels.inl:28-45, a separate launch there).
 __global__ void __launch_bounds__(128) k_pf_embed(const int* __restrict__ ids, const bf16* __restrict__ embed, bf16* __restrict__ h,
-                                                  int vocab, unsigned int* status) {
+                                                  int vocab, unsigned int* status, const bf16* __restrict__ audio = nullptr,
+                                                  int audio_start = 0, int audio_len = 0) {
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     const int s = blockIdx.x;
+    if (audio != nullptr && s >= audio_start && s < audio_start + audio_len) {
+        reinterpret_cast<uint4*>(h + (size_t)s * H)[threadIdx.x] =
+            __ldg(reinterpret_cast<const uint4*>(audio + (size_t)(s - audio_start) * H) + threadIdx.x);
+        return;
+    }
     int tok = ids[s];
     if (tok < 0 || tok >= vocab) {
         if (threadIdx.x == 0) atomicOr(status, MQ_STATUS_BAD_TOKEN);
@@ -775,6 +809,264 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __re
         const int col = head * D + dt * 8 + (lane & 3) * 2;
         if (r_lo < S) *reinterpret_cast<uint32_t*>(out + (size_t)r_lo * QSZ + col) = pack_bf16x2(o[dt][0] * inv0, o[dt][1] * inv0);
         if (r_hi < S) *reinterpret_cast<uint32_t*>(out + (size_t)r_hi * QSZ + col) = pack_bf16x2(o[dt][2] * inv1, o[dt][3] * inv1);
+    }
+}
+
+// ---------------------------------------------------------------- causal attention on tcgen05 (one prompt)
+// One CTA per (query head, 128-query tile); key tiles of 128 positions.  Both contractions run
+// on the 5th-generation tensor cores with their accumulators in tensor memory:
+//     S = Q K^T     A = Q tile [128 q x 128 d], B = K tile [128 keys x 128 d] straight from the KV cache
+//     O_j = P V     A = P tile [128 q x 128 keys] (bf16, written by the softmax warps),
+//                   B = V^T tile [128 d x 128 keys] from a transposed copy of the layer's V rows
+// (all operands K-major under the 128-byte swizzle, fetched by TMA).  Warp 0 feeds the K / V^T
+// rings, warp 1 issues the MMAs, warps 2-5 hold ONE QUERY ROW PER THREAD: they read the row's
+// scores from tensor memory (tcgen05.ld), keep the running max / sum and write the probabilities
+// rounded to bf16 as the next MMA's A operand; the output accumulates in tensor memory and is
+// rescaled (tcgen05.ld / st) only when the maximum has grown by more than 2^8.  S is
+// double-buffered: QK^T of tile j + 1 runs while tile j is in the softmax.  Replaces the reference's serial-per-warp kernel and its experimental tiles
+// (csrc/megakernel/fused_prefill_kernels.inl:265-342, 347-445, 486-613).
+constexpr int TA_BQ = 128, TA_BK = 128;
+constexpr int TA_THREADS = 192;
+constexpr int TA_TILE_BYTES = 128 * 128 * 2;               // two 64-column halves of [128 rows x 128 bytes]
+constexpr int TA_HALF_BYTES = TA_TILE_BYTES / 2;
+constexpr size_t TA_SMEM = (size_t)7 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/;   // Q, 2 K, 2 V^T, 2 P
+constexpr uint32_t TA_TMEM_COLS = 512;                      // S0 | S1 | O (128 columns each)
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__global__ void __launch_bounds__(TA_THREADS, 1)
+k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmVt,
+                  bf16* __restrict__ out, int S, int pos0, int layer, int max_seq, unsigned int* status) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ uint8_t ta_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ta_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + TA_TILE_BYTES;            // [2]
+    uint8_t* sV = sK + 2 * TA_TILE_BYTES;        // [2]
+    uint8_t* sP = sV + 2 * TA_TILE_BYTES;        // [2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TA_TILE_BYTES);
+    uint64_t* q_full = bars;                     // 1
+    uint64_t* k_full = bars + 1;                 // 2
+    uint64_t* k_empty = bars + 3;                // 2
+    uint64_t* v_full = bars + 5;                 // 2
+    uint64_t* v_empty = bars + 7;                // 2
+    uint64_t* s_full = bars + 9;                 // 2
+    uint64_t* s_free = bars + 11;                // 2 (128 arrivals)
+    uint64_t* p_full = bars + 13;                // 2 (128 arrivals)
+    uint64_t* p_free = bars + 15;                // 2
+    uint64_t* o_full = bars + 17;                // 1
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int head = blockIdx.x, g = head / (NQ / NKV);
+    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * TA_BQ;        // longest query tiles first
+    const int kv_end = min(pos0 + S, pos0 + q0 + TA_BQ);                  // keys any row of the tile may see
+    const int nt = (kv_end + TA_BK - 1) / TA_BK;
+
+    if (tid == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128); mbar_init(&p_full[i], 128); mbar_init(&p_free[i], 1);
+        }
+        mbar_init(o_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TA_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    const uint32_t tmem_o = tmem_base + 256;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, TA_TILE_BYTES);
+            tma_load_2d(sQ, &tmQ, head * D, q0, q_full);
+            tma_load_2d(sQ + TA_HALF_BYTES, &tmQ, head * D + 64, q0, q_full);
+            const int krow0 = (layer * NKV + g) * max_seq;
+            for (int j = 0; j < nt; ++j) {
+                const int st = j & 1;
+                if (j >= 2 && !mbar_wait(&k_empty[st], (uint32_t)((j >> 1) - 1) & 1u, status)) break;
+                mbar_expect_tx(&k_full[st], TA_TILE_BYTES);
+                tma_load_2d(sK + st * TA_TILE_BYTES, &tmK, 0, krow0 + j * TA_BK, &k_full[st]);
+                tma_load_2d(sK + st * TA_TILE_BYTES + TA_HALF_BYTES, &tmK, 64, krow0 + j * TA_BK, &k_full[st]);
+                if (j >= 2 && !mbar_wait(&v_empty[st], (uint32_t)((j >> 1) - 1) & 1u, status)) break;
+                mbar_expect_tx(&v_full[st], TA_TILE_BYTES);
+                tma_load_2d(sV + st * TA_TILE_BYTES, &tmVt, j * TA_BK, g * D, &v_full[st]);
+                tma_load_2d(sV + st * TA_TILE_BYTES + TA_HALF_BYTES, &tmVt, j * TA_BK + 64, g * D, &v_full[st]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            bool ok = mbar_wait(q_full, 0, status);
+            auto issue_s = [&](int j) {      // S[j & 1] = Q K_j^T
+                const int st = j & 1;
+                ok = ok && mbar_wait(&k_full[st], (uint32_t)(j >> 1) & 1u, status);
+                if (j >= 2) ok = ok && mbar_wait(&s_free[st], (uint32_t)((j >> 1) - 1) & 1u, status);
+                tc_fence_after();
+                if (ok) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint64_t da = smem_desc_sw128(sQ + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
+                        const uint64_t db = smem_desc_sw128(sK + st * TA_TILE_BYTES + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
+                        umma_bf16(tmem_base + st * 128, da, db, idesc, kk > 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(&k_empty[st]);
+                umma_commit(&s_full[st]);
+            };
+            issue_s(0);
+            for (int j = 0; j < nt; ++j) {
+                const int st = j & 1;
+                if (j + 1 < nt) issue_s(j + 1);
+                ok = ok && mbar_wait(&p_full[st], (uint32_t)(j >> 1) & 1u, status);
+                ok = ok && mbar_wait(&v_full[st], (uint32_t)(j >> 1) & 1u, status);
+                tc_fence_after();
+                if (ok) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint64_t da = smem_desc_sw128(sP + st * TA_TILE_BYTES + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
+                        const uint64_t db = smem_desc_sw128(sV + st * TA_TILE_BYTES + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
+                        umma_bf16(tmem_o, da, db, idesc, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates over all key tiles
+                    }
+                }
+                umma_commit(&v_empty[st]);
+                umma_commit(&p_free[st]);
+                umma_commit(o_full);
+            }
+        }
+        __syncwarp();
+    } else {
+        // softmax warps: thread owns query row r = TMEM lane r.  The output accumulates in tensor
+        // memory over all key tiles; it is only rescaled when the running maximum has grown by more
+        // than 2^8 since the value the accumulator is scaled to (then p <= 256 in between, exact in
+        // fp32 and harmless in bf16), which after the first tiles practically never happens.
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const int qpos = pos0 + q0 + r;                       // absolute position of this thread's query
+        const float c = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+        float m = -INFINITY, l = 0.f;                         // m: the maximum the sums are scaled to (raw score units)
+        bool ok = true;
+        for (int j = 0; j < nt; ++j) {
+            const int st = j & 1;
+            const uint32_t ts = tmem_base + st * 128 + lane_off;
+            ok = ok && mbar_wait(&s_full[st], (uint32_t)(j >> 1) & 1u, status);
+            tc_fence_after();
+            const int k0 = j * TA_BK;
+            const bool diag = k0 + TA_BK - 1 > qpos;          // some keys of this tile lie beyond the query
+            uint32_t sv[128];
+#pragma unroll
+            for (int cb = 0; cb < 4; ++cb) tmem_ld32_nowait(ts + cb * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cb * 32]));
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&s_free[st]);                         // the scores are in registers: S[st] may be overwritten
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; ++i) {
+                if (diag && k0 + i > qpos) sv[i] = 0xff800000u;   // -inf
+                mx = fmaxf(mx, __uint_as_float(sv[i]));
+            }
+            // tcgen05.ld / st are warp-wide: the warp rescales together, rows that need none by 1
+            const bool grow = (mx - m) * c > 8.0f;            // also true for the first tile (m = -inf)
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? fast_exp2((m - mx) * c) : 1.0f;   // 0 for the first tile
+                if (j > 0) {
+                    // the previous P V product must have landed before the accumulator is touched
+                    ok = ok && mbar_wait(o_full, (uint32_t)(j - 1) & 1u, status);
+                    tc_fence_after();
+#pragma unroll
+                    for (int cb = 0; cb < 4; ++cb) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_o + lane_off + cb * 32, v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st32(tmem_o + lane_off + cb * 32, v);
+                    }
+                    tc_fence_before();
+                }
+                l *= alpha;
+                if (grow) m = mx;
+            }
+            const float mc = m * c;
+            if (j >= 2) ok = ok && mbar_wait(&p_free[st], (uint32_t)((j >> 1) - 1) & 1u, status);
+            // probabilities -> bf16 -> A operand of the P V product (K-major, 128-byte swizzle)
+            float rs = 0.f;
+            uint8_t* prow = sP + st * TA_TILE_BYTES + r * 128;
+#pragma unroll
+            for (int c16 = 0; c16 < 16; ++c16) {              // 16-byte chunk = 8 keys
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c16 * 8 + 2 * e]), c, -mc));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c16 * 8 + 2 * e + 1]), c, -mc));
+                    rs += p0 + p1;
+                    pk[e] = pack_bf16x2(p0, p1);
+                }
+                uint8_t* dst = prow + (c16 >> 3) * TA_HALF_BYTES + (((c16 & 7) ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            l += rs;
+            fence_async_smem();                               // the tensor core reads P through the async proxy
+            mbar_arrive(&p_full[st]);
+        }
+        // the last P V product, then out = O / l
+        ok = ok && mbar_wait(o_full, (uint32_t)(nt - 1) & 1u, status);
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        bf16* orow = out + (size_t)(q0 + r) * QSZ + head * D;
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb) {
+            uint32_t v[32];
+            tmem_ld32(tmem_o + lane_off + cb * 32, v);
+            if (q0 + r < S) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    reinterpret_cast<uint4*>(orow + cb * 32)[q] =
+                        make_uint4(pack_bf16x2(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv),
+                                   pack_bf16x2(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv),
+                                   pack_bf16x2(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv),
+                                   pack_bf16x2(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv));
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TA_TMEM_COLS);
+}
+
+// vt[g][d][key] = v_cache[layer][g][key][d] for key < n_keys, zero up to key_pad (the B operand of
+// the P V product must be K-major, i.e. contiguous along the keys).  grid (key_pad / 64, 8).
+__global__ void __launch_bounds__(256) k_pf_transpose_v(const bf16* __restrict__ v_cache, bf16* __restrict__ vt, int layer, int max_seq,
+                                                        int n_keys, int key_pad) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ bf16 tile[64][D + 2];
+    const int g = blockIdx.y, key0 = blockIdx.x * 64;
+    const bf16* src = v_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
+    for (int i = threadIdx.x; i < 64 * (D / 2); i += 256) {
+        const int k = i / (D / 2), dp = i % (D / 2);
+        const uint32_t u = key0 + k < n_keys ? *reinterpret_cast<const uint32_t*>(src + (size_t)(key0 + k) * D + 2 * dp) : 0u;
+        *reinterpret_cast<uint32_t*>(&tile[k][2 * dp]) = u;
+    }
+    __syncthreads();
+    const int d = threadIdx.x >> 1, kh = threadIdx.x & 1;
+    bf16* dst = vt + ((size_t)(g * D + d)) * key_pad + key0 + 32 * kh;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = 32 * kh + 8 * q + 2 * e;
+            const uint16_t a = *reinterpret_cast<const uint16_t*>(&tile[k][d]), b = *reinterpret_cast<const uint16_t*>(&tile[k + 1][d]);
+            w[e] = (uint32_t)a | ((uint32_t)b << 16);
+        }
+        *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -1148,7 +1440,7 @@ __global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restri
 using namespace mq;
 
 // kernels of one prefill (at most: the split-K path needs one norm kernel fewer per layer after the first)
-extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 8 + 2; }
+extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 9 + 2; }
 
 // C[M,N] = A[M,K] * B[N,K]^T on the tcgen05 path (bf16 in/out, fp32 accumulate);
 // optional residual R (same shape and leading dimension as C, may alias C).
@@ -1160,8 +1452,26 @@ extern "C" int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* 
     return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream);
 }
 
+static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,
+                        int seq_len, int pos0, const bf16* audio, int audio_start, int audio_len, int* out_token, float* logits,
+                        void* stream_v);
+
 extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,
                                  int seq_len, int pos0, int* out_token, float* logits, void* stream_v) {
+    return prefill_impl(model, dbuf, pb, ids, seq_len, pos0, nullptr, 0, 0, out_token, logits, stream_v);
+}
+
+extern "C" int mq_launch_prefill_asr(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,
+                                     int seq_len, int pos0, const void* audio_embeds, int audio_start, int audio_len,
+                                     int* out_token, float* logits, void* stream_v) {
+    if (!audio_embeds || audio_len <= 0 || audio_start < 0 || audio_start + audio_len > seq_len) return MQ_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(audio_embeds) & 15u) != 0) return MQ_ERR_ALIGNMENT;
+    return prefill_impl(model, dbuf, pb, ids, seq_len, pos0, (const bf16*)audio_embeds, audio_start, audio_len, out_token, logits, stream_v);
+}
+
+static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,
+                        int seq_len, int pos0, const bf16* audio, int audio_start, int audio_len, int* out_token, float* logits,
+                        void* stream_v) {
     if (!model || !dbuf || !pb || !ids || !out_token) return MQ_ERR_BAD_ARG;
     if (!pb->h || !pb->x || !pb->qkv || !pb->attn || !pb->act) return MQ_ERR_BAD_ARG;
     if (seq_len <= 0 || pos0 < 0) return MQ_ERR_BAD_ARG;
@@ -1179,7 +1489,25 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         if (e != cudaSuccess) return (int)e;
         fa_attr[dev] = true;
     }
-    launch_pdl(k_pf_embed, dim3(S), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status);
+    // From 128 prompt rows on the attention runs on tcgen05; it needs a transposed copy of the layer's V rows
+    // (8 x 128 x key_pad bf16), which lives in the MLP activation buffer until the gate/up GEMM overwrites it.
+    const int key_pad = (pos0 + S + TA_BK - 1) / TA_BK * TA_BK;
+    const bool use_tc = S >= TA_BQ && (size_t)key_pad * KVSZ <= (size_t)pb->max_tokens * I;
+    CUtensorMap map_q, map_k, map_vt;
+    if (use_tc) {
+        static bool ta_attr[64] = {false};
+        if (dev >= 0 && dev < 64 && !ta_attr[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(k_pf_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TA_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            ta_attr[dev] = true;
+        }
+        int mrc = get_map(qkv, (uint64_t)S, (uint64_t)QKV, (uint64_t)QKV, TA_BQ, &map_q);
+        if (mrc == MQ_OK) mrc = get_map(dbuf->k_cache, (uint64_t)model->num_layers * NKV * model->max_seq_len, (uint64_t)D, (uint64_t)D, TA_BK, &map_k);
+        if (mrc == MQ_OK) mrc = get_map(act, (uint64_t)KVSZ, (uint64_t)key_pad, (uint64_t)key_pad, D, &map_vt);
+        if (mrc != MQ_OK) return mrc;
+    }
+    launch_pdl(k_pf_embed, dim3(S), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status, audio,
+               audio_start, audio_len);
     int rc;
     const bool big = S >= 1024;
     // Between 512 and 1024 rows the N = 1024 projections (O, down) split K over two CTAs per 128 x 128 tile:
@@ -1204,8 +1532,16 @@ extern "C" int mq_launch_prefill(const MqModel* model, const MqDecodeBuffers* db
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0, nullptr, 0, 0, nullptr);
-        launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache, (const bf16*)dbuf->v_cache,
-                                                                                          attn, S, pos0, l, model->max_seq_len, PackedTiles());
+        if (use_tc) {
+            // V^T of this layer's keys goes into the (still unused) MLP activation buffer
+            launch_pdl(k_pf_transpose_v, dim3(key_pad / 64, NKV), dim3(256), 0, stream, (const bf16*)dbuf->v_cache, act, l, model->max_seq_len,
+                       pos0 + S, key_pad);
+            launch_pdl(k_pf_attention_tc, dim3(NQ, (S + TA_BQ - 1) / TA_BQ), dim3(TA_THREADS), TA_SMEM, stream, map_q, map_k, map_vt, attn, S, pos0, l,
+                       model->max_seq_len, status);
+        } else {
+            launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache,
+                       (const bf16*)dbuf->v_cache, attn, S, pos0, l, model->max_seq_len, PackedTiles());
+        }
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
         if (splitk) {
             rc = launch_gemm<128, EPI_PARTIAL>(attn, QSZ, (const bf16*)w.o_proj, nullptr, (bf16*)part, nullptr, S, H, QSZ, H, status, stream,
@@ -1270,7 +1606,8 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
     }
     PackedTiles pt;
     pt.tile_seq = tile_seq; pt.tile_q0 = tile_q0; pt.seq_len = seq_len; pt.seq_row0 = seq_row0; pt.seq_stride = seq_stride;
-    launch_pdl(k_pf_embed, dim3(T), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status);
+    launch_pdl(k_pf_embed, dim3(T), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status,
+               (const bf16*)nullptr, 0, 0);
     int rc;
     const bool big = T >= 1024;
     for (int l = 0; l < model->num_layers; ++l) {
@@ -1333,7 +1670,8 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
             bd_attr[dev] = true;
         }
     }
-    launch_pdl(k_pf_embed, dim3(B), dim3(128), 0, stream, in_tokens, (const bf16*)model->embed, h, model->vocab_size, status);
+    launch_pdl(k_pf_embed, dim3(B), dim3(128), 0, stream, in_tokens, (const bf16*)model->embed, h, model->vocab_size, status,
+               (const bf16*)nullptr, 0, 0);
     int rc;
     const size_t need_part = (size_t)4 * B * 2 * I * sizeof(float);   // largest partial: gate|up, 4 K-splits
     const bool skinny = B <= 64 && bb->partials != nullptr && bb->partials_bytes >= need_part;

@@ -425,7 +425,27 @@ class MegakernelDecoder:
         self._check_prefill(ids, self.position_)
         return self._prefill_gemm(ids)
 
-    def _prefill_gemm(self, ids: torch.Tensor, want_logits: bool = False):
+    def prefill_asr(self, input_token_ids, audio_embeds, audio_start_idx: int) -> int:
+        """prefill_step with rows audio_start_idx .. + audio_len - 1 of the embedded prompt replaced by
+        ``audio_embeds`` [audio_len, 1024] (CUDA bf16).  Same checks and texts as the reference
+        (bindings_prefill.cpp:835-861)."""
+        ids = torch.as_tensor(input_token_ids, dtype=torch.int32).reshape(-1)
+        n = self._check_prefill(ids, 0)
+        if (not torch.is_tensor(audio_embeds) or not audio_embeds.is_cuda or audio_embeds.dtype != torch.bfloat16
+                or audio_embeds.dim() != 2):
+            raise RuntimeError("audio_embeds must be a CUDA bfloat16 2D tensor [audio_len, hidden_size]")
+        audio_len, hidden = int(audio_embeds.shape[0]), int(audio_embeds.shape[1])
+        if hidden != _HIDDEN:
+            raise RuntimeError("audio_embeds hidden_size mismatch with compiled megakernel spec: "
+                               f"expected={_HIDDEN}, got={hidden}")
+        if audio_len <= 0:
+            raise RuntimeError("audio_embeds must have audio_len > 0")
+        if audio_start_idx < 0 or audio_start_idx + audio_len > n:
+            raise RuntimeError("Invalid audio_start_idx/audio_len for the given seq_len")
+        self.position_ = 0
+        return self._prefill_gemm(ids, audio=(audio_embeds.contiguous(), int(audio_start_idx)))
+
+    def _prefill_gemm(self, ids: torch.Tensor, want_logits: bool = False, audio=None):
         """Full-sequence forward on the tcgen05 GEMM path (mq_launch_prefill)."""
         n = int(ids.numel())
         with torch.cuda.device(self.device):
@@ -441,8 +461,13 @@ class MegakernelDecoder:
                 if self._logits is None:
                     self._logits = torch.empty(self.vocab_size_, dtype=torch.float32, device=self.device)
                 logits_ptr = _ptr(self._logits)
-            rc = self._lib.mq_launch_prefill(C.byref(self._model), C.byref(self._buf), C.byref(self._pf), _ptr(dev_ids), n,
-                                             self.position_, _ptr(self._scalars), logits_ptr, self._stream())
+            if audio is not None:
+                rc = self._lib.mq_launch_prefill_asr(C.byref(self._model), C.byref(self._buf), C.byref(self._pf), _ptr(dev_ids), n,
+                                                     self.position_, _ptr(audio[0]), audio[1], int(audio[0].shape[0]),
+                                                     _ptr(self._scalars), logits_ptr, self._stream())
+            else:
+                rc = self._lib.mq_launch_prefill(C.byref(self._model), C.byref(self._buf), C.byref(self._pf), _ptr(dev_ids), n,
+                                                 self.position_, _ptr(self._scalars), logits_ptr, self._stream())
             _lib.check(rc, "mq_launch_prefill")
             self.launches += self._lib.mq_prefill_launch_count(self.num_layers_)
             self.position_ += n

@@ -104,9 +104,11 @@ class RestatedQwen3:
         self.v_cache.zero_()
         self.position = 0
 
-    def forward(self, ids, return_hidden: bool = False) -> torch.Tensor:
+    def forward(self, ids, return_hidden: bool = False, patch=None) -> torch.Tensor:
         """Consume ``ids`` (s >= 1 tokens) at positions position..position+s-1;
-        returns fp32 logits [V] of the last row (bf16 values)."""
+        returns fp32 logits [V] of the last row (bf16 values).  ``patch`` = (start, rows
+        [n, H] bf16) replaces embedded rows start..start+n-1 before the first layer, as the
+        reference's speech front-end does (csrc/megakernel/fused_prefill_kernels.inl:28-45)."""
         sp, w = self.spec, self.w
         ids = torch.as_tensor(ids, dtype=torch.long).view(-1)
         s = ids.numel()
@@ -115,6 +117,9 @@ class RestatedQwen3:
         cos = w["cos_table"][p0:p0 + s].view(s, 1, sp.head_dim)
         sin = w["sin_table"][p0:p0 + s].view(s, 1, sp.head_dim)
         h = w["embed_weight"][ids]                                   # [s, H] bf16
+        if patch is not None:
+            h = h.clone()
+            h[patch[0]:patch[0] + patch[1].shape[0]] = patch[1].to(h.dtype)
         for l in range(sp.num_layers):
             (w_in, wq, wk, wv, w_qn, w_kn, wo, w_post, wg, wu, wd) = w["layer_weights"][11 * l: 11 * l + 11]
             x = rms_norm(h, w_in, sp.rms_eps)
