@@ -198,10 +198,10 @@ def _measure_batched(out, common, w, dev, only_config5, seq_seed0):
     def events():
         return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def batched(name, lens, steps, max_seq, cfg_idx):
+    def batched(name, lens, steps, max_seq, cfg_idx, kv_fp8=False):
         B = len(lens)
         cos, sin = w["cos_table"][:max_seq].contiguous().to(dev), w["sin_table"][:max_seq].contiguous().to(dev)
-        bd = MegakernelBatchDecoder(*common, cos, sin, spec.num_layers, max_seq, B, max(lens))
+        bd = MegakernelBatchDecoder(*common, cos, sin, spec.num_layers, max_seq, B, max(lens), kv_fp8=kv_fp8)
         prompts = [random_prompt(spec, n, cfg_idx, seq_seed0 + i) for i, n in enumerate(lens)]
         torch.cuda.synchronize(dev)
         t0 = time.perf_counter()
@@ -224,7 +224,8 @@ def _measure_batched(out, common, w, dev, only_config5, seq_seed0):
         bd.check_status()
         ms = e0.elapsed_time(e1)
         mean_len = sum(lens) / B + steps / 2
-        step_bytes = spec.weight_bytes() + B * spec.kv_bytes_per_position() * (mean_len + 1)
+        # bytes a step must move: the weights once, every cached K/V row once (half as many with the e4m3 shadow)
+        step_bytes = spec.weight_bytes() + B * spec.kv_bytes_per_position() * (mean_len + 1) * (0.5 if kv_fp8 else 1.0)
         out[name] = {"batch": B, "prefill_tokens_per_s": sum(lens) / (t1 - t0), "decode_tokens_per_s": B * steps / ms * 1e3,
                      "ms_per_step": ms / steps, "achieved_GBps": step_bytes / (ms / steps * 1e-3) / 1e9}
         del bd
@@ -233,6 +234,9 @@ def _measure_batched(out, common, w, dev, only_config5, seq_seed0):
     if not only_config5:
         batched("config4_batch32_ragged", random_lengths(32, 256, 512), 128, 1024, 4)
     batched("config5_batch64_ctx1024", [1024] * 64, 256, 1296, 5)
+    if not only_config5:
+        # the same workload with the attention reading the e4m3 shadow KV cache (opt-in, row f3)
+        batched("config5_batch64_ctx1024_kv_fp8", [1024] * 64, 64, 1296, 5, kv_fp8=True)
     return out
 
 

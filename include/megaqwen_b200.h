@@ -123,6 +123,37 @@ int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf,
                      const int* in_token, int* out_token, const int* position,
                      float* logits, int flags, void* stream);
 
+/* ---- FP8 (e4m3) shadow KV cache, opt-in (reference: MEGAQWEN_SPLIT_KV_FP8,
+ * csrc/megakernel/bindings_prefill.cpp:513, 1371-1400; kernels split_decode_gemm.cu:74-78,
+ * 223-300, 429-493, 950-1310).  The bf16 caches stay authoritative and are still written by
+ * every step; the attention kernels read K and V from the shadow cache instead: half the
+ * bytes per cached position.  One scale per (layer, kv head): x ~ e4m3 * scale.
+ *   k_fp8 / v_fp8     u8  [num_layers, 8, max_seq_len, 128]  (batched: one such block per sequence)
+ *   k_scale / v_scale f32 [num_layers, 8]                    (batched: [batch, num_layers, 8]);
+ *                     a stored scale below 1e-8 reads as 1, so zero-filled scales are valid
+ *                     before the first mq_launch_kv_quantize_fp8. */
+typedef struct MqKvFp8 {
+    void* k_fp8;
+    void* v_fp8;
+    float* k_scale;
+    float* v_scale;
+} MqKvFp8;
+
+/* Quantises positions [start_pos, end_pos) of ONE sequence's bf16 caches into its shadow
+ * caches and SETS the scales from that span: scale = max|x| / 448 (1 if the span is all zero),
+ * value = e4m3_rn_satfinite(x / scale).  k_cache / v_cache: bf16 [num_layers, 8, max_seq_len,
+ * 128].  An empty span is a no-op.  Replaces launch_split_quantize_kv_cache_fp8
+ * (split_decode_gemm.cu:302-345); rows appended later by decode steps are quantised with the
+ * scales found here (split_decode_gemm.cu:487-493). */
+int mq_launch_kv_quantize_fp8(const void* k_cache, const void* v_cache, const MqKvFp8* kv8, int num_layers,
+                              int max_seq_len, int start_pos, int end_pos, void* stream);
+
+/* mq_launch_decode with the attention reading the shadow cache (the step also quantises its
+ * own new K/V row into it). */
+int mq_launch_decode_kv8(const MqModel* model, const MqDecodeBuffers* buf, const MqKvFp8* kv8,
+                         const int* in_token, int* out_token, const int* position,
+                         float* logits, int flags, void* stream);
+
 /* ---- Persistent decode: n_steps greedy steps in ONE cooperative launch (one CTA per SM).
  * The device-resident equivalent of the reference's cooperative megakernel and of its
  * decode_steps_cuda / decode_greedy_cuda chains (csrc/megakernel/fused_decode_ldg_kernel.inl:
@@ -151,8 +182,8 @@ int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf,
  * 3 attention, 4 split merge, 5 wait for the attention output, 6 Wo rows, 7 wait for the
  * post-attention hidden vector, 8 RMSNorm + gate/up rows, 9 wait for the MLP activation,
  * 10 Wd rows; in row [num_layers]: 11 wait for the last hidden vector, 12 LM head, 13 wait for
- * the arg-max keys, 15 cycles spent waiting for weight pages (the counterpart of the
- * reference's per-stage clock64 counters, fused_decode_ldg_common.inl:24-69).
+ * the arg-max keys; slots 14 and 15 are unused (the counterpart of the reference's per-stage
+ * clock64 counters, fused_decode_ldg_common.inl:24-69).
  * Results agree with n_steps calls of mq_launch_decode up to fp32 summation order. */
 size_t mq_stream_packed_bytes(const MqModel* model);
 int mq_stream_pack(const MqModel* model, void* packed, size_t packed_bytes, void* stream);
@@ -262,6 +293,11 @@ int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const
 int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffers* bb, const int* ids, const int* row_seq,
                              const int* row_pos, const int* tile_seq, const int* tile_q0, const int* seq_len,
                              const int* seq_row0, int total_rows, int num_tiles, int* out_tokens, void* stream);
+
+/* mq_launch_decode_batch with the attention reading the shadow caches (kv8 holds one block and
+ * one scale row per sequence, see MqKvFp8). */
+int mq_launch_decode_batch_kv8(const MqModel* model, const MqBatchBuffers* bb, const MqKvFp8* kv8,
+                               const int* in_tokens, int* out_tokens, float* logits_f32, void* stream);
 
 /* Kernels one step launches on the tile-GEMM path (batch > 64); at most one fewer per layer otherwise. */
 int mq_decode_batch_launch_count(int num_layers);

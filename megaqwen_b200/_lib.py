@@ -51,6 +51,10 @@ class MqBatchBuffers(C.Structure):
                 ("partials_bytes", C.c_size_t)]
 
 
+class MqKvFp8(C.Structure):
+    _fields_ = [("k_fp8", C.c_void_p), ("v_fp8", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/megaqwen_b200.h declares.
 SIGNATURES = {
     "mq_abi_version": (C.c_int, []),
@@ -81,6 +85,11 @@ SIGNATURES = {
     "mq_launch_prefill_packed": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers)] + [C.c_void_p] * 7 +
                                  [C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "mq_decode_batch_launch_count": (C.c_int, [C.c_int]),
+    "mq_launch_kv_quantize_fp8": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(MqKvFp8), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "mq_launch_decode_kv8": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqDecodeBuffers), C.POINTER(MqKvFp8), C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "mq_launch_decode_batch_kv8": (C.c_int, [C.POINTER(MqModel), C.POINTER(MqBatchBuffers), C.POINTER(MqKvFp8), C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_void_p]),
     "mq_prefill_launch_count": (C.c_int, [C.c_int]),
     "mq_launch_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                       C.c_int, C.c_void_p, C.c_void_p]),

@@ -14,13 +14,13 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import MqBatchBuffers, MqDecodeBuffers, MqLayerWeights, MqModel, MqPrefillBuffers
+from ._lib import MqBatchBuffers, MqDecodeBuffers, MqKvFp8, MqLayerWeights, MqModel, MqPrefillBuffers
 from .decoder import _D, _HIDDEN, _INTER, _LAYER_SHAPES, _NKV, _NQ, _ptr
 
 
 class MegakernelBatchDecoder:
     def __init__(self, embed_weight, layer_weights, final_norm_weight, lm_head_weight, cos_table, sin_table,
-                 num_layers, max_seq_len, max_batch, max_prefill_len=None):
+                 num_layers, max_seq_len, max_batch, max_prefill_len=None, kv_fp8=False):
         if not torch.cuda.is_available():
             raise RuntimeError("megaqwen_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
         self._lib = _lib.lib()
@@ -65,6 +65,15 @@ class MegakernelBatchDecoder:
             self.use_packed_prefill = True
             self._chain = None
             self._graphs = {}
+            # e4m3 shadow caches, one scale per (sequence, layer, kv head): prefill_batch quantises
+            # every prompt, the decode steps append with those scales and attend over the shadow
+            self.kv_fp8 = bool(kv_fp8)
+            self._kv8 = None
+            if self.kv_fp8:
+                self.k_cache_fp8_ = torch.zeros(self.k_cache_.shape, dtype=torch.uint8, device=dev)
+                self.v_cache_fp8_ = torch.zeros_like(self.k_cache_fp8_)
+                self.kv_scales_ = torch.ones((2, B, self.num_layers_, _NKV), dtype=torch.float32, device=dev)   # [k | v]
+                self._kv8 = MqKvFp8(_ptr(self.k_cache_fp8_), _ptr(self.v_cache_fp8_), _ptr(self.kv_scales_[0]), _ptr(self.kv_scales_[1]))
         self.batch_ = 0
         self.launches = 0
 
@@ -88,6 +97,22 @@ class MegakernelBatchDecoder:
         self.v_cache_.zero_()
         self._positions.zero_()
         self.batch_ = 0
+        if self.kv_fp8:
+            self.k_cache_fp8_.zero_()
+            self.v_cache_fp8_.zero_()
+            self.kv_scales_.fill_(1.0)
+
+    def _quantize_prompts(self, lens) -> None:
+        """Shadow caches and scales of sequences 0 .. len(lens) - 1 from their prompts' bf16 rows."""
+        if not self.kv_fp8:
+            return
+        with torch.cuda.device(self.device):
+            for b, n in enumerate(lens):
+                kv8 = MqKvFp8(_ptr(self.k_cache_fp8_[b]), _ptr(self.v_cache_fp8_[b]), _ptr(self.kv_scales_[0, b]), _ptr(self.kv_scales_[1, b]))
+                rc = self._lib.mq_launch_kv_quantize_fp8(_ptr(self.k_cache_[b]), _ptr(self.v_cache_[b]), C.byref(kv8), self.num_layers_,
+                                                         self.max_seq_len_, 0, int(n), self._stream())
+                _lib.check(rc, "mq_launch_kv_quantize_fp8")
+                self.launches += 1
 
     def positions(self) -> torch.Tensor:
         return self._positions[: self.batch_].clone()
@@ -154,6 +179,7 @@ class MegakernelBatchDecoder:
                     self._prefill_packed(prompts[b:e], b, out)
                     b = e
             self.batch_ = len(prompts)
+            self._quantize_prompts([int(p.numel()) for p in prompts])
             res = out.cpu()
             self.check_status()
             return res
@@ -171,13 +197,18 @@ class MegakernelBatchDecoder:
                 lens.append(n)
             self._positions[: len(prompts)].copy_(torch.tensor(lens, dtype=torch.int32), non_blocking=False)
         self.batch_ = len(prompts)
+        self._quantize_prompts(lens)
         res = out.cpu()
         self.check_status()
         return res
 
     def _step(self, in_ptr: int, out_ptr: int, logits_ptr=None) -> None:
         bb = self._bb(self.batch_)
-        rc = self._lib.mq_launch_decode_batch(C.byref(self._model), C.byref(bb), in_ptr, out_ptr, logits_ptr, self._stream())
+        if self.kv_fp8:
+            rc = self._lib.mq_launch_decode_batch_kv8(C.byref(self._model), C.byref(bb), C.byref(self._kv8), in_ptr, out_ptr, logits_ptr,
+                                                      self._stream())
+        else:
+            rc = self._lib.mq_launch_decode_batch(C.byref(self._model), C.byref(bb), in_ptr, out_ptr, logits_ptr, self._stream())
         _lib.check(rc, "mq_launch_decode_batch")
         self.launches += self._lib.mq_decode_batch_launch_count(self.num_layers_)
 

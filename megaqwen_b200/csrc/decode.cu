@@ -92,6 +92,10 @@ struct DecodeArgs {
     int max_seq;
     int nsplit;
     int chunk_cap;
+    uint8_t* k8;     // FP8 shadow cache (k_attn_fp8 only): e4m3 [num_layers, 8, max_seq, 128]
+    uint8_t* v8;
+    const float* k_scale;   // [num_layers, 8]
+    const float* v_scale;
     int kseq;        // launch index within the step (timeline builds only)
     int exp_flags;   // experiments (benchmarks only): 1 skip dot products, 2 skip RMSNorm, 4 no weight copies in the per-layer GEMV kernels
 };
@@ -268,7 +272,12 @@ __device__ __forceinline__ void attn_cta_done(const DecodeArgs& a, unsigned int 
 
 constexpr int KV_LD = D + 8;   // K/V rows are padded by 16 bytes in shared memory (conflict-free ldmatrix)
 
-__global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeights w, int layer) {
+// FP8 = true: the cached rows come from the e4m3 shadow cache (a.k8 / a.v8) and are expanded to f16
+// tiles in place; the new position's K / V are quantised with the stored scales, written to both
+// caches and attended over in their quantised form; scores carry the K scale, the output the V
+// scale (reference: csrc/megakernel/split_decode_gemm.cu:429-493, 950-1310).
+template <bool FP8>
+__device__ __forceinline__ void attn_body(const DecodeArgs& a, const MqLayerWeights& w, int layer) {
     TL(a, 0);
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int cap = a.chunk_cap;
@@ -285,6 +294,11 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = blockIdx.x % NKV, s = blockIdx.x / NKV;   // CTAs beyond 8 * nsplit only hold their SM's slot
+    float ks = 1.f, vs = 1.f;                               // FP8: set before the first step, constant afterwards
+    if constexpr (FP8) {
+        ks = kv_fp8_scale_guard(a.k_scale[layer * NKV + g]);
+        vs = kv_fp8_scale_guard(a.v_scale[layer * NKV + g]);
+    }
     const int pos = ld_cg_i32(a.pos);
     const bool valid = pos >= 0 && pos < a.max_seq;
     const int len = pos + 1;
@@ -310,12 +324,26 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
                             : v == 2 ? a.cos + (size_t)pos * D : a.sin + (size_t)pos * D;
             cp_async16(cst + v * D + c * 8, src + c * 8);
         }
-        const bf16* ksrc = a.k_cache + head_off + (size_t)c0 * D;
-        const bf16* vsrc = a.v_cache + head_off + (size_t)c0 * D;
-        for (int i = tid; i < n_cached * 16; i += ATT_THREADS) {
-            const int r = i >> 4, c = i & 15;
-            cp_async16(kt + (size_t)r * KV_LD + c * 8, ksrc + (size_t)r * D + c * 8);
-            cp_async16(vt + (size_t)r * KV_LD + c * 8, vsrc + (size_t)r * D + c * 8);
+        if constexpr (FP8) {
+            // raw e4m3 rows go to the END of each tile array: expanding row r in place (below) then
+            // never overwrites a raw row that has not been read (272 r + 256 <= 144 cap + 128 (r + 1))
+            const uint8_t* ksrc = a.k8 + head_off + (size_t)c0 * D;
+            const uint8_t* vsrc = a.v8 + head_off + (size_t)c0 * D;
+            uint8_t* kst = reinterpret_cast<uint8_t*>(kt) + (size_t)cap * (KV_LD * 2 - D);
+            uint8_t* vst = reinterpret_cast<uint8_t*>(vt) + (size_t)cap * (KV_LD * 2 - D);
+            for (int i = tid; i < n_cached * 8; i += ATT_THREADS) {
+                const int r = i >> 3, c = i & 7;
+                cp_async16(kst + (size_t)r * D + c * 16, ksrc + (size_t)r * D + c * 16);
+                cp_async16(vst + (size_t)r * D + c * 16, vsrc + (size_t)r * D + c * 16);
+            }
+        } else {
+            const bf16* ksrc = a.k_cache + head_off + (size_t)c0 * D;
+            const bf16* vsrc = a.v_cache + head_off + (size_t)c0 * D;
+            for (int i = tid; i < n_cached * 16; i += ATT_THREADS) {
+                const int r = i >> 4, c = i & 15;
+                cp_async16(kt + (size_t)r * KV_LD + c * 8, ksrc + (size_t)r * D + c * 8);
+                cp_async16(vt + (size_t)r * KV_LD + c * 8, vsrc + (size_t)r * D + c * 8);
+            }
         }
         cp_async_commit();
     }
@@ -338,28 +366,76 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     __syncthreads();   // this thread's copies are complete; the barrier makes everybody's visible
     // release the slot holders now: by this time the next kernel's CTA is resident on their SMs
     if (tid == ATT_THREADS - 1) attn_cta_done(a, n_working, tag);
+    if constexpr (FP8) {
+        // e4m3 -> f16 in place, 64 rows at a time: thread t reads 32 bytes of K and of V of row
+        // r0 + t / 4, the block barrier ends all reads of the group, then the padded f16 rows are written
+        const uint8_t* kst = reinterpret_cast<const uint8_t*>(kt) + (size_t)cap * (KV_LD * 2 - D);
+        const uint8_t* vst = reinterpret_cast<const uint8_t*>(vt) + (size_t)cap * (KV_LD * 2 - D);
+        for (int r0 = 0; r0 < n_cached; r0 += 64) {
+            const int r = r0 + (tid >> 2), seg = (tid & 3) * 32;
+            const bool have = r < n_cached;
+            uint4 k0 = make_uint4(0u, 0u, 0u, 0u), k1 = k0, v0 = k0, v1 = k0;
+            if (have) {
+                k0 = *reinterpret_cast<const uint4*>(kst + (size_t)r * D + seg);
+                k1 = *reinterpret_cast<const uint4*>(kst + (size_t)r * D + seg + 16);
+                v0 = *reinterpret_cast<const uint4*>(vst + (size_t)r * D + seg);
+                v1 = *reinterpret_cast<const uint4*>(vst + (size_t)r * D + seg + 16);
+            }
+            __syncthreads();
+            if (have) {
+                uint4* kd = reinterpret_cast<uint4*>(kt + (size_t)r * KV_LD + seg);
+                uint4* vd = reinterpret_cast<uint4*>(vt + (size_t)r * KV_LD + seg);
+                fp8x16_to_f16x16(k0, kd[0], kd[1]);
+                fp8x16_to_f16x16(k1, kd[2], kd[3]);
+                fp8x16_to_f16x16(v0, vd[0], vd[1]);
+                fp8x16_to_f16x16(v1, vd[2], vd[3]);
+            }
+        }
+    }
 
     // ---- per-head norm + RoPE of q (both heads), and of the new k; v raw; zero the V rows
     //      between n and the end of the last 16-position tile (they are multiplied by p = 0)
     if (warp < 2) {
         float lo[2], hi[2];
         norm_rope_head(a.qkv + (2 * g + warp) * D, cst, cst + 2 * D, cst + 3 * D, lane, lo, hi);
-        *reinterpret_cast<uint32_t*>(qs + warp * D + 2 * lane) = pack_bf16x2(lo[0], lo[1]);
-        *reinterpret_cast<uint32_t*>(qs + warp * D + 64 + 2 * lane) = pack_bf16x2(hi[0], hi[1]);
+        *reinterpret_cast<uint32_t*>(qs + warp * D + 2 * lane) = FP8 ? pack_f16x2(lo[0], lo[1]) : pack_bf16x2(lo[0], lo[1]);
+        *reinterpret_cast<uint32_t*>(qs + warp * D + 64 + 2 * lane) = FP8 ? pack_f16x2(hi[0], hi[1]) : pack_bf16x2(hi[0], hi[1]);
     } else if (warp == 2 && is_last) {
         float lo[2], hi[2];
         norm_rope_head(a.qkv + QSZ + g * D, cst + D, cst + 2 * D, cst + 3 * D, lane, lo, hi);
         const uint32_t plo = pack_bf16x2(lo[0], lo[1]), phi = pack_bf16x2(hi[0], hi[1]);
         bf16* krow = kt + (size_t)(n - 1) * KV_LD;
-        *reinterpret_cast<uint32_t*>(krow + 2 * lane) = plo;
-        *reinterpret_cast<uint32_t*>(krow + 64 + 2 * lane) = phi;
         bf16* gk = a.k_cache + head_off + (size_t)pos * D;
         *reinterpret_cast<uint32_t*>(gk + 2 * lane) = plo;
         *reinterpret_cast<uint32_t*>(gk + 64 + 2 * lane) = phi;
+        if constexpr (FP8) {
+            const float inv = 1.0f / ks;
+            const uint32_t qlo = f32x2_to_fp8x2(lo[0] * inv, lo[1] * inv), qhi = f32x2_to_fp8x2(hi[0] * inv, hi[1] * inv);
+            uint8_t* g8 = a.k8 + head_off + (size_t)pos * D;
+            *reinterpret_cast<uint16_t*>(g8 + 2 * lane) = (uint16_t)qlo;
+            *reinterpret_cast<uint16_t*>(g8 + 64 + 2 * lane) = (uint16_t)qhi;
+            uint32_t flo, fhi, unused;
+            fp8x4_to_f16x4(qlo, flo, unused);
+            fp8x4_to_f16x4(qhi, fhi, unused);
+            *reinterpret_cast<uint32_t*>(krow + 2 * lane) = flo;
+            *reinterpret_cast<uint32_t*>(krow + 64 + 2 * lane) = fhi;
+        } else {
+            *reinterpret_cast<uint32_t*>(krow + 2 * lane) = plo;
+            *reinterpret_cast<uint32_t*>(krow + 64 + 2 * lane) = phi;
+        }
     } else if (warp == 3 && is_last) {
         const uint2 u = ld_cg_u2(a.qkv + QSZ + KVSZ + g * D + 4 * lane);
-        *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * KV_LD + 4 * lane) = u;
         *reinterpret_cast<uint2*>(a.v_cache + head_off + (size_t)pos * D + 4 * lane) = u;
+        if constexpr (FP8) {
+            const float inv = 1.0f / vs;
+            const uint32_t q4 = f32x4_to_fp8x4(bf_lo(u.x) * inv, bf_hi(u.x) * inv, bf_lo(u.y) * inv, bf_hi(u.y) * inv);
+            *reinterpret_cast<uint32_t*>(a.v8 + head_off + (size_t)pos * D + 4 * lane) = q4;
+            uint2 f;
+            fp8x4_to_f16x4(q4, f.x, f.y);
+            *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * KV_LD + 4 * lane) = f;
+        } else {
+            *reinterpret_cast<uint2*>(vt + (size_t)(n - 1) * KV_LD + 4 * lane) = u;
+        }
     } else if (warp >= 4) {
         const int n16 = (n + 15) & ~15;
         for (int i = (warp - 4) * 32 + lane; i < (n16 - n) * 16; i += 128)
@@ -373,7 +449,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     // of the tile, probabilities to bf16, out += P . V_tile (heads in M, dims in N).
     {
         const int gi = lane >> 2, ti = lane & 3;
-        const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+        const float scale = 0.08838834764831845f * ks;  // 1/sqrt(128) (x the K scale)
         float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
         float o[16][4];
 #pragma unroll
@@ -389,7 +465,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
                 ldsm4(af, smem_u32(kt) + rowoff + ks * 32);
                 uint32_t b0 = lds32(qaddr + ks * 32), b1 = lds32(qaddr + ks * 32 + 16);
                 if (gi >= 2) { b0 = 0u; b1 = 0u; }
-                mma16816(c, af, b0, b1);
+                mma16816_sel<FP8>(c, af, b0, b1);
             }
             // lanes with ti == 0 hold head 0 / head 1 of positions gi (c[0], c[1]) and gi + 8 (c[2], c[3])
             const int p_lo = tile * 16 + gi, p_hi = p_lo + 8;
@@ -418,8 +494,14 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
             l0 = l0 * cr0 + __shfl_sync(0xffffffffu, u0, 0);
             l1 = l1 * cr1 + __shfl_sync(0xffffffffu, u1, 0);
             if (own) {
-                pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
-                pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+                if constexpr (FP8) {   // rounded to bf16 as on the bf16 path; exact in f16 (8 significant bits, e <= 1)
+                    __half* ph = reinterpret_cast<__half*>(pw);
+                    ph[gi] = __float2half_rn(rbf(e00)); ph[gi + 8] = __float2half_rn(rbf(e10));
+                    ph[16 + gi] = __float2half_rn(rbf(e01)); ph[16 + gi + 8] = __float2half_rn(rbf(e11));
+                } else {
+                    pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
+                    pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+                }
             }
             __syncwarp();
             // A = P: row gi is head gi (rows 2..15 are zero)
@@ -434,8 +516,8 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
                 uint32_t bv[4];
                 ldsm4_t(bv, smem_u32(vt) + rowoff + j * 32);
                 o[2 * j][0] *= crg; o[2 * j][1] *= crg; o[2 * j + 1][0] *= crg; o[2 * j + 1][1] *= crg;
-                mma16816(o[2 * j], pa, bv[0], bv[1]);
-                mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
+                mma16816_sel<FP8>(o[2 * j], pa, bv[0], bv[1]);
+                mma16816_sel<FP8>(o[2 * j + 1], pa, bv[2], bv[3]);
             }
             __syncwarp();
         }
@@ -463,6 +545,7 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
         if (d == 0) { ml[hh * 2] = M; ml[hh * 2 + 1] = lsum; }
         // every thread of a head needs (M, l): publish through shared memory
         __syncthreads();
+        acc *= vs;                          // 1 on the bf16 path
     }
     const int qhead = 2 * g + hh;
     if (n_act == 1) {
@@ -526,6 +609,9 @@ __global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeigh
     TL_SYNC();
     TL(a, 3);
 }
+
+__global__ void __launch_bounds__(ATT_THREADS) k_attn(DecodeArgs a, MqLayerWeights w, int layer) { attn_body<false>(a, w, layer); }
+__global__ void __launch_bounds__(ATT_THREADS) k_attn_fp8(DecodeArgs a, MqLayerWeights w, int layer) { attn_body<true>(a, w, layer); }
 
 // ---------------------------------------------------------------- k_oproj
 // hidden[r] = bf16( hidden[r] + bf16( Wo[r,:] . attn ) )
@@ -903,6 +989,7 @@ static int ensure_device(DeviceState** out) {
         MQ_SET_SMEM(k_down, smem_down(MIN_GRID));
         MQ_SET_SMEM(k_lmhead, smem_lmhead());
         MQ_SET_SMEM(k_attn, smem_attn(ATT_MAX_CAP));
+        MQ_SET_SMEM(k_attn_fp8, smem_attn(ATT_MAX_CAP));
 #undef MQ_SET_SMEM
         st.ready = true;
     }
@@ -991,9 +1078,10 @@ extern "C" size_t mq_decode_partials_bytes(int max_seq_len) {
 
 extern "C" int mq_decode_launch_count(int num_layers) { return 5 * num_layers + 1; }
 
-extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf, const int* in_token, int* out_token,
-                                const int* position, float* logits, int flags, void* stream_v) {
+static int decode_impl(const MqModel* model, const MqDecodeBuffers* buf, const MqKvFp8* kv8, const int* in_token, int* out_token,
+                       const int* position, float* logits, int flags, void* stream_v) {
     if (!model || !buf || !in_token || !out_token || !position) return MQ_ERR_BAD_ARG;
+    if (kv8 && (!kv8->k_fp8 || !kv8->v_fp8 || !kv8->k_scale || !kv8->v_scale)) return MQ_ERR_BAD_ARG;
     if (!model->embed || !model->layers || !model->final_norm || !model->lm_head || !model->cos_table || !model->sin_table)
         return MQ_ERR_BAD_ARG;
     if (model->num_layers <= 0 || model->vocab_size <= 0 || model->max_seq_len <= 0) return MQ_ERR_BAD_ARG;
@@ -1039,6 +1127,10 @@ extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf
     a.chunk_cap = cap;
     a.exp_flags = g_decode_exp_flags;
     a.kseq = 0;
+    a.k8 = kv8 ? (uint8_t*)kv8->k_fp8 : nullptr;
+    a.v8 = kv8 ? (uint8_t*)kv8->v_fp8 : nullptr;
+    a.k_scale = kv8 ? kv8->k_scale : nullptr;
+    a.v_scale = kv8 ? kv8->v_scale : nullptr;
 
     const bool pdl = !(flags & MQ_FLAG_NO_PDL);
     const int G = st->sm_count;
@@ -1050,7 +1142,7 @@ extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf
         e = launch(k_qkv, dim3(G), dim3(GEMV_THREADS), slot(5 * l, smem_qkv(G)), stream, pdl && (!first || (flags & MQ_FLAG_CHAINED)), a, w, l);
         if (e != cudaSuccess) return (int)e;
         a.kseq = 5 * l + 1;
-        e = launch(k_attn, dim3(NKV * nsplit > G ? NKV * nsplit : G), dim3(ATT_THREADS), slot(5 * l + 1, smem_attn(cap)), stream, pdl, a, w, l);
+        e = launch(kv8 ? k_attn_fp8 : k_attn, dim3(NKV * nsplit > G ? NKV * nsplit : G), dim3(ATT_THREADS), slot(5 * l + 1, smem_attn(cap)), stream, pdl, a, w, l);
         if (e != cudaSuccess) return (int)e;
         a.kseq = 5 * l + 2;
         e = launch(k_oproj, dim3(G), dim3(GEMV_THREADS), slot(5 * l + 2, smem_oproj(G)), stream, pdl, a, w);
@@ -1066,6 +1158,17 @@ extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf
     e = launch(k_lmhead, dim3(G), dim3(LM_THREADS), slot(5 * model->num_layers, smem_lmhead()), stream, pdl, a);
     if (e != cudaSuccess) return (int)e;
     return MQ_OK;
+}
+
+extern "C" int mq_launch_decode(const MqModel* model, const MqDecodeBuffers* buf, const int* in_token, int* out_token,
+                                const int* position, float* logits, int flags, void* stream_v) {
+    return decode_impl(model, buf, nullptr, in_token, out_token, position, logits, flags, stream_v);
+}
+
+extern "C" int mq_launch_decode_kv8(const MqModel* model, const MqDecodeBuffers* buf, const MqKvFp8* kv8, const int* in_token,
+                                    int* out_token, const int* position, float* logits, int flags, void* stream_v) {
+    if (!kv8) return MQ_ERR_BAD_ARG;
+    return decode_impl(model, buf, kv8, in_token, out_token, position, logits, flags, stream_v);
 }
 
 extern "C" int mq_launch_fill_iota(int* dst, int start, int n, void* stream) {

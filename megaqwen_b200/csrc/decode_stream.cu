@@ -53,9 +53,14 @@ constexpr int ST_WARPS = 8;
 constexpr int ST_THREADS = ST_WARPS * 32;        // 256: every warp streams, multiplies and polls
 constexpr uint32_t ST_UNIT = 2048;               // bytes per ring slot = one bulk copy = 4 blocks of 512 bytes
 #ifndef MQ_ST_NSLOT
-#define MQ_ST_NSLOT 9
+#define MQ_ST_NSLOT 4
 #endif
-constexpr int ST_NSLOT = MQ_ST_NSLOT;            // slots per warp: 8 x 9 x 2 KB = 144 KB in flight per SM
+constexpr int ST_NSLOT = MQ_ST_NSLOT;            // ring slots per warp
+#ifndef MQ_ST_COPY
+#define MQ_ST_COPY 2
+#endif
+constexpr int ST_COPY = MQ_ST_COPY;              // units per bulk copy = per ring slot
+constexpr uint32_t ST_SLOT_BYTES = ST_COPY * ST_UNIT;
 constexpr int ST_KV_CAP = 128;                   // cached positions one CTA attends over
 constexpr int ST_KV_LD = D + 8;                  // K/V rows padded by 16 bytes (conflict-free ldmatrix)
 constexpr int ST_MAX_SPLIT = 18;                 // CTAs per kv head
@@ -288,32 +293,43 @@ struct WRing {
     unsigned int* status;
     uint32_t slot;            // slot of the next unit to use
     uint32_t parity;          // its barrier phase
+    uint32_t sub;             // unit within the slot
+    uint32_t cur_n;           // units the slot holds
+    uint32_t cidx;            // index (within a step) of the next unit to use
     uint32_t fidx;            // index (within a step) of the next unit to fetch
     uint32_t step_units;      // units per step
     uint32_t left;            // units still to fetch in this launch
 
-    __device__ __forceinline__ void fetch(uint32_t k) {          // lane 0 only
-        const uint32_t bar = smem_u32(&full[k]);
-        mbar_expect_tx_addr(bar, ST_UNIT);
-        bulk_g2s_addr(base + k * ST_UNIT, src + (size_t)fidx * ST_UNIT, ST_UNIT, bar);
-    }
-    __device__ __forceinline__ void advance_fetch() {
-        --left;
-        if (++fidx == step_units) fidx = 0u;
+    // one bulk copy of up to ST_COPY consecutive units (never across the end of a step's stream)
+    __device__ __forceinline__ void fetch(uint32_t k, int lane) {
+        const uint32_t n = min((uint32_t)ST_COPY, step_units - fidx);
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(&full[k]);
+            mbar_expect_tx_addr(bar, n * ST_UNIT);
+            bulk_g2s_addr(base + k * ST_SLOT_BYTES, src + (size_t)fidx * ST_UNIT, n * ST_UNIT, bar);
+        }
+        left -= n;
+        fidx += n;
+        if (fidx == step_units) fidx = 0u;
     }
     // shared address of the next unit, once it has landed
     __device__ __forceinline__ uint32_t acquire() {
-        if (!mbar_try_wait(&full[slot], parity)) mbar_wait_slow(&full[slot], parity, status);
-        return base + slot * ST_UNIT;
-    }
-    // the unit's bytes are in registers (their consumers have been issued): refill its slot
-    __device__ __forceinline__ void release(int lane) {
-        __syncwarp();
-        if (left) {
-            if (lane == 0) fetch(slot);
-            advance_fetch();
+        if (sub == 0u) {
+            if (!mbar_try_wait(&full[slot], parity)) mbar_wait_slow(&full[slot], parity, status);
+            cur_n = min((uint32_t)ST_COPY, step_units - cidx);
         }
-        if (++slot == (uint32_t)ST_NSLOT) { slot = 0u; parity ^= 1u; }
+        return base + slot * ST_SLOT_BYTES + sub * ST_UNIT;
+    }
+    // the unit's bytes are in registers (their consumers have been issued); after the last unit
+    // of a slot the slot is refilled
+    __device__ __forceinline__ void release(int lane) {
+        if (++cidx == step_units) cidx = 0u;
+        if (++sub == cur_n) {
+            sub = 0u;
+            __syncwarp();
+            if (left) fetch(slot, lane);
+            if (++slot == (uint32_t)ST_NSLOT) { slot = 0u; parity ^= 1u; }
+        }
     }
 };
 
@@ -454,7 +470,7 @@ __device__ __forceinline__ unsigned long long argmax_key64(float v, int idx) {
 __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* ring = smem_raw;                                                    // [ST_WARPS][ST_NSLOT][ST_UNIT]
-    bf16* kt = reinterpret_cast<bf16*>(smem_raw + (size_t)ST_WARPS * ST_NSLOT * ST_UNIT);   // [ST_KV_CAP][ST_KV_LD]
+    bf16* kt = reinterpret_cast<bf16*>(smem_raw + (size_t)ST_WARPS * ST_NSLOT * ST_SLOT_BYTES);   // [ST_KV_CAP][ST_KV_LD]
     bf16* vt = kt + (size_t)ST_KV_CAP * ST_KV_LD;
     bf16* xs = vt + (size_t)ST_KV_CAP * ST_KV_LD;                                // [3072] activation vector of a GEMV phase
     float* red = reinterpret_cast<float*>(xs + I);                               // [8][ST_RED_ROWS] per-warp partial sums
@@ -507,19 +523,19 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     {
         size_t woff = 0;
         for (int v = 0; v < warp; ++v) woff += (size_t)st_step_units(pl, v, L) * ST_UNIT;
-        rg.base = smem_u32(ring) + (uint32_t)warp * ST_NSLOT * ST_UNIT;
+        rg.base = smem_u32(ring) + (uint32_t)warp * ST_NSLOT * ST_SLOT_BYTES;
         rg.full = full + warp * ST_NSLOT;
         rg.src = a.packed + pl.stream_off + woff;
         rg.status = a.status;
         rg.slot = 0u;
         rg.parity = 0u;
+        rg.sub = 0u;
+        rg.cur_n = 0u;
+        rg.cidx = 0u;
         rg.fidx = 0u;
         rg.step_units = st_step_units(pl, warp, L);
         rg.left = rg.step_units * (uint32_t)a.n_steps;
-        for (int k = 0; k < ST_NSLOT && rg.left; ++k) {
-            if (lane == 0) rg.fetch((uint32_t)k);
-            rg.advance_fetch();
-        }
+        for (int k = 0; k < ST_NSLOT && rg.left; ++k) rg.fetch((uint32_t)k, lane);
     }
     unsigned long long* dbg = a.dbg ? a.dbg + (size_t)cta * (L + 1) * ST_STAGES : nullptr;
 #define ST_T0() long long t0_ = timing ? clock64() : 0
@@ -1059,7 +1075,7 @@ __global__ void k_pack_norms(MqLayerWeights w, bf16* dst) {
 
 // ------------------------------------------------------------------ host side
 static size_t st_smem_bytes() {
-    return (size_t)ST_WARPS * ST_NSLOT * ST_UNIT + (size_t)2 * ST_KV_CAP * ST_KV_LD * 2 + (size_t)I * 2 + (size_t)ST_WARPS * ST_RED_ROWS * 4 +
+    return (size_t)ST_WARPS * ST_NSLOT * ST_SLOT_BYTES + (size_t)2 * ST_KV_CAP * ST_KV_LD * 2 + (size_t)I * 2 + (size_t)ST_WARPS * ST_RED_ROWS * 4 +
            (4 * D + 2 * D + ST_WARPS * 32 + 4 * D) * 2 + (16 + 16 + 4 + 8 + 4) * 4 + ST_WARPS * 8 + ST_WARPS * ST_NSLOT * 8 + 16;
 }
 

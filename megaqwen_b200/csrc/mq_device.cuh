@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -174,6 +175,49 @@ __device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t saddr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
 }
+// ---- FP8 (e4m3) KV cache: the attention kernels multiply f16 tiles (every e4m3 value is exact
+// in f16) with the same fragment layouts as the bf16 tiles.
+__device__ __forceinline__ void mma16816_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <bool F16>
+__device__ __forceinline__ void mma16816_sel(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (F16) mma16816_f16(c, a, b0, b1);
+    else mma16816(c, a, b0, b1);
+}
+// four e4m3 bytes (little endian) -> four f16 (lo = elements 0, 1; hi = elements 2, 3)
+__device__ __forceinline__ void fp8x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    asm("{ .reg .b16 l, h; mov.b32 {l, h}, %2; cvt.rn.f16x2.e4m3x2 %0, l; cvt.rn.f16x2.e4m3x2 %1, h; }" : "=r"(lo), "=r"(hi) : "r"(w));
+}
+// sixteen e4m3 bytes -> sixteen f16 (two 16-byte words)
+__device__ __forceinline__ void fp8x16_to_f16x16(const uint4& w, uint4& a, uint4& b) {
+    fp8x4_to_f16x4(w.x, a.x, a.y);
+    fp8x4_to_f16x4(w.y, a.z, a.w);
+    fp8x4_to_f16x4(w.z, b.x, b.y);
+    fp8x4_to_f16x4(w.w, b.z, b.w);
+}
+// round-to-nearest-even, saturating at +-448 (the conversion of __nv_fp8_e4m3(float)); hi -> upper byte
+__device__ __forceinline__ uint32_t f32x2_to_fp8x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t)r;
+}
+__device__ __forceinline__ uint32_t f32x4_to_fp8x4(float a, float b, float c, float d) {
+    return f32x2_to_fp8x2(a, b) | (f32x2_to_fp8x2(c, d) << 16);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// the scale a quantised cache is read with: amax / 448, or 1 for an all-zero span
+// (reference: kv_fp8_max_abs_scale, csrc/megakernel/split_decode_gemm.cu:74-78)
+__host__ __device__ __forceinline__ float kv_fp8_scale_of(float amax) { return amax < 1.0e-8f ? 1.0f : amax / 448.0f; }
+// a stored scale below 1e-8 reads as 1 (split_decode_gemm.cu:445-446)
+__device__ __forceinline__ float kv_fp8_scale_guard(float s) { return s < 1.0e-8f ? 1.0f : s; }
+
 // 16-byte asynchronous copies global -> shared (any shared address: padded rows)
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");

@@ -1238,6 +1238,11 @@ namespace mq {
 constexpr int BD_THREADS = 384, BD_STAGES = 2, BD_LD = D + 8;   // 12 warps x 2 stages x 8.5 KB = 209 KB
 constexpr int BD_STAGE_ELEMS = 2 * 16 * BD_LD;                                  // K tile then V tile
 constexpr size_t BD_SMEM = (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS * 2 + 2 * D * 2 + (BD_THREADS / 32) * 32 * 2;
+// FP8 cache: a warp's ring holds the raw e4m3 rows (K 16 x 128 bytes, then V), two stages, followed
+// by ONE padded f16 tile pair the current stage is expanded into before it is multiplied
+constexpr int BD8_RAW = 2 * 16 * D;                                             // bytes per raw stage
+constexpr int BD8_WARP_BYTES = BD_STAGES * BD8_RAW + BD_STAGE_ELEMS * 2;
+static_assert((size_t)(BD_THREADS / 32) * BD8_WARP_BYTES <= (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS * 2, "the fp8 ring fits the bf16 ring");
 
 __device__ __forceinline__ void bd_load_tile(bf16* stage, const bf16* kb, const bf16* vb, int tile, int len, int lane) {
     // 16 rows x 16 chunks of 16 bytes for K and the same for V: 16 copies per lane.  Rows past
@@ -1254,37 +1259,113 @@ __device__ __forceinline__ void bd_load_tile(bf16* stage, const bf16* kb, const 
         cp_async16(sdst + (16 + 2 * i) * BD_LD, vb + goff);
     }
 }
+// e4m3 rows: 16 rows x 8 chunks of 16 bytes for K and for V, 8 copies per lane; copy i of a lane
+// is chunk (lane & 7) of row 4 * (i & 3) + (lane >> 3) of K (i < 4) or V
+__device__ __forceinline__ void bd_load_tile_fp8(uint8_t* raw, const uint8_t* kb, const uint8_t* vb, int tile, int len, int lane) {
+    const int c16 = (lane & 7) * 16, r0 = lane >> 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = 4 * i + r0;
+        const size_t goff = (size_t)min(tile * 16 + r, len - 1) * D + c16;
+        cp_async16(raw + r * D + c16, kb + goff);
+        cp_async16(raw + 16 * D + r * D + c16, vb + goff);
+    }
+}
+// the raw stage -> padded f16 tiles (same chunk assignment as the copies)
+__device__ __forceinline__ void bd_expand_tile_fp8(const uint8_t* raw, bf16* tile16, int lane) {
+    const int c16 = (lane & 7) * 16, r0 = lane >> 3;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int r = 4 * (i & 3) + r0 + (i >> 2) * 16;      // rows 16..31 are V
+        const uint4 w = *reinterpret_cast<const uint4*>(raw + r * D + c16);
+        uint4 a, b;
+        fp8x16_to_f16x16(w, a, b);
+        uint4* dst = reinterpret_cast<uint4*>(tile16 + r * BD_LD + c16);
+        dst[0] = a;
+        dst[1] = b;
+    }
+}
 
-__global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
-                                                               const bf16* __restrict__ v_cache, bf16* __restrict__ out,
-                                                               const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
+// FP8 = true: K and V are read from the e4m3 shadow cache (k8 / v8, one scale per sequence, layer
+// and kv head: scores are multiplied by the K scale, the output by the V scale; reference:
+// decode attention with KV_FP8, csrc/megakernel/split_decode_gemm.cu:950-1310).  The row of
+// the new position was written to the bf16 cache by the preceding kernel; this CTA quantises
+// it into the shadow cache first (split_decode_gemm.cu:487-493).
+template <bool FP8>
+__device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                                                  bf16* __restrict__ out, const int* __restrict__ positions, int layer, int max_seq,
+                                                  size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
+                                                  const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride) {
+    // the scales are set by the quantise kernel before the first step and constant afterwards
+    float ks = 1.f, vs = 1.f;
+    if constexpr (FP8) {
+        ks = kv_fp8_scale_guard(k_scale[(size_t)blockIdx.x * scale_stride + layer * NKV + blockIdx.y]);
+        vs = kv_fp8_scale_guard(v_scale[(size_t)blockIdx.x * scale_stride + layer * NKV + blockIdx.y]);
+    }
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
     extern __shared__ __align__(128) uint8_t bd_smem[];
-    bf16* ring = reinterpret_cast<bf16*>(bd_smem);                                    // [8 warps][3 stages][K 16 rows | V 16 rows][BD_LD]
+    bf16* ring = reinterpret_cast<bf16*>(bd_smem);                                    // [12 warps][2 stages][K 16 rows | V 16 rows][BD_LD]
     bf16* qs = ring + (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS;         // [2][D]
-    bf16* ps = qs + 2 * D;                                                            // [8 warps][2][16]
+    bf16* ps = qs + 2 * D;                                                            // [12 warps][2][16]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x, g = blockIdx.y;
     const int pos = min(max(positions[b], 0), max_seq - 1);
     const int len = pos + 1;
     const int ntiles = (len + 15) >> 4;
-    const bf16* kb = k_cache + (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
-    const bf16* vb = v_cache + (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
+    const size_t head_off = (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
+    const bf16* kb = k_cache + head_off;
+    const bf16* vb = v_cache + head_off;
     bf16* wring = ring + (size_t)warp * BD_STAGES * BD_STAGE_ELEMS;
+    uint8_t* wraw = bd_smem + (size_t)warp * BD8_WARP_BYTES;                          // FP8: [2][raw stage] | f16 tile pair
+    bf16* wtile = reinterpret_cast<bf16*>(wraw + BD_STAGES * BD8_RAW);
+    const uint8_t* k8b = FP8 ? k8 + head_off : nullptr;
+    const uint8_t* v8b = FP8 ? v8 + head_off : nullptr;
 
-    // first two tiles of this warp are requested before anything else
+    // The first tile of this warp is requested before anything else.  FP8: the tile that holds the
+    // new position is requested only after the block barrier below, which orders it after the
+    // quantised row written by threads 0..63.
 #pragma unroll
     for (int s = 0; s < BD_STAGES - 1; ++s) {
         const int t = warp + s * (BD_THREADS / 32);
-        if (t < ntiles) bd_load_tile(wring + s * BD_STAGE_ELEMS, kb, vb, t, len, lane);
+        if (t < ntiles) {
+            if constexpr (FP8) {
+                if (t != ntiles - 1) bd_load_tile_fp8(wraw + s * BD8_RAW, k8b, v8b, t, len, lane);
+            } else {
+                bd_load_tile(wring + s * BD_STAGE_ELEMS, kb, vb, t, len, lane);
+            }
+        }
         cp_async_commit();
     }
-    if (tid < 32) *reinterpret_cast<uint4*>(qs + tid * 8) = *reinterpret_cast<const uint4*>(qkv + (size_t)b * QKV + 2 * g * D + tid * 8);
+    if constexpr (FP8) {
+        if (tid < 64) {
+            const int e4 = 4 * (tid & 31);
+            const bool isk = tid < 32;
+            const uint2 u = *reinterpret_cast<const uint2*>((isk ? kb : vb) + (size_t)pos * D + e4);
+            const float inv = 1.0f / (isk ? ks : vs);
+            *reinterpret_cast<uint32_t*>((isk ? k8 : v8) + head_off + (size_t)pos * D + e4) =
+                f32x4_to_fp8x4(bf_lo(u.x) * inv, bf_hi(u.x) * inv, bf_lo(u.y) * inv, bf_hi(u.y) * inv);
+            __threadfence_block();
+        }
+    }
+    if (tid >= 64 && tid < 96) {
+        const int t8 = tid - 64;
+        uint4 q = *reinterpret_cast<const uint4*>(qkv + (size_t)b * QKV + 2 * g * D + t8 * 8);
+        if constexpr (FP8) {   // f16 tiles are multiplied with an f16 query
+            q.x = pack_f16x2(bf_lo(q.x), bf_hi(q.x)); q.y = pack_f16x2(bf_lo(q.y), bf_hi(q.y));
+            q.z = pack_f16x2(bf_lo(q.z), bf_hi(q.z)); q.w = pack_f16x2(bf_lo(q.w), bf_hi(q.w));
+        }
+        *reinterpret_cast<uint4*>(qs + t8 * 8) = q;
+    }
     __syncthreads();
+    if constexpr (FP8) {
+        if (ntiles - 1 < (BD_STAGES - 1) * (BD_THREADS / 32) && warp == (ntiles - 1) % (BD_THREADS / 32))
+            bd_load_tile_fp8(wraw + ((ntiles - 1) / (BD_THREADS / 32)) * BD8_RAW, k8b, v8b, ntiles - 1, len, lane);
+        cp_async_commit();
+    }
 
     const int gi = lane >> 2, ti = lane & 3;
-    const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+    const float scale = 0.08838834764831845f * ks;  // 1/sqrt(128) (x the K scale)
     float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
     float o[16][4];
 #pragma unroll
@@ -1293,9 +1374,9 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
     {
         const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            qb[ks][0] = gi < 2 ? lds32(qaddr + ks * 32) : 0u;
-            qb[ks][1] = gi < 2 ? lds32(qaddr + ks * 32 + 16) : 0u;
+        for (int ks16 = 0; ks16 < D / 16; ++ks16) {
+            qb[ks16][0] = gi < 2 ? lds32(qaddr + ks16 * 32) : 0u;
+            qb[ks16][1] = gi < 2 ? lds32(qaddr + ks16 * 32 + 16) : 0u;
         }
     }
     bf16* pw = ps + warp * 32;
@@ -1303,21 +1384,28 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
     for (int tile = warp; tile < ntiles; tile += BD_THREADS / 32, ++it) {
         cp_async_wait<BD_STAGES - 2>();   // this tile has landed (one younger group may be in flight)
         __syncwarp();
-        const bf16* st = wring + (it % BD_STAGES) * BD_STAGE_ELEMS;
-        // the stage consumed in the previous iteration is free: request the tile two ahead
+        const bf16* st = FP8 ? wtile : wring + (it % BD_STAGES) * BD_STAGE_ELEMS;
+        // the stage consumed in the previous iteration is free: request the next tile of this warp
         {
             const int tn = tile + (BD_STAGES - 1) * (BD_THREADS / 32);
-            if (tn < ntiles) bd_load_tile(wring + ((it + BD_STAGES - 1) % BD_STAGES) * BD_STAGE_ELEMS, kb, vb, tn, len, lane);
+            if (tn < ntiles) {
+                if constexpr (FP8) bd_load_tile_fp8(wraw + ((it + BD_STAGES - 1) % BD_STAGES) * BD8_RAW, k8b, v8b, tn, len, lane);
+                else bd_load_tile(wring + ((it + BD_STAGES - 1) % BD_STAGES) * BD_STAGE_ELEMS, kb, vb, tn, len, lane);
+            }
             cp_async_commit();
+        }
+        if constexpr (FP8) {
+            bd_expand_tile_fp8(wraw + (it % BD_STAGES) * BD8_RAW, wtile, lane);
+            __syncwarp();
         }
         const uint32_t rowoff = (uint32_t)(((lane & 15) * BD_LD + (lane >> 4) * 8) * 2);
         const uint32_t kaddr = smem_u32(st) + rowoff, vaddr = kaddr + 16 * BD_LD * 2;
         float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
+        for (int ks16 = 0; ks16 < D / 16; ++ks16) {
             uint32_t af[4];
-            ldsm4(af, kaddr + ks * 32);
-            mma16816(c, af, qb[ks][0], qb[ks][1]);
+            ldsm4(af, kaddr + ks16 * 32);
+            mma16816_sel<FP8>(c, af, qb[ks16][0], qb[ks16][1]);
         }
         // lanes with ti == 0 hold head 0 / head 1 of positions gi (c[0], c[1]) and gi + 8 (c[2], c[3])
         const int p_lo = tile * 16 + gi, p_hi = p_lo + 8;
@@ -1346,8 +1434,14 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
         l0 = l0 * cr0 + __shfl_sync(0xffffffffu, u0, 0);
         l1 = l1 * cr1 + __shfl_sync(0xffffffffu, u1, 0);
         if (own) {
-            pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
-            pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+            if constexpr (FP8) {   // probabilities rounded to bf16 as on the bf16 path (exact in f16: 8 significant bits, e <= 1)
+                __half* ph = reinterpret_cast<__half*>(pw);
+                ph[gi] = __float2half_rn(rbf(e00)); ph[gi + 8] = __float2half_rn(rbf(e10));
+                ph[16 + gi] = __float2half_rn(rbf(e01)); ph[16 + gi + 8] = __float2half_rn(rbf(e11));
+            } else {
+                pw[gi] = __float2bfloat16_rn(e00); pw[gi + 8] = __float2bfloat16_rn(e10);
+                pw[16 + gi] = __float2bfloat16_rn(e01); pw[16 + gi + 8] = __float2bfloat16_rn(e11);
+            }
         }
         __syncwarp();
         uint32_t pa[4] = {0u, 0u, 0u, 0u};   // A = P: row gi is head gi (rows 2..15 are zero)
@@ -1364,16 +1458,16 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
         for (int j = 0; j < 8; ++j) {
             uint32_t bv[4];
             ldsm4_t(bv, vaddr + j * 32);
-            mma16816(o[2 * j], pa, bv[0], bv[1]);
-            mma16816(o[2 * j + 1], pa, bv[2], bv[3]);
+            mma16816_sel<FP8>(o[2 * j], pa, bv[0], bv[1]);
+            mma16816_sel<FP8>(o[2 * j + 1], pa, bv[2], bv[3]);
         }
         __syncwarp();
     }
     cp_async_wait_all();
     __syncthreads();   // every warp is done with its ring: the merge buffers reuse it
-    float* s_acc = reinterpret_cast<float*>(bd_smem);          // [8][2][D]
-    float* s_m = s_acc + (BD_THREADS / 32) * 2 * D;            // [8][2]
-    float* s_l = s_m + (BD_THREADS / 32) * 2;                  // [8][2]
+    float* s_acc = reinterpret_cast<float*>(bd_smem);          // [12][2][D]
+    float* s_m = s_acc + (BD_THREADS / 32) * 2 * D;            // [12][2]
+    float* s_l = s_m + (BD_THREADS / 32) * 2;                  // [12][2]
     if (lane == 0) { s_m[warp * 2] = m0; s_m[warp * 2 + 1] = m1; s_l[warp * 2] = l0; s_l[warp * 2 + 1] = l1; }
     if (gi < 2) {
 #pragma unroll
@@ -1393,7 +1487,20 @@ __global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __re
         den = fmaf(s_l[w8 * 2 + hh], f, den);
         num = fmaf(s_acc[(w8 * 2 + hh) * D + d], f, num);
     }
-    out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den);
+    out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den * vs);
+}
+
+__global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                                                               const bf16* __restrict__ v_cache, bf16* __restrict__ out,
+                                                               const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
+    bd_attention_body<false>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, nullptr, nullptr, nullptr, nullptr, 0);
+}
+__global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention_fp8(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
+                                                                   const bf16* __restrict__ v_cache, bf16* __restrict__ out,
+                                                                   const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride,
+                                                                   uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
+                                                                   const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride) {
+    bd_attention_body<true>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, k8, v8, k_scale, v_scale, scale_stride);
 }
 
 // out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
@@ -1647,9 +1754,22 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
 // kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
 extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
 
-extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens, int* out_tokens,
-                                      float* logits_f32, void* stream_v) {
+// attention of one layer of a batched decode step, from the bf16 caches or from the e4m3 shadow caches
+static void launch_bd_attention(int B, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn, int l,
+                                const MqModel* model, size_t seq_stride) {
+    if (kv8)
+        launch_pdl(k_bd_attention_fp8, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn,
+                   (const int*)bb->positions, l, model->max_seq_len, seq_stride, (uint8_t*)kv8->k_fp8, (uint8_t*)kv8->v_fp8, (const float*)kv8->k_scale,
+                   (const float*)kv8->v_scale, model->num_layers * NKV);
+    else
+        launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn,
+                   (const int*)bb->positions, l, model->max_seq_len, seq_stride);
+}
+
+static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, const MqKvFp8* kv8, const int* in_tokens, int* out_tokens,
+                             float* logits_f32, void* stream_v) {
     if (!model || !bb || !in_tokens || !out_tokens) return MQ_ERR_BAD_ARG;
+    if (kv8 && (!kv8->k_fp8 || !kv8->v_fp8 || !kv8->k_scale || !kv8->v_scale)) return MQ_ERR_BAD_ARG;
     if (!bb->k_cache || !bb->v_cache || !bb->positions || !bb->logits || !bb->status) return MQ_ERR_BAD_ARG;
     const MqPrefillBuffers* pb = &bb->act;
     if (!pb->h || !pb->x || !pb->qkv || !pb->attn || !pb->act) return MQ_ERR_BAD_ARG;
@@ -1666,6 +1786,8 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
         cudaGetDevice(&dev);
         if (dev >= 0 && dev < 64 && !bd_attr[dev]) {
             cudaError_t e = cudaFuncSetAttribute(k_bd_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BD_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(k_bd_attention_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BD_SMEM);
             if (e != cudaSuccess) return (int)e;
             bd_attr[dev] = true;
         }
@@ -1688,8 +1810,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
             launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                              (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                              model->max_seq_len, bb->positions, seq_stride, (const float*)part, 4, B, nullptr);
-            launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
-                                                             model->max_seq_len, seq_stride);
+            launch_bd_attention(B, stream, qkv, bb, kv8, attn, l, model, seq_stride);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
             const int ro[1] = {H};
             rc = launch_skinny(wo, ro, 1, attn, QSZ, part, B, QSZ, 8, status, stream);
@@ -1719,8 +1840,7 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                          model->max_seq_len, bb->positions, seq_stride, nullptr, 0, 0, nullptr);
-        launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn, bb->positions, l,
-                                                         model->max_seq_len, seq_stride);
+        launch_bd_attention(B, stream, qkv, bb, kv8, attn, l, model, seq_stride);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
         if (rc) return rc;
         launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, B);
@@ -1735,5 +1855,72 @@ extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers
                                      model->vocab_size, status, stream);
     if (rc) return rc;
     launch_pdl(k_bd_argmax_advance, dim3(B), dim3(1024), 0, stream, (const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, logits_f32);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int mq_launch_decode_batch(const MqModel* model, const MqBatchBuffers* bb, const int* in_tokens, int* out_tokens,
+                                      float* logits_f32, void* stream_v) {
+    return decode_batch_impl(model, bb, nullptr, in_tokens, out_tokens, logits_f32, stream_v);
+}
+
+extern "C" int mq_launch_decode_batch_kv8(const MqModel* model, const MqBatchBuffers* bb, const MqKvFp8* kv8, const int* in_tokens,
+                                          int* out_tokens, float* logits_f32, void* stream_v) {
+    if (!kv8) return MQ_ERR_BAD_ARG;
+    return decode_batch_impl(model, bb, kv8, in_tokens, out_tokens, logits_f32, stream_v);
+}
+
+// ---------------------------------------------------------------- FP8 shadow cache
+// One CTA per (layer, kv head): scale = max |x| over positions [start, end) / 448 (1 for an all-zero
+// span), then every element of the span as e4m3(x / scale), K and V separately (reference:
+// split_quantize_kv_cache_fp8_kernel, csrc/megakernel/split_decode_gemm.cu:223-300).
+__global__ void __launch_bounds__(256) k_kv_quantize_fp8(const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                                                         uint8_t* __restrict__ k8, uint8_t* __restrict__ v8, float* __restrict__ k_scale,
+                                                         float* __restrict__ v_scale, int max_seq, int start, int end) {
+    __shared__ float s_k[8], s_v[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const size_t base = (size_t)blockIdx.x * max_seq * D;
+    const int n8 = (end - start) * (D / 8);                        // 16-byte groups of the span
+    const uint4* kp = reinterpret_cast<const uint4*>(k_cache + base + (size_t)start * D);
+    const uint4* vp = reinterpret_cast<const uint4*>(v_cache + base + (size_t)start * D);
+    auto amax4 = [](const uint4& u) {
+        float m = fmaxf(fabsf(bf_lo(u.x)), fabsf(bf_hi(u.x)));
+        m = fmaxf(m, fmaxf(fabsf(bf_lo(u.y)), fabsf(bf_hi(u.y))));
+        m = fmaxf(m, fmaxf(fabsf(bf_lo(u.z)), fabsf(bf_hi(u.z))));
+        return fmaxf(m, fmaxf(fabsf(bf_lo(u.w)), fabsf(bf_hi(u.w))));
+    };
+    float km = 0.f, vm = 0.f;
+    for (int i = tid; i < n8; i += 256) {
+        km = fmaxf(km, amax4(kp[i]));
+        vm = fmaxf(vm, amax4(vp[i]));
+    }
+    km = warp_max(km);
+    vm = warp_max(vm);
+    if (lane == 0) { s_k[warp] = km; s_v[warp] = vm; }
+    __syncthreads();
+    km = 0.f; vm = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { km = fmaxf(km, s_k[w]); vm = fmaxf(vm, s_v[w]); }
+    const float ks = kv_fp8_scale_of(km), vs = kv_fp8_scale_of(vm);
+    if (tid == 0) { k_scale[blockIdx.x] = ks; v_scale[blockIdx.x] = vs; }
+    const float ik = 1.0f / ks, iv = 1.0f / vs;
+    uint2* k8p = reinterpret_cast<uint2*>(k8 + base + (size_t)start * D);
+    uint2* v8p = reinterpret_cast<uint2*>(v8 + base + (size_t)start * D);
+    for (int i = tid; i < n8; i += 256) {
+        const uint4 a = kp[i], b = vp[i];
+        k8p[i] = make_uint2(f32x4_to_fp8x4(bf_lo(a.x) * ik, bf_hi(a.x) * ik, bf_lo(a.y) * ik, bf_hi(a.y) * ik),
+                            f32x4_to_fp8x4(bf_lo(a.z) * ik, bf_hi(a.z) * ik, bf_lo(a.w) * ik, bf_hi(a.w) * ik));
+        v8p[i] = make_uint2(f32x4_to_fp8x4(bf_lo(b.x) * iv, bf_hi(b.x) * iv, bf_lo(b.y) * iv, bf_hi(b.y) * iv),
+                            f32x4_to_fp8x4(bf_lo(b.z) * iv, bf_hi(b.z) * iv, bf_lo(b.w) * iv, bf_hi(b.w) * iv));
+    }
+}
+
+extern "C" int mq_launch_kv_quantize_fp8(const void* k_cache, const void* v_cache, const MqKvFp8* kv8, int num_layers, int max_seq_len,
+                                         int start_pos, int end_pos, void* stream_v) {
+    if (!k_cache || !v_cache || !kv8 || !kv8->k_fp8 || !kv8->v_fp8 || !kv8->k_scale || !kv8->v_scale) return MQ_ERR_BAD_ARG;
+    if (num_layers <= 0 || max_seq_len <= 0) return MQ_ERR_BAD_ARG;
+    const int start = start_pos < 0 ? 0 : start_pos, end = end_pos > max_seq_len ? max_seq_len : end_pos;
+    if (start >= end) return MQ_OK;                                  // an empty span is a no-op, as in the reference
+    k_kv_quantize_fp8<<<num_layers * NKV, 256, 0, (cudaStream_t)stream_v>>>((const bf16*)k_cache, (const bf16*)v_cache, (uint8_t*)kv8->k_fp8,
+                                                                            (uint8_t*)kv8->v_fp8, kv8->k_scale, kv8->v_scale, max_seq_len, start, end);
     return (int)cudaGetLastError();
 }

@@ -9,11 +9,12 @@ calls the C ABI of libmegaqwen_b200.so for every piece of arithmetic.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
 from . import _lib
-from ._lib import MqDecodeBuffers, MqLayerWeights, MqModel, MqPrefillBuffers
+from ._lib import MqDecodeBuffers, MqKvFp8, MqLayerWeights, MqModel, MqPrefillBuffers
 
 _HIDDEN, _INTER, _NQ, _NKV, _D = 1024, 3072, 16, 8, 128
 _LAYER_SHAPES = [(_HIDDEN,), (_NQ * _D, _HIDDEN), (_NKV * _D, _HIDDEN), (_NKV * _D, _HIDDEN), (_D,), (_D,),
@@ -32,16 +33,25 @@ class MegakernelDecoder:
     arg-max next token and increments the position.  ``prefill_step(ids)`` sets
     ``position = len(ids)`` and returns the token following the prompt.
     ``reset()`` zeroes the KV cache and the position.
+
+    ``kv_fp8=True`` (default: the reference's switch, environment variable
+    ``MEGAQWEN_SPLIT_KV_FP8``, bindings_prefill.cpp:513) keeps an e4m3 shadow of
+    the KV cache with one scale per (layer, kv head) and lets the decode
+    attention read it.  As in the reference (bindings_prefill.cpp:1371-1400) the
+    rows a prefill wrote are quantised, and the scales set from them, right before
+    the next decode launch; decode steps quantise their own rows with those scales.
+    The bf16 caches stay complete (``get_k_cache``).  The persistent kernel reads
+    the bf16 cache only and is not available in this mode.
     """
 
     def __init__(self, embed_weight, layer_weights, final_norm_weight, lm_head_weight, cos_table, sin_table,
-                 num_layers, max_seq_len, max_prefill_len=512, *w4_args, **w4_kwargs):
+                 num_layers, max_seq_len, max_prefill_len=512, *w4_args, kv_fp8=None, **w4_kwargs):
         if not torch.cuda.is_available():
             raise RuntimeError("megaqwen_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
         self._lib = _lib.lib()
         for extra in list(w4_args) + list(w4_kwargs.values()):
             if extra is not None and hasattr(extra, "__len__") and len(extra) > 0:
-                raise RuntimeError("W4 / FP8-KV / paged-KV options are not supported by this engine")
+                raise RuntimeError("W4 / paged-KV options are not supported by this engine")
         if len(layer_weights) != 11 * num_layers:
             raise RuntimeError(f"layer_weights must hold 11 tensors per layer, got {len(layer_weights)} for {num_layers} layers")
         self.device = embed_weight.device
@@ -108,6 +118,17 @@ class MegakernelDecoder:
             self._chain_tokens = None
             self._chain_pos = None
             self._graphs = {}
+            if kv_fp8 is None:
+                kv_fp8 = os.environ.get("MEGAQWEN_SPLIT_KV_FP8", "0").strip().lower() in ("1", "true", "yes", "on")
+            self.kv_fp8 = bool(kv_fp8)
+            self._kv8 = None
+            self._kv8_ready = 0        # positions [0, _kv8_ready) of the shadow cache are current
+            if self.kv_fp8:
+                self.k_cache_fp8_ = torch.zeros(self.k_cache_.shape, dtype=torch.uint8, device=dev)
+                self.v_cache_fp8_ = torch.zeros_like(self.k_cache_fp8_)
+                self.kv_scales_ = torch.ones((2, self.num_layers_, _NKV), dtype=torch.float32, device=dev)   # [k | v]
+                self._kv8 = MqKvFp8(_ptr(self.k_cache_fp8_), _ptr(self.v_cache_fp8_), _ptr(self.kv_scales_[0]), _ptr(self.kv_scales_[1]))
+                self.persistent_available = False
         self._buf = MqDecodeBuffers(_ptr(self.k_cache_), _ptr(self.v_cache_), _ptr(self._hidden), _ptr(self._qkv),
                                     _ptr(self._attn), _ptr(self._act), _ptr(self._partials), _ptr(self._counters),
                                     _ptr(self._slot), _ptr(self._scalars) + 4, nsplit)
@@ -124,10 +145,25 @@ class MegakernelDecoder:
 
     def _launch(self, in_ptr: int, out_ptr: int, pos_ptr: int, logits_ptr, chained: bool) -> None:
         flags = (_lib.MQ_FLAG_CHAINED if chained else 0) | (0 if self.use_pdl else _lib.MQ_FLAG_NO_PDL)
-        rc = self._lib.mq_launch_decode(C.byref(self._model), C.byref(self._buf), in_ptr, out_ptr, pos_ptr,
-                                        logits_ptr, flags, self._stream())
+        if self.kv_fp8:
+            rc = self._lib.mq_launch_decode_kv8(C.byref(self._model), C.byref(self._buf), C.byref(self._kv8), in_ptr, out_ptr,
+                                                pos_ptr, logits_ptr, flags, self._stream())
+        else:
+            rc = self._lib.mq_launch_decode(C.byref(self._model), C.byref(self._buf), in_ptr, out_ptr, pos_ptr,
+                                            logits_ptr, flags, self._stream())
         _lib.check(rc, "mq_launch_decode")
         self.launches += 5 * self.num_layers_ + 1
+
+    def _kv8_sync(self) -> None:
+        """Before a decode launch: rows written by a prefill since the last decode are quantised into
+        the shadow cache and the scales are set from them (the whole prefix, so that one scale
+        covers every cached row).  Not inside a graph capture: callers run it first."""
+        if self.kv_fp8 and self._kv8_ready < self.position_:
+            rc = self._lib.mq_launch_kv_quantize_fp8(_ptr(self.k_cache_), _ptr(self.v_cache_), C.byref(self._kv8), self.num_layers_,
+                                                     self.max_seq_len_, 0, self.position_, self._stream())
+            _lib.check(rc, "mq_launch_kv_quantize_fp8")
+            self.launches += 1
+            self._kv8_ready = self.position_
 
     def _check_status(self, status: int) -> None:
         if status:
@@ -170,6 +206,11 @@ class MegakernelDecoder:
         self.position_ = 0
         self.k_cache_.zero_()
         self.v_cache_.zero_()
+        if self.kv_fp8:
+            self._kv8_ready = 0
+            self.k_cache_fp8_.zero_()
+            self.v_cache_fp8_.zero_()
+            self.kv_scales_.fill_(1.0)
 
     def _single(self, input_token_id: int, logits_ptr) -> int:
         if self.position_ >= self.max_seq_len_:
@@ -178,11 +219,13 @@ class MegakernelDecoder:
             # scalar fills carry the value as a kernel argument: no host buffer to race on
             self._in_token.fill_(int(input_token_id))
             self._pos_dev.fill_(self.position_)
+            self._kv8_sync()
             if logits_ptr is None and self.use_step_graph:
                 self._replay_step_graph()
             else:
                 self._launch(_ptr(self._in_token), _ptr(self._scalars), _ptr(self._pos_dev), logits_ptr, False)
             self.position_ += 1
+            self._kv8_ready = self.position_
             tok, status = self._scalars[:2].tolist()
         self._check_status(status)
         return tok
@@ -225,12 +268,13 @@ class MegakernelDecoder:
             raise RuntimeError(f"{what} would exceed max_seq_len")
         with torch.cuda.device(self.device):
             self._ensure_chain(num_steps)
+            self._kv8_sync()
             tk, ps = self._chain_tokens, self._chain_pos
             if torch.is_tensor(first_token):
                 tk[0:1].copy_(first_token.reshape(1).to(torch.int32), non_blocking=True)
             else:
                 tk[0:1].fill_(int(first_token))
-            if self.use_persistent and use_graph and self.position_ + num_steps <= self._stream_max_context:
+            if self.use_persistent and not self.kv_fp8 and use_graph and self.position_ + num_steps <= self._stream_max_context:
                 self._launch_stream(_ptr(tk), None, _ptr(tk) + 4, num_steps, None, False, None)
                 self.position_ += num_steps
                 return tk[1:num_steps + 1]
@@ -242,6 +286,7 @@ class MegakernelDecoder:
                 for i in range(num_steps):
                     self._launch(_ptr(tk) + 4 * i, _ptr(tk) + 4 * (i + 1), _ptr(ps) + 4 * i, None, i > 0)
             self.position_ += num_steps
+            self._kv8_ready = self.position_
             return tk[1:num_steps + 1]
 
     def _replay_graph(self, num_steps: int) -> None:
@@ -299,6 +344,8 @@ class MegakernelDecoder:
         self.launches += 1
 
     def _check_stream(self, num_steps: int, what: str) -> None:
+        if self.kv_fp8:
+            raise RuntimeError("the persistent kernel reads the bf16 KV cache only (kv_fp8 is on)")
         if not self.persistent_available:
             raise RuntimeError("persistent decode is not available on this device")
         if self.position_ + num_steps >= self.max_seq_len_:
@@ -471,6 +518,7 @@ class MegakernelDecoder:
             _lib.check(rc, "mq_launch_prefill")
             self.launches += self._lib.mq_prefill_launch_count(self.num_layers_)
             self.position_ += n
+            self._kv8_ready = 0        # the prefill wrote bf16 rows only (bindings_prefill.cpp:831)
             tok, status = self._scalars[:2].tolist()
         self._check_status(status)
         if want_logits:
@@ -492,6 +540,7 @@ class MegakernelDecoder:
         n = int(ids.numel())
         with torch.cuda.device(self.device):
             self._ensure_chain(n)
+            self._kv8_sync()
             dev_ids = ids.to(self.device, non_blocking=True)
             tk, ps = self._chain_tokens, self._chain_pos
             _lib.check(self._lib.mq_launch_fill_iota(_ptr(ps), self.position_, n, self._stream()), "mq_launch_fill_iota")
@@ -499,6 +548,7 @@ class MegakernelDecoder:
             for i in range(n):
                 self._launch(_ptr(dev_ids) + 4 * i, _ptr(self._scalars), _ptr(ps) + 4 * i, None, i > 0)
             self.position_ += n
+            self._kv8_ready = self.position_
             tok, status = self._scalars[:2].tolist()
         self._check_status(status)
         return tok
