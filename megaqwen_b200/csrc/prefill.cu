@@ -105,7 +105,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
 // ---------------------------------------------------------------- GEMM  C[M,N] = A[M,K] * B[N,K]^T
 constexpr int GM_BM = 128;
 constexpr int GM_BK = 64;
-constexpr int GM_THREADS = 192;    // warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..5 epilogue
+constexpr int GM_THREADS = 192;    // skinny GEMM: warp 0 TMA, warp 1 MMA + TMEM owner, warps 2..5 epilogue
+// Tile GEMM: eight epilogue warps.  Warps w and w + 4 read the same quarter of the TMEM lanes (a warp may
+// only touch lanes 32 (w % 4) .. + 31) and split the accumulator columns; with four warps the SwiGLU
+// epilogue of a 256 x 256 tile (65 536 silu + products on 128 threads) took as long as its main loop.
+constexpr int GM_EPI_WARPS = 8;
+constexpr int GM_TILE_THREADS = 64 + 32 * GM_EPI_WARPS;
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };   // PARTIAL: fp32 plane blockIdx.z of a K split
 
 // Every kernel of the prefill and batched-decode chains is launched with programmatic
@@ -141,17 +146,21 @@ struct GemmCfg {
     static constexpr int A_BYTES = MT * GM_BM * GM_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + NB * BN * GM_BK * 2;
     static constexpr int STAGES = (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES > 6 ? 6 : (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES;
-    static constexpr int TMEM_COLS = MT * NB * BN;                               // power of two >= 32, at most 512
+    static constexpr int ACC_COLS = MT * NB * BN;                                // accumulator columns in use
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;   // allocations are powers of two
+    static_assert(ACC_COLS <= 512 && BN % 32 == 0, "tensor memory holds 512 columns; the epilogue reads 32 at a time");
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
+// x / (1 + e^-x) with the hardware exponential and reciprocal (2 ulp of fp32; the result is rounded to bf16)
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 template <int BN, int EPI, int MT>
-__global__ void __launch_bounds__(GM_THREADS, MQ_GEMM_MIN_CTAS)
+__global__ void __launch_bounds__(GM_TILE_THREADS, MQ_GEMM_MIN_CTAS)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
        bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
-    pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
-    pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
+    pdl_trigger();   // the next grid may be scheduled already; it waits for this one below, after its own set-up
     // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
     // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
     // and tmB2 (up) for the same tile.
@@ -186,6 +195,9 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+    // Barriers and tensor memory are set up while the preceding grid may still be running; nothing of
+    // global memory has been touched yet.  From here on its results are complete and visible.
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -203,15 +215,20 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
+            // instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3, M >> 4.  EPI_SWIGLU: the gate
+            // and the up tile sit back to back in the stage (2 BN rows of one K-major operand), so ONE
+            // instruction of N = 2 BN fills both accumulators (columns [0, BN) gate, [BN, 2 BN) up).  A
+            // 128 x 128 x 16 instruction reads 8 KB of shared memory for 64 cycles of math, which is the
+            // SM's whole shared-memory bandwidth; at N = 256 it is 12 KB for 128 cycles.
+            constexpr int UMMA_N = Cfg::NB * BN;
+            static_assert(UMMA_N <= 256, "one instruction spans at most 256 columns");
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
             for (int kb = 0; kb < nk; ++kb) {
                 const int s = kb % Cfg::STAGES;
                 mbar_wait(&full[s], (uint32_t)(kb / Cfg::STAGES) & 1u, status);
                 tc_fence_after();
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
                 const uint64_t db = smem_desc_sw128(st + Cfg::A_BYTES);
-                const uint64_t db2 = smem_desc_sw128(st + Cfg::A_BYTES + BN * GM_BK * 2);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {   // accumulator (mt, nb) lives at TMEM column (mt * NB + nb) * BN
                     const uint64_t da = smem_desc_sw128(st + mt * GM_BM * GM_BK * 2);
@@ -219,7 +236,6 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                     for (int k = 0; k < GM_BK / 16; ++k) {
                         const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
                         umma_bf16(tmem_base + mt * Cfg::NB * BN, da + 2 * k, db + 2 * k, idesc, acc);   // +32 bytes per K=16 step
-                        if (EPI == EPI_SWIGLU) umma_bf16(tmem_base + (mt * Cfg::NB + 1) * BN, da + 2 * k, db2 + 2 * k, idesc, acc);
                     }
                 }
                 umma_commit(&empty[s]);     // frees this stage once the MMAs above have read it
@@ -228,16 +244,19 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         }
         __syncwarp();
     } else {
-        // epilogue: warp (2..5) owns TMEM lanes 32*(warp%4) .. +31 = tile rows
+        // epilogue: warp (2..9) owns TMEM lanes 32*(warp%4) .. +31 = tile rows and half of the columns
         mbar_wait(accum, 0, status);
         tc_fence_after();
-        const int quarter = warp & 3;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // the two warps of a quarter take one 128-row accumulator each (MT = 2) or half of the columns (MT = 1)
+        static_assert(GM_EPI_WARPS == 8 && (MT == 2 || (BN / 2) % 32 == 0), "epilogue split");
+        const int cbeg = MT == 2 ? 0 : half * (BN / 2), cend = MT == 2 ? BN : cbeg + BN / 2;
 #pragma unroll 1
-        for (int mt = 0; mt < MT; ++mt) {
+        for (int mt = (MT == 2 ? half : 0); mt < (MT == 2 ? half + 1 : 1); ++mt) {
         const int row = m0 + mt * GM_BM + quarter * 32 + lane;
         const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * Cfg::NB * BN);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = cbeg; c0 < cend; c0 += 32) {
             uint32_t v[32];
             tmem_ld32(trow + c0, v);
             if (EPI == EPI_PARTIAL) {   // raw fp32 accumulators into plane blockIdx.z of C (a float [gridDim.z][M][ldc] array)
@@ -257,7 +276,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 for (int j = 0; j < 16; ++j) {
                     const float g0 = rbf(__uint_as_float(v[2 * j])), g1 = rbf(__uint_as_float(v[2 * j + 1]));
                     const float u0 = rbf(__uint_as_float(u[2 * j])), u1 = rbf(__uint_as_float(u[2 * j + 1]));
-                    out[j] = pack_bf16x2(rbf(silu_f32(g0)) * u0, rbf(silu_f32(g1)) * u1);
+                    out[j] = pack_bf16x2(rbf(silu_fast(g0)) * u0, rbf(silu_fast(g1)) * u1);
                 }
             } else if (EPI == EPI_RESID) {
                 if (row < M) {
@@ -974,11 +993,16 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             // tcgen05.ld / st are warp-wide: the warp rescales together, rows that need none by 1
             const bool grow = (mx - m) * c > 8.0f;            // also true for the first tile (m = -inf)
+            // o_full completes once per key tile and is waited on by parity, so every thread consumes EVERY
+            // phase, in order (a parity wait that is two phases behind returns at once): phase j - 1 here if
+            // the accumulator is rescaled, else just before this tile's probabilities are handed over.
+            bool seen_prev = j == 0;
             if (__any_sync(0xffffffffu, grow)) {
                 const float alpha = grow ? fast_exp2((m - mx) * c) : 1.0f;   // 0 for the first tile
                 if (j > 0) {
                     // the previous P V product must have landed before the accumulator is touched
                     ok = ok && mbar_wait(o_full, (uint32_t)(j - 1) & 1u, status);
+                    seen_prev = true;
                     tc_fence_after();
 #pragma unroll
                     for (int cb = 0; cb < 4; ++cb) {
@@ -1012,6 +1036,7 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             l += rs;
+            if (!seen_prev) ok = ok && mbar_wait(o_full, (uint32_t)(j - 1) & 1u, status);   // P V of tile j - 1 (precedes this tile's anyway)
             fence_async_smem();                               // the tensor core reads P through the async proxy
             mbar_arrive(&p_full[st]);
         }
@@ -1157,7 +1182,7 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
     }
     if (ksplit < 1 || (ksplit > 1 && EPI != EPI_PARTIAL) || K / GM_BK < ksplit) return MQ_ERR_BAD_ARG;
     dim3 grid(N / BN, (M + GM_BM * MT - 1) / (GM_BM * MT), ksplit);
-    launch_pdl(k_gemm<BN, EPI, MT>, dim3(grid), dim3(GM_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
+    launch_pdl(k_gemm<BN, EPI, MT>, dim3(grid), dim3(GM_TILE_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
                                                              C, R, M, N, K, ldc, status);
     return (int)cudaGetLastError();
 }
@@ -1661,7 +1686,8 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
             if (rc) return rc;
             launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, S);
         }
-        rc = big ? launch_gemm<128, EPI_SWIGLU, 2>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream)
+        // from 1024 rows on: 256 x (96 gate + 96 up) tiles, 128 CTAs at 1024 rows and two even rounds at 2048
+        rc = big ? launch_gemm<96, EPI_SWIGLU, 2>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream)
                  : launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
         if (rc) return rc;
         if (splitk) {
