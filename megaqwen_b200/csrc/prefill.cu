@@ -838,17 +838,18 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __re
 //     O_j = P V     A = P tile [128 q x 128 keys] (bf16, written by the softmax warps),
 //                   B = V^T tile [128 d x 128 keys] from a transposed copy of the layer's V rows
 // (all operands K-major under the 128-byte swizzle, fetched by TMA).  Warp 0 feeds the K / V^T
-// rings, warp 1 issues the MMAs, warps 2-5 hold ONE QUERY ROW PER THREAD: they read the row's
+// rings, warp 1 issues the MMAs, warps 2-9 hold HALF A QUERY ROW PER THREAD: they read the row's
 // scores from tensor memory (tcgen05.ld), keep the running max / sum and write the probabilities
 // rounded to bf16 as the next MMA's A operand; the output accumulates in tensor memory and is
 // rescaled (tcgen05.ld / st) only when the maximum has grown by more than 2^8.  S is
 // double-buffered: QK^T of tile j + 1 runs while tile j is in the softmax.  Replaces the reference's serial-per-warp kernel and its experimental tiles
 // (csrc/megakernel/fused_prefill_kernels.inl:265-342, 347-445, 486-613).
 constexpr int TA_BQ = 128, TA_BK = 128;
-constexpr int TA_THREADS = 192;
+constexpr int TA_THREADS = 320;                             // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 constexpr int TA_TILE_BYTES = 128 * 128 * 2;               // two 64-column halves of [128 rows x 128 bytes]
 constexpr int TA_HALF_BYTES = TA_TILE_BYTES / 2;
-constexpr size_t TA_SMEM = (size_t)7 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/;   // Q, 2 K, 2 V^T, 2 P
+constexpr size_t TA_SMEM = (size_t)7 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + TA_BQ * 8 /*row exchange*/;   // Q, 2 K, 2 V^T, 2 P
+static_assert(TA_SMEM <= 232448, "shared memory of one CTA");
 constexpr uint32_t TA_TMEM_COLS = 512;                      // S0 | S1 | O (128 columns each)
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -871,11 +872,12 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint64_t* v_full = bars + 5;                 // 2
     uint64_t* v_empty = bars + 7;                // 2
     uint64_t* s_full = bars + 9;                 // 2
-    uint64_t* s_free = bars + 11;                // 2 (128 arrivals)
-    uint64_t* p_full = bars + 13;                // 2 (128 arrivals)
+    uint64_t* s_free = bars + 11;                // 2 (256 arrivals)
+    uint64_t* p_full = bars + 13;                // 2 (256 arrivals)
     uint64_t* p_free = bars + 15;                // 2
     uint64_t* o_full = bars + 17;                // 1
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    float (*xm)[2] = reinterpret_cast<float(*)[2]>(bars + 20);   // [128][2]: the two half-row maxima (at the end: sums) of a query row
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int head = blockIdx.x, g = head / (NQ / NKV);
@@ -887,7 +889,7 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 128); mbar_init(&p_full[i], 128); mbar_init(&p_free[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 256); mbar_init(&p_full[i], 256); mbar_init(&p_free[i], 1);
         }
         mbar_init(o_full, 1);
         mbar_fence_init();
@@ -961,36 +963,53 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         __syncwarp();
     } else {
-        // softmax warps: thread owns query row r = TMEM lane r.  The output accumulates in tensor
-        // memory over all key tiles; it is only rescaled when the running maximum has grown by more
-        // than 2^8 since the value the accumulator is scaled to (then p <= 256 in between, exact in
-        // fp32 and harmless in bf16), which after the first tiles practically never happens.
-        const int quarter = warp & 3;
+        // softmax warps: TWO threads per query row r = TMEM lane r (warps w and w + 4 share a quarter of the
+        // lanes); thread `half` owns keys [64 half, 64 half + 64) of every key tile and output columns
+        // [64 half, +64).  The two exchange their half-row maxima through shared memory (one 64-thread
+        // named barrier per tile), so both scale by the same running maximum.  The output accumulates in
+        // tensor memory over all key tiles; it is only rescaled when the running maximum has grown by
+        // more than 2^8 since the value the accumulator is scaled to (then p <= 256 in between, exact in
+        // fp32 and harmless in bf16), which after the first tiles practically never happens.  With one
+        // thread per row the 128 exponentials per tile on four warps (one per scheduler) bounded the kernel.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;
         const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+        const uint32_t col_off = (uint32_t)(half * 64);
         const int qpos = pos0 + q0 + r;                       // absolute position of this thread's query
         const float c = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
         float m = -INFINITY, l = 0.f;                         // m: the maximum the sums are scaled to (raw score units)
         bool ok = true;
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
         for (int j = 0; j < nt; ++j) {
             const int st = j & 1;
-            const uint32_t ts = tmem_base + st * 128 + lane_off;
+            const uint32_t ts = tmem_base + st * 128 + lane_off + col_off;
             ok = ok && mbar_wait(&s_full[st], (uint32_t)(j >> 1) & 1u, status);
             tc_fence_after();
-            const int k0 = j * TA_BK;
-            const bool diag = k0 + TA_BK - 1 > qpos;          // some keys of this tile lie beyond the query
-            uint32_t sv[128];
+            const int k0 = j * TA_BK + half * 64;             // first key of this thread's half
+            const bool diag = k0 + 63 > qpos;                 // some keys of this half lie beyond the query
+            uint32_t sv[64];
 #pragma unroll
-            for (int cb = 0; cb < 4; ++cb) tmem_ld32_nowait(ts + cb * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cb * 32]));
+            for (int cb = 0; cb < 2; ++cb) tmem_ld32_nowait(ts + cb * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[cb * 32]));
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(&s_free[st]);                         // the scores are in registers: S[st] may be overwritten
-            float mx = -INFINITY;
+            float mh = -INFINITY;
+            if (__any_sync(0xffffffffu, diag)) {              // only the last one or two key tiles of a query tile
 #pragma unroll
-            for (int i = 0; i < 128; ++i) {
-                if (diag && k0 + i > qpos) sv[i] = 0xff800000u;   // -inf
-                mx = fmaxf(mx, __uint_as_float(sv[i]));
+                for (int i = 0; i < 64; ++i) {
+                    if (k0 + i > qpos) sv[i] = 0xff800000u;   // -inf
+                    mh = fmaxf(mh, __uint_as_float(sv[i]));
+                }
+            } else {
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int i = 0; i < 64; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[i]));
+                mh = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
+            xm[r][half] = mh;
+            pair_sync();
+            const float mx = fmaxf(xm[r][0], xm[r][1]);       // the same value in both threads of the row
+            pair_sync();                                      // both have read it: the slot is free for the next tile
             // tcgen05.ld / st are warp-wide: the warp rescales together, rows that need none by 1
             const bool grow = (mx - m) * c > 8.0f;            // also true for the first tile (m = -inf)
             // o_full completes once per key tile and is waited on by parity, so every thread consumes EVERY
@@ -1005,12 +1024,12 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     seen_prev = true;
                     tc_fence_after();
 #pragma unroll
-                    for (int cb = 0; cb < 4; ++cb) {
+                    for (int cb = 0; cb < 2; ++cb) {
                         uint32_t v[32];
-                        tmem_ld32(tmem_o + lane_off + cb * 32, v);
+                        tmem_ld32(tmem_o + lane_off + col_off + cb * 32, v);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        tmem_st32(tmem_o + lane_off + cb * 32, v);
+                        tmem_st32(tmem_o + lane_off + col_off + cb * 32, v);
                     }
                     tc_fence_before();
                 }
@@ -1019,11 +1038,12 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             const float mc = m * c;
             if (j >= 2) ok = ok && mbar_wait(&p_free[st], (uint32_t)((j >> 1) - 1) & 1u, status);
-            // probabilities -> bf16 -> A operand of the P V product (K-major, 128-byte swizzle)
+            // probabilities -> bf16 -> A operand of the P V product (K-major, 128-byte swizzle); this thread's
+            // 64 keys are the 64-column half `half` of the tile
             float rs = 0.f;
-            uint8_t* prow = sP + st * TA_TILE_BYTES + r * 128;
+            uint8_t* prow = sP + st * TA_TILE_BYTES + half * TA_HALF_BYTES + r * 128;
 #pragma unroll
-            for (int c16 = 0; c16 < 16; ++c16) {              // 16-byte chunk = 8 keys
+            for (int c16 = 0; c16 < 8; ++c16) {               // 16-byte chunk = 8 keys
                 uint32_t pk[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -1032,23 +1052,24 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     rs += p0 + p1;
                     pk[e] = pack_bf16x2(p0, p1);
                 }
-                uint8_t* dst = prow + (c16 >> 3) * TA_HALF_BYTES + (((c16 & 7) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(prow + ((c16 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             l += rs;
             if (!seen_prev) ok = ok && mbar_wait(o_full, (uint32_t)(j - 1) & 1u, status);   // P V of tile j - 1 (precedes this tile's anyway)
             fence_async_smem();                               // the tensor core reads P through the async proxy
             mbar_arrive(&p_full[st]);
         }
-        // the last P V product, then out = O / l
+        // the last P V product, then out = O / l (l = the sum of the two half-row sums)
         ok = ok && mbar_wait(o_full, (uint32_t)(nt - 1) & 1u, status);
         tc_fence_after();
-        const float inv = 1.0f / l;
-        bf16* orow = out + (size_t)(q0 + r) * QSZ + head * D;
+        xm[r][half] = l;
+        pair_sync();
+        const float inv = 1.0f / (xm[r][0] + xm[r][1]);
+        bf16* orow = out + (size_t)(q0 + r) * QSZ + head * D + half * 64;
 #pragma unroll
-        for (int cb = 0; cb < 4; ++cb) {
+        for (int cb = 0; cb < 2; ++cb) {
             uint32_t v[32];
-            tmem_ld32(tmem_o + lane_off + cb * 32, v);
+            tmem_ld32(tmem_o + lane_off + col_off + cb * 32, v);
             if (q0 + r < S) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -1066,28 +1087,37 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 // vt[g][d][key] = v_cache[layer][g][key][d] for key < n_keys, zero up to key_pad (the B operand of
-// the P V product must be K-major, i.e. contiguous along the keys).  grid (key_pad / 64, 8).
-__global__ void __launch_bounds__(256) k_pf_transpose_v(const bf16* __restrict__ v_cache, bf16* __restrict__ vt, int layer, int max_seq,
+// the P V product must be K-major, i.e. contiguous along the keys).  grid (key_pad / 32, 8), 128
+// threads: 32 keys x 128 dims per CTA, four independent 16-byte loads per thread, then thread d
+// writes the 64 contiguous bytes of its row.
+constexpr int TV_KEYS = 32;
+__global__ void __launch_bounds__(128) k_pf_transpose_v(const bf16* __restrict__ v_cache, bf16* __restrict__ vt, int layer, int max_seq,
                                                         int n_keys, int key_pad) {
     pdl_trigger();
     pdl_wait();
-    __shared__ bf16 tile[64][D + 2];
-    const int g = blockIdx.y, key0 = blockIdx.x * 64;
+    __shared__ __align__(16) bf16 tile[TV_KEYS][D + 8];
+    const int g = blockIdx.y, key0 = blockIdx.x * TV_KEYS, tid = threadIdx.x;
     const bf16* src = v_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
-    for (int i = threadIdx.x; i < 64 * (D / 2); i += 256) {
-        const int k = i / (D / 2), dp = i % (D / 2);
-        const uint32_t u = key0 + k < n_keys ? *reinterpret_cast<const uint32_t*>(src + (size_t)(key0 + k) * D + 2 * dp) : 0u;
-        *reinterpret_cast<uint32_t*>(&tile[k][2 * dp]) = u;
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = tid + 128 * i, k = c >> 4, c8 = (c & 15) * 8;          // chunk c: key k, dims c8 .. c8 + 7
+        v[i] = key0 + k < n_keys ? *reinterpret_cast<const uint4*>(src + (size_t)(key0 + k) * D + c8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = tid + 128 * i, k = c >> 4, c8 = (c & 15) * 8;
+        *reinterpret_cast<uint4*>(&tile[k][c8]) = v[i];
     }
     __syncthreads();
-    const int d = threadIdx.x >> 1, kh = threadIdx.x & 1;
-    bf16* dst = vt + ((size_t)(g * D + d)) * key_pad + key0 + 32 * kh;
+    const int d = tid;
+    bf16* dst = vt + ((size_t)(g * D + d)) * key_pad + key0;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < TV_KEYS / 8; ++q) {
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int k = 32 * kh + 8 * q + 2 * e;
+            const int k = 8 * q + 2 * e;
             const uint16_t a = *reinterpret_cast<const uint16_t*>(&tile[k][d]), b = *reinterpret_cast<const uint16_t*>(&tile[k + 1][d]);
             w[e] = (uint32_t)a | ((uint32_t)b << 16);
         }
@@ -1661,12 +1691,12 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
                  : launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                                (const bf16*)w.v_proj, QSZ, KVSZ);
         if (rc) return rc;
-        launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, 1)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+        launch_pdl(k_pf_qknorm_rope, dim3(dim3(S, S <= 1024 ? 4 : 2)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0, nullptr, 0, 0, nullptr);
         if (use_tc) {
             // V^T of this layer's keys goes into the (still unused) MLP activation buffer
-            launch_pdl(k_pf_transpose_v, dim3(key_pad / 64, NKV), dim3(256), 0, stream, (const bf16*)dbuf->v_cache, act, l, model->max_seq_len,
+            launch_pdl(k_pf_transpose_v, dim3(key_pad / TV_KEYS, NKV), dim3(128), 0, stream, (const bf16*)dbuf->v_cache, act, l, model->max_seq_len,
                        pos0 + S, key_pad);
             launch_pdl(k_pf_attention_tc, dim3(NQ, (S + TA_BQ - 1) / TA_BQ), dim3(TA_THREADS), TA_SMEM, stream, map_q, map_k, map_vt, attn, S, pos0, l,
                        model->max_seq_len, status);
