@@ -271,6 +271,10 @@ typedef struct MqBatchBuffers {
     int batch;
     float* partials;          /* optional fp32 scratch of the split-K path (batch <= 64):        */
     size_t partials_bytes;    /* at least 4 * batch * 6144 * 4 bytes; NULL = 128-row tile GEMMs  */
+    float* attn_parts;        /* optional fp32 scratch that lets several CTAs share the keys of  */
+    size_t attn_parts_bytes;  /* one (sequence, kv head): at least batch * 8 * 4 * 2 * 130 * 4   */
+    unsigned int* attn_tickets; /* bytes, with u32 [batch * 8] counters zeroed ONCE by the caller; */
+                              /* NULL = one CTA per (sequence, kv head)                          */
 } MqBatchBuffers;
 
 /* One greedy decode step for every sequence of the batch: sequence b consumes

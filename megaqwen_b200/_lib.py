@@ -48,7 +48,8 @@ class MqPrefillBuffers(C.Structure):
 class MqBatchBuffers(C.Structure):
     _fields_ = [("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("positions", C.c_void_p), ("logits", C.c_void_p),
                 ("act", MqPrefillBuffers), ("status", C.c_void_p), ("batch", C.c_int), ("partials", C.c_void_p),
-                ("partials_bytes", C.c_size_t)]
+                ("partials_bytes", C.c_size_t), ("attn_parts", C.c_void_p), ("attn_parts_bytes", C.c_size_t),
+                ("attn_tickets", C.c_void_p)]
 
 
 class MqKvFp8(C.Structure):

@@ -61,6 +61,10 @@ class MegakernelBatchDecoder:
             self._slot = torch.zeros(1, dtype=torch.int64, device=dev)
             self._tok_a = torch.zeros(B, dtype=i32, device=dev)
             self._partials = torch.empty(4 * min(B, 64) * 2 * _INTER, dtype=torch.float32, device=dev)
+            # split-KV scratch of the batched attention: (m, l, acc[128]) per (sequence, kv head, part, head) and one ticket per item
+            self._attn_parts = torch.empty(B * _NKV * 4 * 2 * (_D + 2), dtype=torch.float32, device=dev)
+            self._attn_tickets = torch.zeros(B * _NKV, dtype=i32, device=dev)
+            self.use_split_kv = True
             self.use_splitk = True
             self.use_packed_prefill = True
             self._chain = None
@@ -84,7 +88,9 @@ class MegakernelBatchDecoder:
     def _bb(self, batch: int) -> MqBatchBuffers:
         return MqBatchBuffers(_ptr(self.k_cache_), _ptr(self.v_cache_), _ptr(self._positions), _ptr(self._logits),
                               self._pf, _ptr(self._scalars) + 4, batch,
-                              _ptr(self._partials) if self.use_splitk else None, self._partials.numel() * 4)
+                              _ptr(self._partials) if self.use_splitk else None, self._partials.numel() * 4,
+                              _ptr(self._attn_parts) if self.use_split_kv else None, self._attn_parts.numel() * 4,
+                              _ptr(self._attn_tickets) if self.use_split_kv else None)
 
     def check_status(self) -> None:
         st = int(self._scalars[1].item())
@@ -242,7 +248,7 @@ class MegakernelBatchDecoder:
                 self._graphs = {}
             ch = self._chain
             ch[0].copy_(first.to(self.device))
-            key = (num_steps, B, self.use_splitk)     # the partials pointer is baked into the captured launches
+            key = (num_steps, B, self.use_splitk, self.use_split_kv)     # the scratch pointers are baked into the captured launches
             if use_graph:
                 g = self._graphs.get(key)
                 if g is None:

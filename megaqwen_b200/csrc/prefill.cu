@@ -1290,14 +1290,19 @@ namespace mq {
 // are M, the two heads two of the eight N columns), softmax of the tile, P rounded to bf16,
 // out += P . V_tile (ldmatrix.trans on V).  About a sixth of the instructions of an fp32-FMA
 // loop over the same bytes, which is what bounded the FMA version at 2.7 TB/s.
-constexpr int BD_THREADS = 384, BD_STAGES = 2, BD_LD = D + 8;   // 12 warps x 2 stages x 8.5 KB = 209 KB
+constexpr int BD_STAGES = 2, BD_LD = D + 8;                                     // per warp: 2 stages x 8.5 KB
 constexpr int BD_STAGE_ELEMS = 2 * 16 * BD_LD;                                  // K tile then V tile
-constexpr size_t BD_SMEM = (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS * 2 + 2 * D * 2 + (BD_THREADS / 32) * 32 * 2;
+// Two shapes: twelve warps, one CTA per SM (209 KB), or six warps, two CTAs per SM (105 KB each).  The
+// SM streams with twelve warps either way; the small shape doubles the CTA slots, so a batch of up to
+// 2 x SMs (sequence, kv head) items runs in ONE round instead of two half-empty ones.
+constexpr size_t bd_smem_bytes(int warps) { return (size_t)warps * BD_STAGES * BD_STAGE_ELEMS * 2 + 2 * D * 2 + warps * 32 * 2; }
+constexpr int BD_MAX_PARTS = 4;                                                 // CTAs that may share one item's keys
+constexpr int BD_PART = D + 2;                                                  // m, l, acc[128] of one head of one part
 // FP8 cache: a warp's ring holds the raw e4m3 rows (K 16 x 128 bytes, then V), two stages, followed
 // by ONE padded f16 tile pair the current stage is expanded into before it is multiplied
 constexpr int BD8_RAW = 2 * 16 * D;                                             // bytes per raw stage
 constexpr int BD8_WARP_BYTES = BD_STAGES * BD8_RAW + BD_STAGE_ELEMS * 2;
-static_assert((size_t)(BD_THREADS / 32) * BD8_WARP_BYTES <= (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS * 2, "the fp8 ring fits the bf16 ring");
+static_assert(BD8_WARP_BYTES <= BD_STAGES * BD_STAGE_ELEMS * 2, "the fp8 ring fits the bf16 ring");
 
 __device__ __forceinline__ void bd_load_tile(bf16* stage, const bf16* kb, const bf16* vb, int tile, int len, int lane) {
     // 16 rows x 16 chunks of 16 bytes for K and the same for V: 16 copies per lane.  Rows past
@@ -1346,11 +1351,16 @@ __device__ __forceinline__ void bd_expand_tile_fp8(const uint8_t* raw, bf16* til
 // decode attention with KV_FP8, csrc/megakernel/split_decode_gemm.cu:950-1310).  The row of
 // the new position was written to the bf16 cache by the preceding kernel; this CTA quantises
 // it into the shadow cache first (split_decode_gemm.cu:487-493).
-template <bool FP8>
+// nparts > 1: the key tiles of an item are split over nparts CTAs (blockIdx.z); each writes its
+// (m, l, acc) to `parts` and takes a ticket, and the CTA that takes the last one merges them (no CTA
+// waits for another).  tickets: one zero-initialised counter per (sequence, kv head), reset by the merger.
+template <bool FP8, int WARPS>
 __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                                   bf16* __restrict__ out, const int* __restrict__ positions, int layer, int max_seq,
                                                   size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
-                                                  const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride) {
+                                                  const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride,
+                                                  float* __restrict__ parts, unsigned int* __restrict__ tickets) {
+    constexpr int BD_THREADS = WARPS * 32;
     // the scales are set by the quantise kernel before the first step and constant afterwards
     float ks = 1.f, vs = 1.f;
     if constexpr (FP8) {
@@ -1367,7 +1377,12 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     const int b = blockIdx.x, g = blockIdx.y;
     const int pos = min(max(positions[b], 0), max_seq - 1);
     const int len = pos + 1;
-    const int ntiles = (len + 15) >> 4;
+    const int ntiles_all = (len + 15) >> 4;
+    // this CTA's share of the item's key tiles: [tile_lo, ntiles)
+    const int nparts = (int)gridDim.z, part = (int)blockIdx.z;
+    const int tile_lo = (int)(((long long)part * ntiles_all) / nparts);
+    const int ntiles = (int)(((long long)(part + 1) * ntiles_all) / nparts);
+    const bool has_new = part == nparts - 1;                 // the part that holds the new position's tile
     const size_t head_off = (size_t)b * seq_stride + ((size_t)(layer * NKV + g) * max_seq) * D;
     const bf16* kb = k_cache + head_off;
     const bf16* vb = v_cache + head_off;
@@ -1382,10 +1397,10 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     // quantised row written by threads 0..63.
 #pragma unroll
     for (int s = 0; s < BD_STAGES - 1; ++s) {
-        const int t = warp + s * (BD_THREADS / 32);
+        const int t = tile_lo + warp + s * (BD_THREADS / 32);
         if (t < ntiles) {
             if constexpr (FP8) {
-                if (t != ntiles - 1) bd_load_tile_fp8(wraw + s * BD8_RAW, k8b, v8b, t, len, lane);
+                if (!(has_new && t == ntiles - 1)) bd_load_tile_fp8(wraw + s * BD8_RAW, k8b, v8b, t, len, lane);
             } else {
                 bd_load_tile(wring + s * BD_STAGE_ELEMS, kb, vb, t, len, lane);
             }
@@ -1393,7 +1408,7 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
         cp_async_commit();
     }
     if constexpr (FP8) {
-        if (tid < 64) {
+        if (tid < 64 && has_new) {
             const int e4 = 4 * (tid & 31);
             const bool isk = tid < 32;
             const uint2 u = *reinterpret_cast<const uint2*>((isk ? kb : vb) + (size_t)pos * D + e4);
@@ -1414,8 +1429,9 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     }
     __syncthreads();
     if constexpr (FP8) {
-        if (ntiles - 1 < (BD_STAGES - 1) * (BD_THREADS / 32) && warp == (ntiles - 1) % (BD_THREADS / 32))
-            bd_load_tile_fp8(wraw + ((ntiles - 1) / (BD_THREADS / 32)) * BD8_RAW, k8b, v8b, ntiles - 1, len, lane);
+        const int tl = ntiles - 1 - tile_lo;                  // the deferred tile, counted from this part's first
+        if (has_new && tl >= 0 && tl < (BD_STAGES - 1) * (BD_THREADS / 32) && warp == tl % (BD_THREADS / 32))
+            bd_load_tile_fp8(wraw + (tl / (BD_THREADS / 32)) * BD8_RAW, k8b, v8b, ntiles - 1, len, lane);
         cp_async_commit();
     }
 
@@ -1436,7 +1452,7 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     }
     bf16* pw = ps + warp * 32;
     int it = 0;
-    for (int tile = warp; tile < ntiles; tile += BD_THREADS / 32, ++it) {
+    for (int tile = tile_lo + warp; tile < ntiles; tile += BD_THREADS / 32, ++it) {
         cp_async_wait<BD_STAGES - 2>();   // this tile has landed (one younger group may be in flight)
         __syncwarp();
         const bf16* st = FP8 ? wtile : wring + (it % BD_STAGES) * BD_STAGE_ELEMS;
@@ -1520,9 +1536,9 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     }
     cp_async_wait_all();
     __syncthreads();   // every warp is done with its ring: the merge buffers reuse it
-    float* s_acc = reinterpret_cast<float*>(bd_smem);          // [12][2][D]
-    float* s_m = s_acc + (BD_THREADS / 32) * 2 * D;            // [12][2]
-    float* s_l = s_m + (BD_THREADS / 32) * 2;                  // [12][2]
+    float* s_acc = reinterpret_cast<float*>(bd_smem);          // [WARPS][2][D]
+    float* s_m = s_acc + WARPS * 2 * D;                        // [WARPS][2]
+    float* s_l = s_m + WARPS * 2;                              // [WARPS][2]
     if (lane == 0) { s_m[warp * 2] = m0; s_m[warp * 2 + 1] = m1; s_l[warp * 2] = l0; s_l[warp * 2 + 1] = l1; }
     if (gi < 2) {
 #pragma unroll
@@ -1530,32 +1546,70 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
             *reinterpret_cast<float2*>(s_acc + (warp * 2 + gi) * D + j * 8 + 2 * ti) = make_float2(o[j][0], o[j][1]);
     }
     __syncthreads();
-    if (tid >= 2 * D) return;
-    const int hh = tid >> 7, d = tid & 127;
-    float M = -1e30f;
+    const size_t item = (size_t)b * NKV + g;
+    for (int idx = tid; idx < 2 * D; idx += BD_THREADS) {
+        const int hh = idx >> 7, d = idx & 127;
+        float M = -1e30f;
 #pragma unroll
-    for (int w8 = 0; w8 < BD_THREADS / 32; ++w8) M = fmaxf(M, s_m[w8 * 2 + hh]);
-    float num = 0.f, den = 0.f;
+        for (int w8 = 0; w8 < WARPS; ++w8) M = fmaxf(M, s_m[w8 * 2 + hh]);
+        float num = 0.f, den = 0.f;
 #pragma unroll
-    for (int w8 = 0; w8 < BD_THREADS / 32; ++w8) {
-        const float f = expf(s_m[w8 * 2 + hh] - M);
-        den = fmaf(s_l[w8 * 2 + hh], f, den);
-        num = fmaf(s_acc[(w8 * 2 + hh) * D + d], f, num);
+        for (int w8 = 0; w8 < WARPS; ++w8) {
+            const float f = expf(s_m[w8 * 2 + hh] - M);
+            den = fmaf(s_l[w8 * 2 + hh], f, den);
+            num = fmaf(s_acc[(w8 * 2 + hh) * D + d], f, num);
+        }
+        if (nparts == 1) {
+            out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den * vs);
+        } else {
+            float* pp = parts + ((item * BD_MAX_PARTS + part) * 2 + hh) * BD_PART;
+            pp[2 + d] = num;
+            if (d == 0) { pp[0] = M; pp[1] = den; }
+        }
     }
-    out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den * vs);
+    if (nparts == 1) return;
+    // the block barrier orders every thread's partial before thread 0's release; the CTA that takes the
+    // last ticket acquires the others' partials with the same instruction
+    __shared__ int s_last;
+    __syncthreads();
+    if (tid == 0) {
+        unsigned int t;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(tickets + item) : "memory");
+        s_last = (t == (unsigned int)(nparts - 1));
+        if (s_last) tickets[item] = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    for (int idx = tid; idx < 2 * D; idx += BD_THREADS) {
+        const int hh = idx >> 7, d = idx & 127;
+        const float* pb = parts + (item * BD_MAX_PARTS * 2 + hh) * BD_PART;
+        float mj[BD_MAX_PARTS], M = -1e30f;
+#pragma unroll
+        for (int j = 0; j < BD_MAX_PARTS; ++j) {
+            mj[j] = j < nparts ? ld_cg_f32(pb + (size_t)j * 2 * BD_PART) : -1e30f;
+            M = fmaxf(M, mj[j]);
+        }
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int j = 0; j < BD_MAX_PARTS; ++j) {
+            if (j < nparts) {
+                const float f = expf(mj[j] - M);
+                den = fmaf(ld_cg_f32(pb + (size_t)j * 2 * BD_PART + 1), f, den);
+                num = fmaf(ld_cg_f32(pb + (size_t)j * 2 * BD_PART + 2 + d), f, num);
+            }
+        }
+        out[(size_t)b * QSZ + (2 * g + hh) * D + d] = __float2bfloat16_rn(num / den * vs);
+    }
 }
 
-__global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
-                                                               const bf16* __restrict__ v_cache, bf16* __restrict__ out,
-                                                               const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride) {
-    bd_attention_body<false>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, nullptr, nullptr, nullptr, nullptr, 0);
-}
-__global__ void __launch_bounds__(BD_THREADS, 1) k_bd_attention_fp8(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache,
-                                                                   const bf16* __restrict__ v_cache, bf16* __restrict__ out,
-                                                                   const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride,
-                                                                   uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
-                                                                   const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride) {
-    bd_attention_body<true>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, k8, v8, k_scale, v_scale, scale_stride);
+template <bool FP8, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 6 ? 2 : 1)
+k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
+               const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
+               const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride, float* __restrict__ parts,
+               unsigned int* __restrict__ tickets) {
+    bd_attention_body<FP8, WARPS>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, k8, v8, k_scale, v_scale, scale_stride, parts,
+                                  tickets);
 }
 
 // out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
@@ -1810,16 +1864,50 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
 // kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
 extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
 
+// How a batched attention launch is shaped for `items` = 8 x batch (sequence, kv head) pairs: six-warp
+// CTAs (two per SM) while everything fits one round, with the keys of an item split over up to four
+// CTAs when there are few items; twelve-warp CTAs (one per SM), one per item, beyond.  (Splitting the
+// keys there as well, 7 rounds of half items instead of 4 of whole ones at batch 64, was measured
+// slower: 3.02 vs 2.68 ms per step, each CTA pays about 4 us to fill its rings and merge its warps.)
+// Depends on the batch size only, so a captured graph stays valid.
+struct BdShape { int warps, nparts; };
+static BdShape bd_shape(int items, int sms, bool can_split) {
+    if (items > 2 * sms) return {12, 1};
+    const int p = can_split ? (2 * sms) / items : 1;
+    return {6, p < 1 ? 1 : (p > BD_MAX_PARTS ? BD_MAX_PARTS : p)};
+}
+
+template <bool FP8, int WARPS>
+static int bd_set_smem() {
+    static bool done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_bd_attention<FP8, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bd_smem_bytes(WARPS));
+        if (e != cudaSuccess) return (int)e;
+        done[dev] = true;
+    }
+    return MQ_OK;
+}
+
 // attention of one layer of a batched decode step, from the bf16 caches or from the e4m3 shadow caches
-static void launch_bd_attention(int B, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn, int l,
+template <bool FP8, int WARPS>
+static void launch_bd_attention_t(int B, int nparts, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn,
+                                  int l, const MqModel* model, size_t seq_stride) {
+    launch_pdl(k_bd_attention<FP8, WARPS>, dim3(B, NKV, nparts), dim3(WARPS * 32), bd_smem_bytes(WARPS), stream, qkv, (const bf16*)bb->k_cache,
+               (const bf16*)bb->v_cache, attn, (const int*)bb->positions, l, model->max_seq_len, seq_stride,
+               (uint8_t*)(kv8 ? kv8->k_fp8 : nullptr), (uint8_t*)(kv8 ? kv8->v_fp8 : nullptr), (const float*)(kv8 ? kv8->k_scale : nullptr),
+               (const float*)(kv8 ? kv8->v_scale : nullptr), model->num_layers * NKV, bb->attn_parts, bb->attn_tickets);
+}
+static void launch_bd_attention(int B, BdShape sh, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn, int l,
                                 const MqModel* model, size_t seq_stride) {
-    if (kv8)
-        launch_pdl(k_bd_attention_fp8, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn,
-                   (const int*)bb->positions, l, model->max_seq_len, seq_stride, (uint8_t*)kv8->k_fp8, (uint8_t*)kv8->v_fp8, (const float*)kv8->k_scale,
-                   (const float*)kv8->v_scale, model->num_layers * NKV);
-    else
-        launch_pdl(k_bd_attention, dim3(dim3(B, NKV)), dim3(BD_THREADS), BD_SMEM, stream, qkv, (const bf16*)bb->k_cache, (const bf16*)bb->v_cache, attn,
-                   (const int*)bb->positions, l, model->max_seq_len, seq_stride);
+    if (kv8) {
+        if (sh.warps == 6) launch_bd_attention_t<true, 6>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        else launch_bd_attention_t<true, 12>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+    } else {
+        if (sh.warps == 6) launch_bd_attention_t<false, 6>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        else launch_bd_attention_t<false, 12>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+    }
 }
 
 static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, const MqKvFp8* kv8, const int* in_tokens, int* out_tokens,
@@ -1836,21 +1924,26 @@ static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, con
     bf16* h = (bf16*)pb->h; bf16* x = (bf16*)pb->x; bf16* qkv = (bf16*)pb->qkv; bf16* attn = (bf16*)pb->attn; bf16* act = (bf16*)pb->act;
     unsigned int* status = bb->status;
     const size_t seq_stride = (size_t)model->num_layers * NKV * model->max_seq_len * D;
+    int rc = bd_set_smem<false, 6>();
+    if (rc == MQ_OK) rc = bd_set_smem<false, 12>();
+    if (rc == MQ_OK) rc = bd_set_smem<true, 6>();
+    if (rc == MQ_OK) rc = bd_set_smem<true, 12>();
+    if (rc != MQ_OK) return rc;
+    static int sm_count[64] = {0};
     {
-        static bool bd_attr[64] = {false};
         int dev = 0;
         cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && !bd_attr[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(k_bd_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BD_SMEM);
-            if (e != cudaSuccess) return (int)e;
-            e = cudaFuncSetAttribute(k_bd_attention_fp8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BD_SMEM);
-            if (e != cudaSuccess) return (int)e;
-            bd_attr[dev] = true;
-        }
+        if (dev < 0 || dev >= 64) return MQ_ERR_UNSUPPORTED;
+        if (!sm_count[dev]) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count[dev] <= 0) return MQ_ERR_UNSUPPORTED;
     }
+    int dev_now = 0;
+    cudaGetDevice(&dev_now);
+    const bool can_split = bb->attn_parts != nullptr && bb->attn_tickets != nullptr &&
+                           bb->attn_parts_bytes >= (size_t)B * NKV * BD_MAX_PARTS * 2 * BD_PART * sizeof(float);
+    const BdShape shape = bd_shape(B * NKV, sm_count[dev_now], can_split);
     launch_pdl(k_pf_embed, dim3(B), dim3(128), 0, stream, in_tokens, (const bf16*)model->embed, h, model->vocab_size, status,
                (const bf16*)nullptr, 0, 0);
-    int rc;
     const size_t need_part = (size_t)4 * B * 2 * I * sizeof(float);   // largest partial: gate|up, 4 K-splits
     const bool skinny = B <= 64 && bb->partials != nullptr && bb->partials_bytes >= need_part;
     if (skinny) {
@@ -1866,7 +1959,7 @@ static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, con
             launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                              (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                              model->max_seq_len, bb->positions, seq_stride, (const float*)part, 4, B, nullptr);
-            launch_bd_attention(B, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+            launch_bd_attention(B, shape, stream, qkv, bb, kv8, attn, l, model, seq_stride);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
             const int ro[1] = {H};
             rc = launch_skinny(wo, ro, 1, attn, QSZ, part, B, QSZ, 8, status, stream);
@@ -1896,7 +1989,7 @@ static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, con
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                          model->max_seq_len, bb->positions, seq_stride, nullptr, 0, 0, nullptr);
-        launch_bd_attention(B, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        launch_bd_attention(B, shape, stream, qkv, bb, kv8, attn, l, model, seq_stride);
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
         if (rc) return rc;
         launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, B);

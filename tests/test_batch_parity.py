@@ -194,3 +194,41 @@ def test_sequential_prefill_is_reproducible(setup):
     finally:
         bd.use_packed_prefill = True
     bd.check_status()
+
+
+def test_small_batch_splits_keys_over_ctas():
+    """With few (sequence, kv head) items the keys of each item are dealt to up to four CTAs, which merge
+    through tickets: same logits as one CTA per item up to the summation order, and as the restatement."""
+    from megaqwen_b200.batch import MegakernelBatchDecoder
+    from oracle.qwen3_restatement import RestatedQwen3
+    lens = [700, 300, 33, 5]                 # 5 keys: three of the four parts of that item are empty
+    w = random_weights(QWEN3_TINY, 1024)
+    lw = [t.cuda() for t in w["layer_weights"]]
+    e = w["embed_weight"].cuda()
+    bd = MegakernelBatchDecoder(e, lw, w["final_norm_weight"].cuda(), e, w["cos_table"].cuda(), w["sin_table"].cuda(),
+                                QWEN3_TINY.num_layers, 1024, 4)
+    prompts = [random_prompt(QWEN3_TINY, n, 8, i) for i, n in enumerate(lens)]
+    refs = [RestatedQwen3(QWEN3_TINY, w, 1024) for _ in lens]
+    cur = [int(r.forward(p).argmax()) for r, p in zip(refs, prompts)]
+    ref_lg = [r.forward([c]) for r, c in zip(refs, cur)]
+    got = {}
+    for split in (True, False):
+        bd.reset()
+        bd.use_split_kv = split
+        bd.prefill_batch(prompts)
+        _, lg = bd.decode_batch(torch.tensor(cur, dtype=torch.int32), return_logits=True)
+        got[split] = lg.cpu()
+        for b in range(len(lens)):
+            rep = logit_report(got[split][b], ref_lg[b])
+            assert rep["max"] <= 6e-2 and rep["mean"] <= 8e-3, (split, b, rep)
+    d = (got[True] - got[False]).abs()
+    assert float(d.max()) <= 6.25e-2 and float(d.mean()) <= 4e-3, (float(d.max()), float(d.mean()))
+    # the tickets are back at zero: a second step merges as well
+    bd.use_split_kv = True
+    nxt = [int(l.argmax()) for l in ref_lg]
+    _, lg2 = bd.decode_batch(torch.tensor(nxt, dtype=torch.int32), return_logits=True)
+    for b, r in enumerate(refs):
+        rep = logit_report(lg2[b].cpu(), r.forward([nxt[b]]))
+        assert rep["max"] <= 6e-2 and rep["mean"] <= 8e-3, (b, rep)
+    assert int(bd._attn_tickets.abs().sum()) == 0
+    bd.check_status()
