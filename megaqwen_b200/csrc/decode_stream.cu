@@ -49,8 +49,16 @@
 
 namespace mq {
 
-constexpr int ST_WARPS = 8;
-constexpr int ST_THREADS = ST_WARPS * 32;        // 256: every warp streams, multiplies and polls
+#ifndef MQ_ST_WARPS
+#define MQ_ST_WARPS 8
+#endif
+// Eight warps measured faster than sixteen (421 vs 471 us per token at context 1): a GEMV stage is
+// bound by its block barriers, the partial-sum reduction and the publishing, not by the two to
+// six units a warp multiplies in it, and all of those cost more with 512 threads.
+constexpr int ST_WARPS = MQ_ST_WARPS;            // every warp streams and multiplies its own columns
+constexpr int ST_THREADS = ST_WARPS * 32;
+constexpr int ST_VT = 256;                       // threads 0..255 (warps 0..7) also do the vector work: norms, attention, publishing
+constexpr int ST_VW = ST_VT / 32;
 constexpr uint32_t ST_UNIT = 2048;               // bytes per ring slot = one bulk copy = 4 blocks of 512 bytes
 #ifndef MQ_ST_NSLOT
 #define MQ_ST_NSLOT 4
@@ -78,22 +86,28 @@ struct StPlan {
     int od_row0, od_ng;        // rows of Wo and Wd
     int gu_row0, gu_np;        // rows of Wg / Wu: first row and number of (8 gate + 8 up) tiles
     int lm_row0, lm_nt;        // LM head: first vocabulary row and number of 16-row tiles
-    uint32_t layer_units;      // 2 KB units per layer and warp
+    uint32_t layer_units;      // unused (the units per layer differ from warp to warp: st_layer_units)
     uint32_t pad_[3];
     unsigned long long stream_off;   // byte offset of this CTA's streams (warp 0 first) in the packed buffer
     unsigned long long pad2_;
 };
 static_assert(sizeof(StPlan) == 64, "plan layout");
 
-// units per warp of one phase: a full tile holds K/8 columns x 16 rows per warp, a half tile 8 rows
-__host__ __device__ constexpr uint32_t st_phase_units(int K, int ng) { return (uint32_t)((ng >> 1) * (K / 512) + (ng & 1) * (K / 1024)); }
-__host__ __device__ inline uint32_t st_layer_units(const StPlan& p) {
-    return st_phase_units(H, p.a_ng) + st_phase_units(QSZ, p.od_ng) + st_phase_units(H, 2 * p.gu_np) + st_phase_units(I, p.od_ng);
+// Units of warp w in one phase of ng 8-row groups over K columns.  A full tile (16 rows) is split by
+// columns: warp w multiplies columns [w K / W, (w + 1) K / W), K / (64 W) units.  The half tile (8 rows,
+// the last group of an odd count) is K / 128 units of 128 columns: warp w takes units w, w + W, ..
+__host__ __device__ constexpr uint32_t st_half_units(int K, int w) { return (uint32_t)((K / 128 > w) ? (K / 128 - w + ST_WARPS - 1) / ST_WARPS : 0); }
+__host__ __device__ constexpr uint32_t st_phase_units(int K, int ng, int w) {
+    return (uint32_t)((ng >> 1) * (K / (64 * ST_WARPS))) + ((ng & 1) ? st_half_units(K, w) : 0u);
+}
+static_assert(H % (64 * ST_WARPS) == 0 && QSZ % (64 * ST_WARPS) == 0 && I % (64 * ST_WARPS) == 0, "column split of a full tile");
+__host__ __device__ inline uint32_t st_layer_units(const StPlan& p, int w) {
+    return st_phase_units(H, p.a_ng, w) + st_phase_units(QSZ, p.od_ng, w) + st_phase_units(H, 2 * p.gu_np, w) + st_phase_units(I, p.od_ng, w);
 }
 // LM tiles of warp w: tiles w, w + 8, .. of the CTA's lm_nt tiles
 __host__ __device__ inline uint32_t st_lm_tiles(const StPlan& p, int w) { return p.lm_nt > w ? (uint32_t)(p.lm_nt - w + ST_WARPS - 1) / ST_WARPS : 0u; }
 __host__ __device__ inline uint32_t st_step_units(const StPlan& p, int w, int num_layers) {
-    return (uint32_t)num_layers * p.layer_units + st_lm_tiles(p, w) * ST_LM_TILE_UNITS;
+    return (uint32_t)num_layers * st_layer_units(p, w) + st_lm_tiles(p, w) * ST_LM_TILE_UNITS;
 }
 
 // Scratch (caller-owned, zeroed once): tagged exchange vectors, split-KV partials, arg-max keys
@@ -230,32 +244,25 @@ __device__ __forceinline__ uint2 tagged_to_bf16x4(const uint4& v) {
     return o;
 }
 
-// Thread t of the 256 consumers gathers words 4 (t + 256 k) .. + 3, k < NCH, of a tagged vector
-// into shared memory as bf16.  All loads are issued before the first tag check.
-template <int NCH>
-__device__ __forceinline__ void poll_vector(Poller& po, const uint32_t* src, uint32_t tag16, bf16* dst, int tid) {
-    uint4 v[NCH];
+// Warp `warp` gathers the columns of ITS half-tile units (128 columns each: units warp, warp + W, ..) of a
+// tagged vector of K words, which is all its share of a K-split GEMV needs: no block barrier, and the
+// warp starts as soon as its own words are in.  All loads are issued before the first tag check.
+template <int K>
+__device__ __forceinline__ void poll_units(Poller& po, const uint32_t* src, uint32_t tag16, bf16* dst, int warp, int lane) {
+    constexpr int NU = (K / 128 + ST_WARPS - 1) / ST_WARPS;
+    uint4 v[NU];
 #pragma unroll
-    for (int k = 0; k < NCH; ++k) v[k] = ld_relaxed_v4(src + 4 * (tid + k * ST_THREADS));
-#pragma unroll
-    for (int k = 0; k < NCH; ++k) {
-        if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + 4 * (tid + k * ST_THREADS), tag16);
-        *reinterpret_cast<uint2*>(dst + 4 * (tid + k * ST_THREADS)) = tagged_to_bf16x4(v[k]);
+    for (int k = 0; k < NU; ++k) {
+        const int u = warp + k * ST_WARPS;
+        if (u < K / 128) v[k] = ld_relaxed_v4(src + u * 128 + lane * 4);
     }
-}
-
-// Warp `warp` gathers ITS slice of a tagged vector (words warp * 32 * NCH * 4 ..), which is all a
-// K-split GEMV needs of it: no block barrier, and the warp starts as soon as its own words are in.
-template <int NCH>
-__device__ __forceinline__ void poll_slice(Poller& po, const uint32_t* src, uint32_t tag16, bf16* dst, int warp, int lane) {
-    const int base = warp * (32 * NCH * 4) + lane * 4;
-    uint4 v[NCH];
 #pragma unroll
-    for (int k = 0; k < NCH; ++k) v[k] = ld_relaxed_v4(src + base + k * 128);
-#pragma unroll
-    for (int k = 0; k < NCH; ++k) {
-        if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + base + k * 128, tag16);
-        *reinterpret_cast<uint2*>(dst + base + k * 128) = tagged_to_bf16x4(v[k]);
+    for (int k = 0; k < NU; ++k) {
+        const int u = warp + k * ST_WARPS;
+        if (u < K / 128) {
+            if (!Poller::tags_ok(v[k], tag16)) v[k] = po.spin4(src + u * 128 + lane * 4, tag16);
+            *reinterpret_cast<uint2*>(dst + u * 128 + lane * 4) = tagged_to_bf16x4(v[k]);
+        }
     }
     __syncwarp();
 }
@@ -334,10 +341,10 @@ struct WRing {
 };
 
 // ------------------------------------------------------------------ GEMV on the packed stream
-// One phase = `ntf` full tiles (16 rows) and `nh` (0/1) half tile (8 rows); warp w multiplies
-// columns [w kw, (w + 1) kw) of every row (kw = K / 8) with its slice of the activation vector
-// (bf16, shared memory).  Stream of the warp: per full tile kw / 64 units, then kw / 128 units
-// of the half tile.  A unit is four 512-byte blocks, 16 bytes per lane and block:
+// One phase = `ntf` full tiles (16 rows) and `nh` (0/1) half tile (8 rows).  Of a full tile warp w
+// multiplies columns [w K / W, (w + 1) K / W) with its slice of the activation vector (bf16, shared
+// memory); of the half tile the 128-column units w, w + W, ..  Stream of the warp: per full tile
+// K / (64 W) units, then its units of the half tile.  A unit is four 512-byte blocks, 16 bytes per lane and block:
 //   full tile, block s = k-step s of the unit (columns c = C0 + 16 tig + 4 s):
 //       W[g][c, c+1] | W[g+8][c, c+1] | W[g][c+2, c+3] | W[g+8][c+2, c+3]      (a0 a1 a2 a3)
 //   half tile, block u = k-steps 2u, 2u+1 (columns c = C0 + 32 tig + 8 u):
@@ -365,18 +372,18 @@ __device__ __forceinline__ void full_unit(WRing& rg, float (&c)[4][4], uint32_t 
     rg.release(lane);
 }
 
-__device__ __forceinline__ void gemv_phase(WRing& rg, int ntf, int nh, int kw, uint32_t xs_addr, float* red) {
+__device__ __forceinline__ void gemv_phase(WRing& rg, int ntf, int nh, int K, uint32_t xs_addr, float* red) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t xw = xs_addr + (uint32_t)(warp * kw) * 2u;           // this warp's slice of the vector
+    const int cpw = K / ST_WARPS;                                        // this warp's columns of a full tile
     float* rw = red + warp * ST_RED_ROWS + (lane >> 2);
 #pragma unroll 1
     for (int t = 0; t < ntf; ++t) {
         float c[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
-        const uint32_t xl = xw + (uint32_t)(lane & 3) * 32u;
+        const uint32_t xl = xs_addr + (uint32_t)(warp * cpw) * 2u + (uint32_t)(lane & 3) * 32u;
 #pragma unroll 1
-        for (int i = 0; i < kw; i += 64) full_unit(rg, c, xl + (uint32_t)i * 2u, lane);
+        for (int i = 0; i < cpw; i += 64) full_unit(rg, c, xl + (uint32_t)i * 2u, lane);
         if ((lane & 3) == 0) {
             rw[t * 16] = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]);
             rw[t * 16 + 8] = (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]);
@@ -386,13 +393,12 @@ __device__ __forceinline__ void gemv_phase(WRing& rg, int ntf, int nh, int kw, u
         float c[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) { c[q][0] = 0.f; c[q][1] = 0.f; c[q][2] = 0.f; c[q][3] = 0.f; }
-        const uint32_t xl = xw + (uint32_t)(lane & 3) * 64u;
         const bool odd = ((lane >> 2) & 1) != 0;
 #pragma unroll 1
-        for (int i = 0; i < kw; i += 128) {
+        for (int u = warp; u < K / 128; u += ST_WARPS) {
             const uint32_t sa = rg.acquire() + (uint32_t)lane * 16u;
             const uint4 a0 = lds128(sa), a1 = lds128(sa + 512u), a2 = lds128(sa + 1024u), a3 = lds128(sa + 1536u);
-            const uint32_t xa = xl + (uint32_t)i * 2u;
+            const uint32_t xa = xs_addr + (uint32_t)u * 256u + (uint32_t)(lane & 3) * 64u;
             const uint4 x0 = lds128(xa), x1 = lds128(xa + 16u), x2 = lds128(xa + 32u), x3 = lds128(xa + 48u);
             {
                 // One mma per block: rows 0-7 of the A tile are the 8 weight rows at k-step 2u, rows
@@ -406,6 +412,7 @@ __device__ __forceinline__ void gemv_phase(WRing& rg, int ntf, int nh, int kw, u
             }
             rg.release(lane);
         }
+        // a warp without a unit of the half tile contributes zeros
         if ((lane & 3) == 0) rw[ntf * 16] = ((c[0][0] + c[0][3]) + (c[1][0] + c[1][3])) + ((c[2][0] + c[2][3]) + (c[3][0] + c[3][3]));
     }
 }
@@ -473,7 +480,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
     bf16* kt = reinterpret_cast<bf16*>(smem_raw + (size_t)ST_WARPS * ST_NSLOT * ST_SLOT_BYTES);   // [ST_KV_CAP][ST_KV_LD]
     bf16* vt = kt + (size_t)ST_KV_CAP * ST_KV_LD;
     bf16* xs = vt + (size_t)ST_KV_CAP * ST_KV_LD;                                // [3072] activation vector of a GEMV phase
-    float* red = reinterpret_cast<float*>(xs + I);                               // [8][ST_RED_ROWS] per-warp partial sums
+    float* red = reinterpret_cast<float*>(xs + I);                               // [ST_WARPS][ST_RED_ROWS] per-warp partial sums
     float* wacc = reinterpret_cast<float*>(xs);                                  // [8][2][128], attention only (over xs + red)
     bf16* raw = reinterpret_cast<bf16*>(red + ST_WARPS * ST_RED_ROWS);           // [4][128] raw q(2g) | q(2g+1) | k | v
     bf16* qs = raw + 4 * D;                                                      // [2][128] normalised, rotated query heads
@@ -593,29 +600,34 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             // ---------------- phase A: RMSNorm + rows of [Wq;Wk;Wv]
             if (n_a > 0) {
-                const uint2 wv = __ldg(reinterpret_cast<const uint2*>(nrm + 4 * tid));      // input_layernorm
-                float v0, v1, v2, v3;
-                if (l == 0) {
-                    const uint2 u = __ldg(reinterpret_cast<const uint2*>(erow + 4 * tid));
-                    v0 = bf_lo(u.x); v1 = bf_hi(u.x); v2 = bf_lo(u.y); v3 = bf_hi(u.y);
-                } else {
-                    const uint4 u = po.words4(xh + 4 * tid, t16_prev);
-                    v0 = bf_hi(u.x); v1 = bf_hi(u.y); v2 = bf_hi(u.z); v3 = bf_hi(u.w);
+                uint2 wv = make_uint2(0u, 0u);
+                float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+                if (tid < ST_VT) {
+                    wv = __ldg(reinterpret_cast<const uint2*>(nrm + 4 * tid));              // input_layernorm
+                    if (l == 0) {
+                        const uint2 u = __ldg(reinterpret_cast<const uint2*>(erow + 4 * tid));
+                        v0 = bf_lo(u.x); v1 = bf_hi(u.x); v2 = bf_lo(u.y); v3 = bf_hi(u.y);
+                    } else {
+                        const uint4 u = po.words4(xh + 4 * tid, t16_prev);
+                        v0 = bf_hi(u.x); v1 = bf_hi(u.y); v2 = bf_hi(u.z); v3 = bf_hi(u.w);
+                    }
+                    ST_T1(l, 0);
+                    const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
+                    if (lane == 0) ssp[warp] = part;
                 }
-                ST_T1(l, 0);
-                const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
-                if (lane == 0) ssp[warp] = part;
                 consumer_bar();
-                float ss = 0.f;
+                if (tid < ST_VT) {
+                    float ss = 0.f;
 #pragma unroll
-                for (int i = 0; i < ST_WARPS; ++i) ss += ssp[i];
-                const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
-                uint2 o;
-                o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
-                o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
-                *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                    for (int i = 0; i < ST_VW; ++i) ss += ssp[i];
+                    const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+                    uint2 o;
+                    o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
+                    o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
+                    *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                }
                 consumer_bar();
-                gemv_phase(rg, pl.a_ng >> 1, pl.a_ng & 1, H / 8, smem_u32(xs), red);
+                gemv_phase(rg, pl.a_ng >> 1, pl.a_ng & 1, H, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_a) {
                     float s = 0.f;
@@ -672,7 +684,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                 } else if (warp >= 4) {
                     // rows between n and the end of the last 16-position tile are multiplied by p = 0
                     const int n16 = (n + 15) & ~15;
-                    for (int i = (warp - 4) * 32 + lane; i < (n16 - n) * 16; i += 128)
+                    for (int i = (warp - 4) * 32 + lane; i < (n16 - n) * 16; i += (ST_WARPS - 4) * 32)
                         *reinterpret_cast<uint4*>(vt + (size_t)(n + (i >> 4)) * ST_KV_LD + (i & 15) * 8) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 consumer_bar();
@@ -688,7 +700,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                     for (int j = 0; j < 16; ++j) { o[j][0] = 0.f; o[j][1] = 0.f; o[j][2] = 0.f; o[j][3] = 0.f; }
                     const uint32_t qaddr = smem_u32(qs) + (uint32_t)((gi & 1) * D + 2 * ti) * 2u;
                     bf16* pw = ps + warp * 32;
-                    for (int tile = warp; tile * 16 < n; tile += ST_WARPS) {
+                    for (int tile = warp; tile * 16 < n && warp < ST_VW; tile += ST_VW) {
                         const uint32_t rowoff = (uint32_t)(((tile * 16 + (lane & 15)) * ST_KV_LD + (lane >> 4) * 8) * 2);
                         float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -745,23 +757,24 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                         }
                         __syncwarp();
                     }
-                    if (lane == 0) { wm[warp * 2] = m0; wm[warp * 2 + 1] = m1; wl[warp * 2] = l0; wl[warp * 2 + 1] = l1; }
-                    if (gi < 2) {
+                    if (lane == 0 && warp < ST_VW) { wm[warp * 2] = m0; wm[warp * 2 + 1] = m1; wl[warp * 2] = l0; wl[warp * 2 + 1] = l1; }
+                    if (gi < 2 && warp < ST_VW) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             *reinterpret_cast<float2*>(wacc + (warp * 2 + gi) * D + j * 8 + 2 * ti) = make_float2(o[j][0], o[j][1]);
                     }
                 }
                 consumer_bar();
-                const int hh = tid >> 7, d = tid & 127;
+                const int hh = (tid >> 7) & 1, d = tid & 127;
+                const bool vthread = tid < ST_VT;              // the merge, the publishing and the split merge are the vector threads' work
                 float acc = 0.f;
-                {
+                if (vthread) {
                     float M = -1e30f;
 #pragma unroll
-                    for (int w8 = 0; w8 < ST_WARPS; ++w8) M = fmaxf(M, wm[w8 * 2 + hh]);
+                    for (int w8 = 0; w8 < ST_VW; ++w8) M = fmaxf(M, wm[w8 * 2 + hh]);
                     float lsum = 0.f;
 #pragma unroll
-                    for (int w8 = 0; w8 < ST_WARPS; ++w8) {
+                    for (int w8 = 0; w8 < ST_VW; ++w8) {
                         const float f = expf(wm[w8 * 2 + hh] - M);
                         lsum = fmaf(wl[w8 * 2 + hh], f, lsum);
                         acc = fmaf(wacc[(w8 * 2 + hh) * D + d], f, acc);
@@ -770,7 +783,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
                 }
                 consumer_bar();        // (M, l) published; every read of kt / vt / wacc of this layer is done
                 const int qhead = 2 * g + hh;
-                if (ap.n_act == 1) {
+                if (!vthread) {
+                    // warps 8.. have nothing to publish
+                } else if (ap.n_act == 1) {
                     publish(xattn, qhead * D + d, rbf(acc / ml[hh * 2 + 1]), t16);
                     ST_T1(l, 3);
                 } else {
@@ -822,9 +837,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             // ---------------- phase C: rows of Wo + residual
             if (n_od > 0) {
-                poll_slice<2>(po, xattn, t16, xs, warp, lane);      // this warp's 256 columns
+                poll_units<QSZ>(po, xattn, t16, xs, warp, lane);    // the columns of this warp's units
                 ST_T1(l, 5);
-                gemv_phase(rg, pl.od_ng >> 1, pl.od_ng & 1, QSZ / 8, smem_u32(xs), red);
+                gemv_phase(rg, 0, pl.od_ng, QSZ, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_od) {
                     float s = 0.f;
@@ -838,23 +853,29 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             // ---------------- phase D: RMSNorm + gate / up rows + SiLU * up
             if (n_gu > 0) {
-                const uint2 wv = __ldg(reinterpret_cast<const uint2*>(nrm + H + 4 * tid));   // post_attention_layernorm
-                const uint4 u = po.words4(xh1 + 4 * tid, t16);
-                const float v0 = bf_hi(u.x), v1 = bf_hi(u.y), v2 = bf_hi(u.z), v3 = bf_hi(u.w);
-                ST_T1(l, 7);
-                const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
-                if (lane == 0) ssp[warp] = part;
+                uint2 wv = make_uint2(0u, 0u);
+                float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+                if (tid < ST_VT) {
+                    wv = __ldg(reinterpret_cast<const uint2*>(nrm + H + 4 * tid));          // post_attention_layernorm
+                    const uint4 u = po.words4(xh1 + 4 * tid, t16);
+                    v0 = bf_hi(u.x); v1 = bf_hi(u.y); v2 = bf_hi(u.z); v3 = bf_hi(u.w);
+                    ST_T1(l, 7);
+                    const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
+                    if (lane == 0) ssp[warp] = part;
+                }
                 consumer_bar();
-                float ss = 0.f;
+                if (tid < ST_VT) {
+                    float ss = 0.f;
 #pragma unroll
-                for (int i = 0; i < ST_WARPS; ++i) ss += ssp[i];
-                const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
-                uint2 o;
-                o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
-                o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
-                *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                    for (int i = 0; i < ST_VW; ++i) ss += ssp[i];
+                    const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+                    uint2 o;
+                    o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
+                    o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
+                    *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                }
                 consumer_bar();
-                gemv_phase(rg, pl.gu_np, 0, H / 8, smem_u32(xs), red);
+                gemv_phase(rg, pl.gu_np, 0, H, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_gu) {
                     const int t = tid >> 3, i = tid & 7;
@@ -872,9 +893,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
 
             // ---------------- phase E: rows of Wd + residual
             if (n_od > 0) {
-                poll_slice<3>(po, xact, t16, xs, warp, lane);       // this warp's 384 columns
+                poll_units<I>(po, xact, t16, xs, warp, lane);       // the columns of this warp's units
                 ST_T1(l, 9);
-                gemv_phase(rg, pl.od_ng >> 1, pl.od_ng & 1, I / 8, smem_u32(xs), red);
+                gemv_phase(rg, 0, pl.od_ng, I, smem_u32(xs), red);
                 consumer_bar();
                 if (tid < n_od) {
                     float s = 0.f;
@@ -891,21 +912,27 @@ __global__ void __launch_bounds__(ST_THREADS, 1) k_decode_stream(StreamArgs a) {
         // ---------------- final RMSNorm + LM head tiles + arg-max
         {
             ST_T0();
-            const uint2 wv = __ldg(reinterpret_cast<const uint2*>(a.final_norm + 4 * tid));
-            const uint4 u = po.words4(xh + 4 * tid, t16_prev);
-            const float v0 = bf_hi(u.x), v1 = bf_hi(u.y), v2 = bf_hi(u.z), v3 = bf_hi(u.w);
-            ST_T1(L, 11);
-            const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
-            if (lane == 0) ssp[warp] = part;
+            uint2 wv = make_uint2(0u, 0u);
+            float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+            if (tid < ST_VT) {
+                wv = __ldg(reinterpret_cast<const uint2*>(a.final_norm + 4 * tid));
+                const uint4 u = po.words4(xh + 4 * tid, t16_prev);
+                v0 = bf_hi(u.x); v1 = bf_hi(u.y); v2 = bf_hi(u.z); v3 = bf_hi(u.w);
+                ST_T1(L, 11);
+                const float part = warp_sum(fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, v3 * v3))));
+                if (lane == 0) ssp[warp] = part;
+            }
             consumer_bar();
-            float ss = 0.f;
+            if (tid < ST_VT) {
+                float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < ST_WARPS; ++i) ss += ssp[i];
-            const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
-            uint2 o;
-            o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
-            o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
-            *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+                for (int i = 0; i < ST_VW; ++i) ss += ssp[i];
+                const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
+                uint2 o;
+                o.x = pack_bf16x2(rbf(bf_lo(wv.x) * rbf(v0 * r)), rbf(bf_hi(wv.x) * rbf(v1 * r)));
+                o.y = pack_bf16x2(rbf(bf_lo(wv.y) * rbf(v2 * r)), rbf(bf_hi(wv.y) * rbf(v3 * r)));
+                *reinterpret_cast<uint2*>(xs + 4 * tid) = o;
+            }
             consumer_bar();
 
             float* lg = nullptr;
@@ -1008,14 +1035,15 @@ __device__ __forceinline__ void unit_word_pos(bool full_tile, int unit_in_tile, 
     }
 }
 
-// grid (CTAs, 8 warps, z); one layer of one warp's stream per (x, y)
+// grid (CTAs, warps, z); one layer of one warp's stream per (x, y)
 __global__ void k_pack_layer(const StPlan* plans, MqLayerWeights w, uint8_t* packed, int layer, int num_layers) {
     const StPlan pl = plans[blockIdx.x];
     const int warp = blockIdx.y;
     size_t woff = 0;
     for (int v = 0; v < warp; ++v) woff += (size_t)st_step_units(pl, v, num_layers) * ST_UNIT;
-    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + woff + (size_t)layer * pl.layer_units * ST_UNIT);
-    const uint32_t nwords = pl.layer_units * (ST_UNIT / 4);
+    const uint32_t layer_units = st_layer_units(pl, warp);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + woff + (size_t)layer * layer_units * ST_UNIT);
+    const uint32_t nwords = layer_units * (ST_UNIT / 4);
     // units of the four phases, in stream order
     const int ng[4] = {pl.a_ng, pl.od_ng, 2 * pl.gu_np, pl.od_ng};
     const int Ks[4] = {H, QSZ, H, I};
@@ -1023,15 +1051,15 @@ __global__ void k_pack_layer(const StPlan* plans, MqLayerWeights w, uint8_t* pac
         uint32_t unit = wi / (ST_UNIT / 4);
         const uint32_t wd = wi % (ST_UNIT / 4);
         int phase = 0;
-        while (phase < 3 && unit >= st_phase_units(Ks[phase], ng[phase])) { unit -= st_phase_units(Ks[phase], ng[phase]); ++phase; }
-        const int K = Ks[phase], kw = K / 8;
+        while (phase < 3 && unit >= st_phase_units(Ks[phase], ng[phase], warp)) { unit -= st_phase_units(Ks[phase], ng[phase], warp); ++phase; }
+        const int K = Ks[phase];
         const int ntf = ng[phase] >> 1;
-        const uint32_t upt = (uint32_t)(kw / 64);                 // units per full tile
+        const uint32_t upt = (uint32_t)(K / (64 * ST_WARPS));    // units of this warp per full tile
         const bool full_tile = unit < (uint32_t)ntf * upt;
         const int tile = full_tile ? (int)(unit / upt) : ntf;
-        const int uit = full_tile ? (int)(unit % upt) : (int)(unit - (uint32_t)ntf * upt);
         int trow, col;
-        unit_word_pos(full_tile, uit, warp * kw, wd, trow, col);
+        if (full_tile) unit_word_pos(true, (int)(unit % upt), warp * (K / ST_WARPS), wd, trow, col);
+        else unit_word_pos(false, 0, (warp + (int)(unit - (uint32_t)ntf * upt) * ST_WARPS) * 128, wd, trow, col);   // half-tile unit warp + k W
         const bf16* W;
         int row;
         if (phase == 0) {
@@ -1055,7 +1083,7 @@ __global__ void k_pack_lm(const StPlan* plans, const bf16* lm_head, uint8_t* pac
     const int warp = blockIdx.y;
     size_t woff = 0;
     for (int v = 0; v < warp; ++v) woff += (size_t)st_step_units(pl, v, num_layers) * ST_UNIT;
-    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + woff + (size_t)num_layers * pl.layer_units * ST_UNIT);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(packed + pl.stream_off + woff + (size_t)num_layers * st_layer_units(pl, warp) * ST_UNIT);
     const uint32_t nwords = st_lm_tiles(pl, warp) * ST_LM_TILE_UNITS * (ST_UNIT / 4);
     for (uint32_t wi = blockIdx.z * blockDim.x + threadIdx.x; wi < nwords; wi += gridDim.z * blockDim.x) {
         const uint32_t unit = wi / (ST_UNIT / 4), wd = wi % (ST_UNIT / 4);
@@ -1121,8 +1149,8 @@ static int st_make_plans(int grid, int num_layers, int vocab, std::vector<StPlan
         p.gu_row0 = 8 * gu_next; p.gu_np = pairs[c]; gu_next += pairs[c];
         p.lm_nt = lm_tiles / grid + (c < lm_tiles % grid ? 1 : 0);
         p.lm_row0 = 16 * lm_next; lm_next += p.lm_nt;
-        if (p.a_ng > 2 * ST_MAX_TILES || p.od_ng > 2) return MQ_ERR_UNSUPPORTED;
-        p.layer_units = st_layer_units(p);
+        if (p.a_ng > 2 * ST_MAX_TILES || p.od_ng > 1) return MQ_ERR_UNSUPPORTED;   // Wo / Wd rows: one 8-row group per CTA at most
+        p.layer_units = 0;
         p.stream_off = off;
         for (int wv = 0; wv < ST_WARPS; ++wv) off += (size_t)st_step_units(p, wv, num_layers) * ST_UNIT;
     }
