@@ -317,6 +317,14 @@ int mq_prefill_launch_count(int num_layers);
 int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* C, const void* R,
                         int M, int N, int K, int ldc, unsigned int* status, void* stream);
 
+/* Test hook for the error path that every bounded device wait shares: the same GEMM (no residual),
+ * but the TMA producer never requests k-block drop_kb (0 <= drop_kb < K / 64), so one wait of every
+ * CTA runs out after about 0.2 s.  The kernel must then return, set MQ_STATUS_WAIT_TIMEOUT in
+ * *status, store nothing to C, drain the copies and MMAs it has in flight, free its tensor memory,
+ * and leave the device usable (clear *status before the next call).  No production path uses it. */
+int mq_debug_gemm_drop_load(const void* A, int lda, const void* B, void* C, int M, int N, int K, int ldc,
+                            unsigned int* status, void* stream, int drop_kb);
+
 /* Standalone bf16 ops with the rounding points of the fused kernels.  They
  * replace the reference's csrc/kernels launchers (declared in
  * csrc/kernels/__init__.py:40-95): launch_rms_norm (rms_norm.cu:60-170),

@@ -107,18 +107,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait (about 0.2 s of SM clock).  On expiry the sticky status bit is
 // set and the caller carries on with whatever the buffer holds: the kernel
 // finishes, the host sees the bit at its next status check, and the GPU stays
-// usable.  Once the bit is set every later wait gives up at once, so a broken
-// chain drains in microseconds instead of one timeout per wait.  Returns false
-// if the wait was abandoned.
+// usable.  Once the bit is set every later wait gives up after a few dozen
+// polls, so a broken chain drains quickly instead of paying one timeout per
+// wait.  Returns false if the wait was abandoned.
 constexpr long long WAIT_LIMIT_CYCLES = 400000000LL;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (status && (__ldcg(status) & MQ_STATUS_WAIT_TIMEOUT)) return false;
+    // The sticky word lives in global memory (an L2 round trip): it is looked at every 64 polls, not
+    // before the first one, where it would sit in front of every wait that is not
+    // already satisfied (a producer waiting for a free stage, the first tiles of a pipeline).
     const long long t0 = clock64();
+    int polls = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            if (status) atomicOr(status, MQ_STATUS_WAIT_TIMEOUT);
-            return false;
+        if ((++polls & 63) == 0) {
+            if (status && (__ldcg(status) & MQ_STATUS_WAIT_TIMEOUT)) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                if (status) atomicOr(status, MQ_STATUS_WAIT_TIMEOUT);
+                return false;
+            }
         }
     }
     return true;

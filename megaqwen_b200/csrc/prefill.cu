@@ -102,6 +102,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
     return d;
 }
 
+// Bounded wait that does not look at the sticky status word: used while a CTA drains after one of its
+// waits has expired (copies already issued must land, MMAs already issued must finish, before the CTA
+// hands back its shared and tensor memory).  About 1 ms.
+__device__ __forceinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity))
+        if (clock64() - t0 > 2000000LL) return false;
+    return true;
+}
+
 // ---------------------------------------------------------------- GEMM  C[M,N] = A[M,K] * B[N,K]^T
 constexpr int GM_BM = 128;
 constexpr int GM_BK = 64;
@@ -159,7 +169,9 @@ template <int BN, int EPI, int MT>
 __global__ void __launch_bounds__(GM_TILE_THREADS, MQ_GEMM_MIN_CTAS)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
-       bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status) {
+       bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status, int drop_kb) {
+    // drop_kb >= 0 (test hook): the producer never requests k-block drop_kb, so the MMA thread's wait for it
+    // runs out; -1 in every production launch.
     pdl_trigger();   // the next grid may be scheduled already; it waits for this one below, after its own set-up
     // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
     // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
@@ -171,6 +183,9 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     uint64_t* empty = full + Cfg::STAGES;
     uint64_t* accum = empty + Cfg::STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+    // Set by the thread whose bounded wait expired (the sticky status bit is then set as well).  Everybody
+    // stops issuing work; the epilogue stores nothing; the CTA drains what is in flight before it exits.
+    volatile uint32_t* aborted = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * GM_BM * MT, n0 = blockIdx.x * BN;
@@ -190,6 +205,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         mbar_init(accum, 1);
         mbar_fence_init();
     }
+    if (tid == 64) *aborted = 0u;       // by a thread that is idle now (thread 0's set-up gates the first TMA request)
     if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
@@ -199,11 +215,15 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     // global memory has been touched yet.  From here on its results are complete and visible.
     pdl_wait();
 
+    int issued = 0;                       // k-blocks the producer has requested (thread 0 only)
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < nk; ++kb) {
                 const int s = kb % Cfg::STAGES;
-                if (kb >= Cfg::STAGES) mbar_wait(&empty[s], (uint32_t)((kb / Cfg::STAGES) - 1) & 1u, status);
+                if (kb >= Cfg::STAGES && !mbar_wait(&empty[s], (uint32_t)((kb / Cfg::STAGES) - 1) & 1u, status)) { *aborted = 1u; break; }
+                if (*aborted) break;
+                issued = kb + 1;
+                if (kb == drop_kb) continue;
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
                 mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
 #pragma unroll
@@ -225,7 +245,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
             for (int kb = 0; kb < nk; ++kb) {
                 const int s = kb % Cfg::STAGES;
-                mbar_wait(&full[s], (uint32_t)(kb / Cfg::STAGES) & 1u, status);
+                if (!mbar_wait(&full[s], (uint32_t)(kb / Cfg::STAGES) & 1u, status)) { *aborted = 1u; break; }
                 tc_fence_after();
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
                 const uint64_t db = smem_desc_sw128(st + Cfg::A_BYTES);
@@ -240,12 +260,13 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 }
                 umma_commit(&empty[s]);     // frees this stage once the MMAs above have read it
             }
-            umma_commit(accum);             // accumulator complete
+            umma_commit(accum);             // accumulator complete (or, after an expired wait, the MMAs issued so far)
+            if (*aborted) mbar_wait_drain(accum, 0);   // tensor memory is freed below: nothing may still be writing it
         }
         __syncwarp();
     } else {
         // epilogue: warp (2..9) owns TMEM lanes 32*(warp%4) .. +31 = tile rows and half of the columns
-        mbar_wait(accum, 0, status);
+        const bool acc_ok = mbar_wait(accum, 0, status) && !*aborted;   // after an expired wait nothing is read or stored
         tc_fence_after();
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         // the two warps of a quarter take one 128-row accumulator each (MT = 2) or half of the columns (MT = 1)
@@ -253,6 +274,7 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         const int cbeg = MT == 2 ? 0 : half * (BN / 2), cend = MT == 2 ? BN : cbeg + BN / 2;
 #pragma unroll 1
         for (int mt = (MT == 2 ? half : 0); mt < (MT == 2 ? half + 1 : 1); ++mt) {
+        if (!acc_ok) break;
         const int row = m0 + mt * GM_BM + quarter * 32 + lane;
         const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(mt * Cfg::NB * BN);
 #pragma unroll 1
@@ -305,6 +327,13 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         }
         tc_fence_before();
     }
+    // copies that were requested still land in this CTA's shared memory: after an expired wait the producer
+    // waits for the last one of every stage before the CTA may exit
+    if (tid == 0 && *aborted)
+        for (int s = 0; s < Cfg::STAGES && s < issued; ++s) {
+            const int last = ((issued - 1 - s) / Cfg::STAGES) * Cfg::STAGES + s;          // last requested k-block of stage s
+            if (last != drop_kb) mbar_wait_drain(&full[s], (uint32_t)(last / Cfg::STAGES) & 1u);
+        }
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
@@ -1180,7 +1209,8 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
 
 template <int BN, int EPI, int MT = 1>
 static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf16* C, const bf16* R, int M, int N, int K, int ldc,
-                       unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0, int ksplit = 1) {
+                       unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0, int ksplit = 1,
+                       int drop_kb = -1) {
     // rows0 > 0: B, B2, B3 hold rows0, rows1 and N - rows0 - rows1 output columns (concatenated along N)
     using Cfg = GemmCfg<BN, EPI, MT>;
     static bool attr_set[64] = {false};
@@ -1213,7 +1243,7 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
     if (ksplit < 1 || (ksplit > 1 && EPI != EPI_PARTIAL) || K / GM_BK < ksplit) return MQ_ERR_BAD_ARG;
     dim3 grid(N / BN, (M + GM_BM * MT - 1) / (GM_BM * MT), ksplit);
     launch_pdl(k_gemm<BN, EPI, MT>, dim3(grid), dim3(GM_TILE_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
-                                                             C, R, M, N, K, ldc, status);
+                                                             C, R, M, N, K, ldc, status, drop_kb);
     return (int)cudaGetLastError();
 }
 
@@ -1666,6 +1696,17 @@ extern "C" int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* 
     if (lda % 8 != 0 || ldc % 8 != 0) return MQ_ERR_ALIGNMENT;
     if (R) return launch_gemm<128, EPI_RESID>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, (const bf16*)R, M, N, K, ldc, status, (cudaStream_t)stream);
     return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream);
+}
+
+// Test hook: mq_launch_gemm_bf16 (no residual) whose producer never requests k-block drop_kb (0 <= drop_kb < K / 64),
+// so one bounded wait of every CTA runs out: the kernel must return, set MQ_STATUS_WAIT_TIMEOUT in *status, store
+// nothing, and leave the device usable.  Not used by any production path.
+extern "C" int mq_debug_gemm_drop_load(const void* A, int lda, const void* B, void* C, int M, int N, int K, int ldc,
+                                       unsigned int* status, void* stream, int drop_kb) {
+    if (!A || !B || !C || !status || M <= 0 || N <= 0 || K <= 0 || drop_kb < 0 || drop_kb >= K / GM_BK) return MQ_ERR_BAD_ARG;
+    if (lda % 8 != 0 || ldc % 8 != 0) return MQ_ERR_ALIGNMENT;
+    return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream,
+                                       nullptr, 0, 0, 1, drop_kb);
 }
 
 static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,

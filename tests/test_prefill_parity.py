@@ -39,6 +39,48 @@ def test_tcgen05_gemm_matches_torch(M, N, K, resid):
     assert float(d.max()) <= 2 ** -5 * max(1.0, float(ref.float().abs().max()))
 
 
+@pytest.mark.parametrize("drop_kb", [0, 9])
+def test_expired_wait_sets_status_and_leaves_the_device_usable(drop_kb):
+    """The error path every bounded device wait shares, made to run out on the host's terms: the GEMM's
+    TMA producer is told never to request one k-block (a wait for something nothing will ever deliver).
+    The kernel must come back by itself (about 0.2 s), report MQ_STATUS_WAIT_TIMEOUT, store nothing, and
+    the same GEMM must be correct right afterwards once the sticky word is cleared."""
+    import time
+    from megaqwen_b200 import _lib
+    lib = _lib.lib()
+    M, N, K = 300, 512, 1024                      # 3 x 4 tiles, 16 k-blocks: drop_kb 9 lies beyond the 6-stage ring's first lap
+    g = torch.Generator(device="cpu").manual_seed(5)
+    a = (torch.randn((M, K), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    b = (torch.randn((N, K), generator=g) * 0.05).to(torch.bfloat16).cuda()
+    c = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rc = lib.mq_debug_gemm_drop_load(a.data_ptr(), K, b.data_ptr(), c.data_ptr(), M, N, K, N, status.data_ptr(), stream, drop_kb)
+    assert rc == 0
+    torch.cuda.synchronize()                      # the kernel returned: no hang, no fault
+    assert time.perf_counter() - t0 < 5.0
+    assert int(status.item()) & _lib.MQ_STATUS_WAIT_TIMEOUT
+    assert bool((c == 7.0).all())                 # nothing was stored from half-finished accumulators
+    # bad arguments are refused on the host
+    assert lib.mq_debug_gemm_drop_load(a.data_ptr(), K, b.data_ptr(), c.data_ptr(), M, N, K, N, status.data_ptr(), stream, K // 64) != 0
+    # a second launch while the sticky bit is still set gives up at once and still stores nothing
+    rc = lib.mq_launch_gemm_bf16(a.data_ptr(), K, b.data_ptr(), c.data_ptr(), None, M, N, K, N, status.data_ptr(), stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert bool((c == 7.0).all())
+    # cleared: the device, the tensor memory and the barriers are as good as new
+    status.zero_()
+    rc = lib.mq_launch_gemm_bf16(a.data_ptr(), K, b.data_ptr(), c.data_ptr(), None, M, N, K, N, status.data_ptr(), stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = (a.float() @ b.float().t()).to(torch.bfloat16)
+    d = (c.float() - ref.float()).abs()
+    assert float((d > 0).float().mean()) < 2e-2 and float(d.max()) <= 2 ** -5 * max(1.0, float(ref.float().abs().max()))
+
+
 @pytest.fixture(scope="module")
 def tiny():
     return make_decoder(QWEN3_TINY, 2304)
