@@ -1381,21 +1381,27 @@ __device__ __forceinline__ void bd_expand_tile_fp8(const uint8_t* raw, bf16* til
 // decode attention with KV_FP8, csrc/megakernel/split_decode_gemm.cu:950-1310).  The row of
 // the new position was written to the bf16 cache by the preceding kernel; this CTA quantises
 // it into the shadow cache first (split_decode_gemm.cu:487-493).
-// nparts > 1: the key tiles of an item are split over nparts CTAs (blockIdx.z); each writes its
-// (m, l, acc) to `parts` and takes a ticket, and the CTA that takes the last one merges them (no CTA
-// waits for another).  tickets: one zero-initialised counter per (sequence, kv head), reset by the merger.
+// One-dimensional grid: CTAs 0 .. n_full - 1 take one (sequence, kv head) item each; the remaining items
+// are split over p_tail CTAs each (CTA n_full + r: item n_full + r / p_tail, part r % p_tail).  The CTAs
+// of a split item write their (m, l, acc) to `parts` and take a ticket, and the one that takes the last
+// merges them (no CTA waits for another).  tickets: one zero-initialised counter per item, reset by the merger.
 template <bool FP8, int WARPS>
 __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                                   bf16* __restrict__ out, const int* __restrict__ positions, int layer, int max_seq,
                                                   size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
                                                   const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride,
-                                                  float* __restrict__ parts, unsigned int* __restrict__ tickets) {
+                                                  float* __restrict__ parts, unsigned int* __restrict__ tickets, int n_full, int p_tail) {
     constexpr int BD_THREADS = WARPS * 32;
+    const int cta = (int)blockIdx.x;
+    const int item_i = cta < n_full ? cta : n_full + (cta - n_full) / p_tail;
+    const int part = cta < n_full ? 0 : (cta - n_full) % p_tail;
+    const int nparts = cta < n_full ? 1 : p_tail;
+    const int b = item_i / NKV, g = item_i % NKV;
     // the scales are set by the quantise kernel before the first step and constant afterwards
     float ks = 1.f, vs = 1.f;
     if constexpr (FP8) {
-        ks = kv_fp8_scale_guard(k_scale[(size_t)blockIdx.x * scale_stride + layer * NKV + blockIdx.y]);
-        vs = kv_fp8_scale_guard(v_scale[(size_t)blockIdx.x * scale_stride + layer * NKV + blockIdx.y]);
+        ks = kv_fp8_scale_guard(k_scale[(size_t)b * scale_stride + layer * NKV + g]);
+        vs = kv_fp8_scale_guard(v_scale[(size_t)b * scale_stride + layer * NKV + g]);
     }
     pdl_trigger();   // the next grid may be scheduled already (it waits the same way)
     pdl_wait();      // launched with programmatic stream serialisation: the preceding grid has completed
@@ -1404,12 +1410,10 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     bf16* qs = ring + (size_t)(BD_THREADS / 32) * BD_STAGES * BD_STAGE_ELEMS;         // [2][D]
     bf16* ps = qs + 2 * D;                                                            // [12 warps][2][16]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b = blockIdx.x, g = blockIdx.y;
     const int pos = min(max(positions[b], 0), max_seq - 1);
     const int len = pos + 1;
     const int ntiles_all = (len + 15) >> 4;
     // this CTA's share of the item's key tiles: [tile_lo, ntiles)
-    const int nparts = (int)gridDim.z, part = (int)blockIdx.z;
     const int tile_lo = (int)(((long long)part * ntiles_all) / nparts);
     const int ntiles = (int)(((long long)(part + 1) * ntiles_all) / nparts);
     const bool has_new = part == nparts - 1;                 // the part that holds the new position's tile
@@ -1637,9 +1641,9 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 6 ? 2 : 1)
 k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
                const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
                const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride, float* __restrict__ parts,
-               unsigned int* __restrict__ tickets) {
+               unsigned int* __restrict__ tickets, int n_full, int p_tail) {
     bd_attention_body<FP8, WARPS>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, k8, v8, k_scale, v_scale, scale_stride, parts,
-                                  tickets);
+                                  tickets, n_full, p_tail);
 }
 
 // out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
@@ -1905,17 +1909,25 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
 // kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
 extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
 
-// How a batched attention launch is shaped for `items` = 8 x batch (sequence, kv head) pairs: six-warp
-// CTAs (two per SM) while everything fits one round, with the keys of an item split over up to four
-// CTAs when there are few items; twelve-warp CTAs (one per SM), one per item, beyond.  (Splitting the
-// keys there as well, 7 rounds of half items instead of 4 of whole ones at batch 64, was measured
-// slower: 3.02 vs 2.68 ms per step, each CTA pays about 4 us to fill its rings and merge its warps.)
-// Depends on the batch size only, so a captured graph stays valid.
-struct BdShape { int warps, nparts; };
+// How a batched attention launch is shaped for `items` = 8 x batch (sequence, kv head) pairs.  Up to
+// 2 x SMs items: six-warp CTAs (two per SM), one round, the keys of every item split over up to four
+// CTAs when there are few items.  Beyond: twelve-warp CTAs (one per SM); the items of the full rounds
+// get one CTA each and those of the last, partly empty round are split so that they fill it (512
+// items on 148 SMs: 444 whole, 68 in two halves, 3.5 instead of 4 rounds).  Splitting ALL items there
+// (7 rounds of halves) was measured slower, 3.02 vs 2.68 ms per step: every CTA pays about 4 us to
+// fill its rings and merge its warps.  Depends on the batch size only, so a captured graph stays valid.
+struct BdShape { int warps, n_full, p_tail; };
 static BdShape bd_shape(int items, int sms, bool can_split) {
-    if (items > 2 * sms) return {12, 1};
-    const int p = can_split ? (2 * sms) / items : 1;
-    return {6, p < 1 ? 1 : (p > BD_MAX_PARTS ? BD_MAX_PARTS : p)};
+    if (items <= 2 * sms) {
+        int p = can_split ? (2 * sms) / items : 1;
+        p = p < 1 ? 1 : (p > BD_MAX_PARTS ? BD_MAX_PARTS : p);
+        return p == 1 ? BdShape{6, items, 1} : BdShape{6, 0, p};
+    }
+    const int rem = items % sms;
+    if (!can_split || rem == 0) return {12, items, 1};
+    int p = sms / rem;                                           // parts that still fit the last round
+    p = p > BD_MAX_PARTS ? BD_MAX_PARTS : p;
+    return p < 2 ? BdShape{12, items, 1} : BdShape{12, items - rem, p};
 }
 
 template <bool FP8, int WARPS>
@@ -1933,21 +1945,22 @@ static int bd_set_smem() {
 
 // attention of one layer of a batched decode step, from the bf16 caches or from the e4m3 shadow caches
 template <bool FP8, int WARPS>
-static void launch_bd_attention_t(int B, int nparts, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn,
+static void launch_bd_attention_t(int B, BdShape sh, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn,
                                   int l, const MqModel* model, size_t seq_stride) {
-    launch_pdl(k_bd_attention<FP8, WARPS>, dim3(B, NKV, nparts), dim3(WARPS * 32), bd_smem_bytes(WARPS), stream, qkv, (const bf16*)bb->k_cache,
+    const int ctas = sh.n_full + (B * NKV - sh.n_full) * sh.p_tail;
+    launch_pdl(k_bd_attention<FP8, WARPS>, dim3(ctas), dim3(WARPS * 32), bd_smem_bytes(WARPS), stream, qkv, (const bf16*)bb->k_cache,
                (const bf16*)bb->v_cache, attn, (const int*)bb->positions, l, model->max_seq_len, seq_stride,
                (uint8_t*)(kv8 ? kv8->k_fp8 : nullptr), (uint8_t*)(kv8 ? kv8->v_fp8 : nullptr), (const float*)(kv8 ? kv8->k_scale : nullptr),
-               (const float*)(kv8 ? kv8->v_scale : nullptr), model->num_layers * NKV, bb->attn_parts, bb->attn_tickets);
+               (const float*)(kv8 ? kv8->v_scale : nullptr), model->num_layers * NKV, bb->attn_parts, bb->attn_tickets, sh.n_full, sh.p_tail);
 }
 static void launch_bd_attention(int B, BdShape sh, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn, int l,
                                 const MqModel* model, size_t seq_stride) {
     if (kv8) {
-        if (sh.warps == 6) launch_bd_attention_t<true, 6>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
-        else launch_bd_attention_t<true, 12>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        if (sh.warps == 6) launch_bd_attention_t<true, 6>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        else launch_bd_attention_t<true, 12>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
     } else {
-        if (sh.warps == 6) launch_bd_attention_t<false, 6>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
-        else launch_bd_attention_t<false, 12>(B, sh.nparts, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        if (sh.warps == 6) launch_bd_attention_t<false, 6>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        else launch_bd_attention_t<false, 12>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
     }
 }
 
