@@ -1775,7 +1775,9 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
     // 64-wide tiles re-read the A operand sixteen times and are bound by L2 traffic.  The fp32 planes land in
     // the qkv buffer (free after attention; 2 x S x 1024 floats fill it exactly) and one kernel adds them to the
     // residual stream and applies the RMSNorm that follows (the next layer's input norm after the down projection).
-    const bool splitk = S >= 512 && S <= 1024;
+    // Above 1024 and up to 2048 rows the same with 128 x 256 tiles (N = 256 instructions, half the A traffic per FLOP).
+    const bool splitk = S >= 512 && S <= 2048 && (size_t)pb->max_tokens * QKV * sizeof(bf16) >= (size_t)2 * S * H * sizeof(float);
+    const bool wide = splitk && S > 1024;
     float* part = reinterpret_cast<float*>(qkv);
     for (int l = 0; l < model->num_layers; ++l) {
         const MqLayerWeights& w = model->layers[l];
@@ -1805,8 +1807,10 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
         }
         // N = 1024: with M <= 1024 a 128-wide tile gives at most 64 CTAs, 64-wide tiles double that
         if (splitk) {
-            rc = launch_gemm<128, EPI_PARTIAL>(attn, QSZ, (const bf16*)w.o_proj, nullptr, (bf16*)part, nullptr, S, H, QSZ, H, status, stream,
-                                               nullptr, 0, 0, 2);
+            rc = wide ? launch_gemm<256, EPI_PARTIAL>(attn, QSZ, (const bf16*)w.o_proj, nullptr, (bf16*)part, nullptr, S, H, QSZ, H, status, stream,
+                                                      nullptr, 0, 0, 2)
+                      : launch_gemm<128, EPI_PARTIAL>(attn, QSZ, (const bf16*)w.o_proj, nullptr, (bf16*)part, nullptr, S, H, QSZ, H, status, stream,
+                                                      nullptr, 0, 0, 2);
             if (rc) return rc;
             launch_pdl(k_sk_resid_norm, dim3(S), dim3(256), 0, stream, (const float*)part, 2, S, h, (const bf16*)w.post_attn_layernorm, x);
         } else {
@@ -1820,8 +1824,10 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
                  : launch_gemm<128, EPI_SWIGLU>(x, H, (const bf16*)w.gate_proj, (const bf16*)w.up_proj, act, nullptr, S, I, H, I, status, stream);
         if (rc) return rc;
         if (splitk) {
-            rc = launch_gemm<128, EPI_PARTIAL>(act, I, (const bf16*)w.down_proj, nullptr, (bf16*)part, nullptr, S, H, I, H, status, stream,
-                                               nullptr, 0, 0, 2);
+            rc = wide ? launch_gemm<256, EPI_PARTIAL>(act, I, (const bf16*)w.down_proj, nullptr, (bf16*)part, nullptr, S, H, I, H, status, stream,
+                                                      nullptr, 0, 0, 2)
+                      : launch_gemm<128, EPI_PARTIAL>(act, I, (const bf16*)w.down_proj, nullptr, (bf16*)part, nullptr, S, H, I, H, status, stream,
+                                                      nullptr, 0, 0, 2);
             if (rc) return rc;
             const bf16* next_norm = l + 1 < model->num_layers ? (const bf16*)model->layers[l + 1].input_layernorm : nullptr;
             launch_pdl(k_sk_resid_norm, dim3(S), dim3(256), 0, stream, (const float*)part, 2, S, h, next_norm, x);
