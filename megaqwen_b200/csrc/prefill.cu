@@ -1784,10 +1784,10 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
         if (l == 0 || !splitk)
             launch_pdl(k_pf_rmsnorm, dim3((S + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.input_layernorm, x, S);
         // q | k | v in one launch: 32 column tiles from three weight matrices
-        // from 1024 rows on, 256-row tiles (two accumulators per CTA) still give 96-128 CTAs
+        // from 1024 rows on: 128 x 256 tiles (one N = 256 instruction per k-step), 256 x 256 from 2048 rows; 128 CTAs either way
         rc = S >= 2048 ? launch_gemm<256, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                                         (const bf16*)w.v_proj, QSZ, KVSZ)
-           : big ? launch_gemm<128, EPI_STORE, 2>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
+           : big ? launch_gemm<256, EPI_STORE, 1>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                                   (const bf16*)w.v_proj, QSZ, KVSZ)
                  : launch_gemm<128, EPI_STORE>(x, H, (const bf16*)w.q_proj, (const bf16*)w.k_proj, qkv, nullptr, S, QKV, H, QKV, status, stream,
                                                (const bf16*)w.v_proj, QSZ, KVSZ);
