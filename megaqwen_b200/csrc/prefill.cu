@@ -327,14 +327,17 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
         }
         tc_fence_before();
     }
-    // copies that were requested still land in this CTA's shared memory: after an expired wait the producer
-    // waits for the last one of every stage before the CTA may exit
-    if (tid == 0 && *aborted)
-        for (int s = 0; s < Cfg::STAGES && s < issued; ++s) {
-            const int last = ((issued - 1 - s) / Cfg::STAGES) * Cfg::STAGES + s;          // last requested k-block of stage s
-            if (last != drop_kb) mbar_wait_drain(&full[s], (uint32_t)(last / Cfg::STAGES) & 1u);
-        }
     __syncthreads();
+    if (*aborted) {
+        // After an expired wait (anybody's: the flag is read behind the barrier): copies that were requested still
+        // land in this CTA's shared memory, so the producer waits for the last one of every stage before the CTA exits.
+        if (tid == 0)
+            for (int s = 0; s < Cfg::STAGES && s < issued; ++s) {
+                const int last = ((issued - 1 - s) / Cfg::STAGES) * Cfg::STAGES + s;      // last requested k-block of stage s
+                if (last != drop_kb) mbar_wait_drain(&full[s], (uint32_t)(last / Cfg::STAGES) & 1u);
+            }
+        __syncthreads();
+    }
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
