@@ -169,9 +169,10 @@ template <int BN, int EPI, int MT>
 __global__ void __launch_bounds__(GM_TILE_THREADS, MQ_GEMM_MIN_CTAS)
 k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
        const __grid_constant__ CUtensorMap tmB3, int tiles0, int tiles1,
-       bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status, int drop_kb) {
+       bf16* __restrict__ C, const bf16* R, int M, int N, int K, int ldc, unsigned int* status, int drop_kb, int early_b) {
     // drop_kb >= 0 (test hook): the producer never requests k-block drop_kb, so the MMA thread's wait for it
-    // runs out; -1 in every production launch.
+    // runs out; -1 in every production launch.  early_b: B is constant over the stream's lifetime (a weight),
+    // so its first tiles may be requested before the preceding grid has finished.
     pdl_trigger();   // the next grid may be scheduled already; it waits for this one below, after its own set-up
     // EPI_STORE / EPI_RESID may concatenate up to three B matrices along N (q|k|v): column tile
     // blockIdx.x < tiles0 reads tmB, < tiles0 + tiles1 tmB2, else tmB3.  EPI_SWIGLU uses tmB (gate)
@@ -211,11 +212,23 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-    // Barriers and tensor memory are set up while the preceding grid may still be running; nothing of
-    // global memory has been touched yet.  From here on its results are complete and visible.
+    // Barriers and tensor memory are set up while the preceding grid may still be running.  Where the B operand is
+    // a weight matrix that nothing on the stream writes, its tiles for the first ring of stages are requested now
+    // and cross HBM while that grid finishes; the A tiles (its output) follow the wait, from which on its results
+    // are complete and visible.
+    const int npre = !early_b ? 0 : nk < Cfg::STAGES ? nk : Cfg::STAGES;
+    if (tid == 0) {
+        for (int kb = 0; kb < npre; ++kb) {
+            if (kb == drop_kb) continue;
+            uint8_t* st = smem + (size_t)kb * Cfg::STAGE_BYTES;
+            mbar_expect_tx(&full[kb], (uint32_t)Cfg::STAGE_BYTES);
+            tma_load_2d(st + Cfg::A_BYTES, mapB, (kb_first + kb) * GM_BK, brow0, &full[kb]);
+            if (EPI == EPI_SWIGLU) tma_load_2d(st + Cfg::A_BYTES + BN * GM_BK * 2, &tmB2, (kb_first + kb) * GM_BK, n0, &full[kb]);
+        }
+    }
     pdl_wait();
 
-    int issued = 0;                       // k-blocks the producer has requested (thread 0 only)
+    int issued = npre;                    // k-blocks the producer has requested, B tiles at least (thread 0 only)
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = 0; kb < nk; ++kb) {
@@ -225,11 +238,13 @@ k_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensor
                 issued = kb + 1;
                 if (kb == drop_kb) continue;
                 uint8_t* st = smem + (size_t)s * Cfg::STAGE_BYTES;
-                mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
+                if (kb >= npre) mbar_expect_tx(&full[s], (uint32_t)Cfg::STAGE_BYTES);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) tma_load_2d(st + mt * GM_BM * GM_BK * 2, &tmA, (kb_first + kb) * GM_BK, m0 + mt * GM_BM, &full[s]);
-                tma_load_2d(st + Cfg::A_BYTES, mapB, (kb_first + kb) * GM_BK, brow0, &full[s]);
-                if (EPI == EPI_SWIGLU) tma_load_2d(st + Cfg::A_BYTES + BN * GM_BK * 2, &tmB2, (kb_first + kb) * GM_BK, n0, &full[s]);
+                if (kb >= npre) {
+                    tma_load_2d(st + Cfg::A_BYTES, mapB, (kb_first + kb) * GM_BK, brow0, &full[s]);
+                    if (EPI == EPI_SWIGLU) tma_load_2d(st + Cfg::A_BYTES + BN * GM_BK * 2, &tmB2, (kb_first + kb) * GM_BK, n0, &full[s]);
+                }
             }
         }
         __syncwarp();
@@ -1213,7 +1228,8 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
 template <int BN, int EPI, int MT = 1>
 static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf16* C, const bf16* R, int M, int N, int K, int ldc,
                        unsigned int* status, cudaStream_t stream, const bf16* B3 = nullptr, int rows0 = 0, int rows1 = 0, int ksplit = 1,
-                       int drop_kb = -1) {
+                       int drop_kb = -1, bool early_b = true) {
+    // early_b: B (B2, B3) are weights, never written by work on this stream; false for caller-supplied operands
     // rows0 > 0: B, B2, B3 hold rows0, rows1 and N - rows0 - rows1 output columns (concatenated along N)
     using Cfg = GemmCfg<BN, EPI, MT>;
     static bool attr_set[64] = {false};
@@ -1246,7 +1262,7 @@ static int launch_gemm(const bf16* A, int lda, const bf16* B, const bf16* B2, bf
     if (ksplit < 1 || (ksplit > 1 && EPI != EPI_PARTIAL) || K / GM_BK < ksplit) return MQ_ERR_BAD_ARG;
     dim3 grid(N / BN, (M + GM_BM * MT - 1) / (GM_BM * MT), ksplit);
     launch_pdl(k_gemm<BN, EPI, MT>, dim3(grid), dim3(GM_TILE_THREADS), Cfg::SMEM, stream, ma, mb, mb2, mb3, concat ? rows0 / BN : (1 << 30), concat ? rows1 / BN : 0,
-                                                             C, R, M, N, K, ldc, status, drop_kb);
+                                                             C, R, M, N, K, ldc, status, drop_kb, early_b ? 1 : 0);
     return (int)cudaGetLastError();
 }
 
@@ -1701,8 +1717,10 @@ extern "C" int mq_launch_gemm_bf16(const void* A, int lda, const void* B, void* 
                                    unsigned int* status, void* stream) {
     if (!A || !B || !C || !status || M <= 0 || N <= 0 || K <= 0) return MQ_ERR_BAD_ARG;
     if (lda % 8 != 0 || ldc % 8 != 0) return MQ_ERR_ALIGNMENT;
-    if (R) return launch_gemm<128, EPI_RESID>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, (const bf16*)R, M, N, K, ldc, status, (cudaStream_t)stream);
-    return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream);
+    if (R) return launch_gemm<128, EPI_RESID>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, (const bf16*)R, M, N, K, ldc, status, (cudaStream_t)stream,
+                                              nullptr, 0, 0, 1, -1, false);
+    return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream,
+                                       nullptr, 0, 0, 1, -1, false);
 }
 
 // Test hook: mq_launch_gemm_bf16 (no residual) whose producer never requests k-block drop_kb (0 <= drop_kb < K / 64),
@@ -1713,7 +1731,7 @@ extern "C" int mq_debug_gemm_drop_load(const void* A, int lda, const void* B, vo
     if (!A || !B || !C || !status || M <= 0 || N <= 0 || K <= 0 || drop_kb < 0 || drop_kb >= K / GM_BK) return MQ_ERR_BAD_ARG;
     if (lda % 8 != 0 || ldc % 8 != 0) return MQ_ERR_ALIGNMENT;
     return launch_gemm<128, EPI_STORE>((const bf16*)A, lda, (const bf16*)B, nullptr, (bf16*)C, nullptr, M, N, K, ldc, status, (cudaStream_t)stream,
-                                       nullptr, 0, 0, 1, drop_kb);
+                                       nullptr, 0, 0, 1, drop_kb, false);
 }
 
 static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const MqPrefillBuffers* pb, const int* ids,
