@@ -31,6 +31,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -99,6 +105,19 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
     d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
     d |= 1ull << 46;                 // descriptor version (sm_100)
     d |= 2ull << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+// The same tile read as an MN-major operand: [rows = K index][64 elements of the M / N dimension], i.e. a
+// row-major [k][n] matrix used as B without transposing it.  A 128-byte row holds 64 consecutive n of one k;
+// eight k form a 1024-byte swizzle group (stride byte offset); the next 64 n start panel_bytes further on
+// (leading byte offset).  A K = 16 step advances the start address by two groups.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(const void* tile, uint32_t panel_bytes) {
+    uint64_t d = (uint64_t)((smem_u32(tile) >> 4) & 0x3fffu);
+    d |= (uint64_t)((panel_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
     return d;
 }
 
@@ -883,8 +902,10 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __re
 // on the 5th-generation tensor cores with their accumulators in tensor memory:
 //     S = Q K^T     A = Q tile [128 q x 128 d], B = K tile [128 keys x 128 d] straight from the KV cache
 //     O_j = P V     A = P tile [128 q x 128 keys] (bf16, written by the softmax warps),
-//                   B = V^T tile [128 d x 128 keys] from a transposed copy of the layer's V rows
-// (all operands K-major under the 128-byte swizzle, fetched by TMA).  Warp 0 feeds the K / V^T
+//                   B = V tile [128 keys x 128 d] straight from the KV cache, read as an MN-major operand
+//                   (the cache rows are contiguous along d, the product contracts over the keys)
+// (128-byte swizzle, fetched by TMA; the V map ends at the last key of the prompt, so the rows of the
+// last tile beyond it arrive as zeros whatever the cache holds there).  Warp 0 feeds the K / V
 // rings, warp 1 issues the MMAs, warps 2-9 hold HALF A QUERY ROW PER THREAD: they read the row's
 // scores from tensor memory (tcgen05.ld), keep the running max / sum and write the probabilities
 // rounded to bf16 as the next MMA's A operand; the output accumulates in tensor memory and is
@@ -895,14 +916,14 @@ constexpr int TA_BQ = 128, TA_BK = 128;
 constexpr int TA_THREADS = 320;                             // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 constexpr int TA_TILE_BYTES = 128 * 128 * 2;               // two 64-column halves of [128 rows x 128 bytes]
 constexpr int TA_HALF_BYTES = TA_TILE_BYTES / 2;
-constexpr size_t TA_SMEM = (size_t)7 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + TA_BQ * 8 /*row exchange*/;   // Q, 2 K, 2 V^T, 2 P
+constexpr size_t TA_SMEM = (size_t)7 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + TA_BQ * 8 /*row exchange*/;   // Q, 2 K, 2 V, 2 P
 static_assert(TA_SMEM <= 232448, "shared memory of one CTA");
 constexpr uint32_t TA_TMEM_COLS = 512;                      // S0 | S1 | O (128 columns each)
 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __global__ void __launch_bounds__(TA_THREADS, 1)
-k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmVt,
+k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   bf16* __restrict__ out, int S, int pos0, int layer, int max_seq, unsigned int* status) {
     pdl_trigger();
     pdl_wait();
@@ -962,8 +983,8 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tma_load_2d(sK + st * TA_TILE_BYTES + TA_HALF_BYTES, &tmK, 64, krow0 + j * TA_BK, &k_full[st]);
                 if (j >= 2 && !mbar_wait(&v_empty[st], (uint32_t)((j >> 1) - 1) & 1u, status)) break;
                 mbar_expect_tx(&v_full[st], TA_TILE_BYTES);
-                tma_load_2d(sV + st * TA_TILE_BYTES, &tmVt, j * TA_BK, g * D, &v_full[st]);
-                tma_load_2d(sV + st * TA_TILE_BYTES + TA_HALF_BYTES, &tmVt, j * TA_BK + 64, g * D, &v_full[st]);
+                tma_load_3d(sV + st * TA_TILE_BYTES, &tmV, 0, j * TA_BK, layer * NKV + g, &v_full[st]);
+                tma_load_3d(sV + st * TA_TILE_BYTES + TA_HALF_BYTES, &tmV, 64, j * TA_BK, layer * NKV + g, &v_full[st]);
             }
         }
         __syncwarp();
@@ -971,6 +992,7 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint32_t idesc_pv = idesc | (1u << 16);    // B (the V tile) is MN-major
             bool ok = mbar_wait(q_full, 0, status);
             auto issue_s = [&](int j) {      // S[j & 1] = Q K_j^T
                 const int st = j & 1;
@@ -999,8 +1021,9 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
                         const uint64_t da = smem_desc_sw128(sP + st * TA_TILE_BYTES + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
-                        const uint64_t db = smem_desc_sw128(sV + st * TA_TILE_BYTES + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
-                        umma_bf16(tmem_o, da, db, idesc, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates over all key tiles
+                        // 16 keys per step = two 1024-byte groups of the [keys][64 d] panels (d 0-63 | d 64-127)
+                        const uint64_t db = smem_desc_mn_sw128(sV + st * TA_TILE_BYTES, TA_HALF_BYTES) + (uint64_t)(kk * (2048 >> 4));
+                        umma_bf16(tmem_o, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates over all key tiles
                     }
                 }
                 umma_commit(&v_empty[st]);
@@ -1133,45 +1156,6 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (warp == 1) tmem_dealloc(tmem_base, TA_TMEM_COLS);
 }
 
-// vt[g][d][key] = v_cache[layer][g][key][d] for key < n_keys, zero up to key_pad (the B operand of
-// the P V product must be K-major, i.e. contiguous along the keys).  grid (key_pad / 32, 8), 128
-// threads: 32 keys x 128 dims per CTA, four independent 16-byte loads per thread, then thread d
-// writes the 64 contiguous bytes of its row.
-constexpr int TV_KEYS = 32;
-__global__ void __launch_bounds__(128) k_pf_transpose_v(const bf16* __restrict__ v_cache, bf16* __restrict__ vt, int layer, int max_seq,
-                                                        int n_keys, int key_pad) {
-    pdl_trigger();
-    pdl_wait();
-    __shared__ __align__(16) bf16 tile[TV_KEYS][D + 8];
-    const int g = blockIdx.y, key0 = blockIdx.x * TV_KEYS, tid = threadIdx.x;
-    const bf16* src = v_cache + ((size_t)(layer * NKV + g) * max_seq) * D;
-    uint4 v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int c = tid + 128 * i, k = c >> 4, c8 = (c & 15) * 8;          // chunk c: key k, dims c8 .. c8 + 7
-        v[i] = key0 + k < n_keys ? *reinterpret_cast<const uint4*>(src + (size_t)(key0 + k) * D + c8) : make_uint4(0u, 0u, 0u, 0u);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int c = tid + 128 * i, k = c >> 4, c8 = (c & 15) * 8;
-        *reinterpret_cast<uint4*>(&tile[k][c8]) = v[i];
-    }
-    __syncthreads();
-    const int d = tid;
-    bf16* dst = vt + ((size_t)(g * D + d)) * key_pad + key0;
-#pragma unroll
-    for (int q = 0; q < TV_KEYS / 8; ++q) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int k = 8 * q + 2 * e;
-            const uint16_t a = *reinterpret_cast<const uint16_t*>(&tile[k][d]), b = *reinterpret_cast<const uint16_t*>(&tile[k + 1][d]);
-            w[e] = (uint32_t)a | ((uint32_t)b << 16);
-        }
-        *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-}
-
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1179,7 +1163,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 struct MapKey {
     const void* ptr; uint64_t rows, cols, ld; uint32_t box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+    uint64_t planes, plane_ld;           // 0, 0 for a matrix
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && planes == o.planes && plane_ld == o.plane_ld;
+    }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
@@ -1187,6 +1174,7 @@ struct MapKeyHash {
         h ^= k.rows * 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
         h ^= k.cols * 0xc2b2ae3d27d4eb4full + (h << 6) + (h >> 2);
         h ^= (k.ld * 31 + k.box_rows) + (h << 6) + (h >> 2);
+        h ^= (k.planes * 0x9e3779b97f4a7c15ull + k.plane_ld) + (h << 6) + (h >> 2);
         return h;
     }
 };
@@ -1197,7 +1185,10 @@ static EncodeTiledFn g_encode = nullptr;
 // Tensor map of a row-major bf16 matrix [rows, cols] with leading dimension ld
 // (elements); box = 64 columns x box_rows rows, 128-byte swizzle, zero fill
 // outside the matrix.  Maps are cached: weight matrices never move.
-static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, CUtensorMap* out) {
+// planes > 0: a stack of `planes` such matrices, plane_ld elements apart (a third coordinate selects the plane,
+// and rows beyond `rows` of a plane are filled with zeros instead of running into the next plane).
+static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, CUtensorMap* out, uint64_t planes = 0,
+                   uint64_t plane_ld = 0) {
     std::lock_guard<std::mutex> lk(g_map_mu);
     if (!g_encode) {
         void* fn = nullptr;
@@ -1207,16 +1198,16 @@ static int get_map(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, u
         if (!fn || qres != cudaDriverEntryPointSuccess) return MQ_ERR_UNSUPPORTED;
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    const MapKey key{ptr, rows, cols, ld, box_rows};
+    const MapKey key{ptr, rows, cols, ld, box_rows, planes, plane_ld};
     auto it = g_maps.find(key);
     if (it != g_maps.end()) { *out = it->second; return MQ_OK; }
     if (g_maps.size() > 4096) g_maps.clear();
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {ld * 2};
-    const cuuint32_t box[2] = {GM_BK, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
+    const cuuint64_t dims[3] = {cols, rows, planes};
+    const cuuint64_t strides[2] = {ld * 2, plane_ld * 2};
+    const cuuint32_t box[3] = {GM_BK, box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
     CUtensorMap m;
-    const CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    const CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, planes > 0 ? 3 : 2, const_cast<void*>(ptr), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return MQ_ERR_BAD_ARG;
@@ -1709,7 +1700,7 @@ __global__ void __launch_bounds__(1024) k_bd_argmax_advance(const bf16* __restri
 using namespace mq;
 
 // kernels of one prefill (at most: the split-K path needs one norm kernel fewer per layer after the first)
-extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 9 + 2; }
+extern "C" int mq_prefill_launch_count(int num_layers) { return 1 + num_layers * 8 + 2; }
 
 // C[M,N] = A[M,K] * B[N,K]^T on the tcgen05 path (bf16 in/out, fp32 accumulate);
 // optional residual R (same shape and leading dimension as C, may alias C).
@@ -1771,11 +1762,11 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
         if (e != cudaSuccess) return (int)e;
         fa_attr[dev] = true;
     }
-    // From 128 prompt rows on the attention runs on tcgen05; it needs a transposed copy of the layer's V rows
-    // (8 x 128 x key_pad bf16), which lives in the MLP activation buffer until the gate/up GEMM overwrites it.
-    const int key_pad = (pos0 + S + TA_BK - 1) / TA_BK * TA_BK;
-    const bool use_tc = S >= TA_BQ && (size_t)key_pad * KVSZ <= (size_t)pb->max_tokens * I;
-    CUtensorMap map_q, map_k, map_vt;
+    // From 128 prompt rows on the attention runs on tcgen05, its K and V tiles straight from the cache.  The V map
+    // is a stack of (layer, kv head) planes that end at the prompt's last key: what the cache holds beyond it
+    // (possibly not even numbers) is multiplied by probabilities of zero and must read as zero.
+    const bool use_tc = S >= TA_BQ;
+    CUtensorMap map_q, map_k, map_v;
     if (use_tc) {
         static bool ta_attr[64] = {false};
         if (dev >= 0 && dev < 64 && !ta_attr[dev]) {
@@ -1785,7 +1776,9 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
         }
         int mrc = get_map(qkv, (uint64_t)S, (uint64_t)QKV, (uint64_t)QKV, TA_BQ, &map_q);
         if (mrc == MQ_OK) mrc = get_map(dbuf->k_cache, (uint64_t)model->num_layers * NKV * model->max_seq_len, (uint64_t)D, (uint64_t)D, TA_BK, &map_k);
-        if (mrc == MQ_OK) mrc = get_map(act, (uint64_t)KVSZ, (uint64_t)key_pad, (uint64_t)key_pad, D, &map_vt);
+        if (mrc == MQ_OK)
+            mrc = get_map(dbuf->v_cache, (uint64_t)(pos0 + S), (uint64_t)D, (uint64_t)D, TA_BK, &map_v, (uint64_t)model->num_layers * NKV,
+                          (uint64_t)model->max_seq_len * D);
         if (mrc != MQ_OK) return mrc;
     }
     launch_pdl(k_pf_embed, dim3(S), dim3(128), 0, stream, ids, (const bf16*)model->embed, h, model->vocab_size, status, audio,
@@ -1817,10 +1810,7 @@ static int prefill_impl(const MqModel* model, const MqDecodeBuffers* dbuf, const
                                                          (const bf16*)model->sin_table, (bf16*)dbuf->k_cache, (bf16*)dbuf->v_cache, l, pos0,
                                                          model->max_seq_len, nullptr, 0, nullptr, 0, 0, nullptr);
         if (use_tc) {
-            // V^T of this layer's keys goes into the (still unused) MLP activation buffer
-            launch_pdl(k_pf_transpose_v, dim3(key_pad / TV_KEYS, NKV), dim3(128), 0, stream, (const bf16*)dbuf->v_cache, act, l, model->max_seq_len,
-                       pos0 + S, key_pad);
-            launch_pdl(k_pf_attention_tc, dim3(NQ, (S + TA_BQ - 1) / TA_BQ), dim3(TA_THREADS), TA_SMEM, stream, map_q, map_k, map_vt, attn, S, pos0, l,
+            launch_pdl(k_pf_attention_tc, dim3(NQ, (S + TA_BQ - 1) / TA_BQ), dim3(TA_THREADS), TA_SMEM, stream, map_q, map_k, map_v, attn, S, pos0, l,
                        model->max_seq_len, status);
         } else {
             launch_pdl(k_pf_attention, dim3(dim3(NQ, (S + FA_BQ - 1) / FA_BQ)), dim3(FA_THREADS), fa_smem, stream, qkv, (const bf16*)dbuf->k_cache,

@@ -113,6 +113,24 @@ def test_tiny_prefill_matches_restatement(tiny, plen):
     assert r2["max"] <= 6e-2 and r2["mean"] <= 8e-3, (plen, r2)
 
 
+@pytest.mark.parametrize("plen", [300, 1000])
+def test_prefill_ignores_cache_rows_beyond_the_prompt(tiny, plen):
+    """The attention's last key tile reaches past the prompt; what the cache holds there (here: NaN in K and
+    V) belongs to nobody and must not reach the result: same logits, bit for bit, as over a zeroed cache."""
+    dec, _ = tiny
+    prompt = random_prompt(QWEN3_TINY, plen, 12, plen)
+    dec.reset()
+    _, clean = dec.prefill_step_logits(prompt)
+    clean = clean.clone()
+    dec.reset()
+    dec.get_k_cache()[:, :, plen:] = float("nan")
+    dec.get_v_cache()[:, :, plen:] = float("nan")
+    _, lg = dec.prefill_step_logits(prompt)
+    assert not bool(torch.isnan(lg).any())
+    assert torch.equal(lg, clean)
+    dec.reset()
+
+
 def test_tiny_prefill_matches_hf_golden_and_decode_only_path(tiny):
     dec, _ = tiny
     g = load_golden("tiny_p300_n24")
