@@ -1333,8 +1333,7 @@ namespace mq {
 constexpr int BD_STAGES = 2, BD_LD = D + 8;                                     // per warp: 2 stages x 8.5 KB
 constexpr int BD_STAGE_ELEMS = 2 * 16 * BD_LD;                                  // K tile then V tile
 // Two shapes: twelve warps, one CTA per SM (209 KB), or six warps, two CTAs per SM (105 KB each).  The
-// SM streams with twelve warps either way; the small shape doubles the CTA slots, so a batch of up to
-// 2 x SMs (sequence, kv head) items runs in ONE round instead of two half-empty ones.
+// SM streams with twelve warps either way; bd_shape() below says which is used when.
 constexpr size_t bd_smem_bytes(int warps) { return (size_t)warps * BD_STAGES * BD_STAGE_ELEMS * 2 + 2 * D * 2 + warps * 32 * 2; }
 constexpr int BD_MAX_PARTS = 4;                                                 // CTAs that may share one item's keys
 constexpr int BD_PART = D + 2;                                                  // m, l, acc[128] of one head of one part
@@ -1926,25 +1925,28 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
 // kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
 extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
 
-// How a batched attention launch is shaped for `items` = 8 x batch (sequence, kv head) pairs.  Up to
-// 2 x SMs items: six-warp CTAs (two per SM), one round, the keys of every item split over up to four
-// CTAs when there are few items.  Beyond: twelve-warp CTAs (one per SM); the items of the full rounds
-// get one CTA each and those of the last, partly empty round are split so that they fill it (512
-// items on 148 SMs: 444 whole, 68 in two halves, 3.5 instead of 4 rounds).  Splitting ALL items there
-// (7 rounds of halves) was measured slower, 3.02 vs 2.68 ms per step: every CTA pays about 4 us to
-// fill its rings and merge its warps.  Depends on the batch size only, so a captured graph stays valid.
+// How a batched attention launch is shaped for `items` = 8 x batch (sequence, kv head) pairs.  Up to one
+// item per SM: twelve-warp CTAs, the keys of every item split over up to four CTAs while those still fit one
+// round.  Beyond: six-warp CTAs, two per SM.  The SM streams with twelve warps either way, but two CTAs
+// per SM are at different points of their items, so one CTA's ring fill and warp merge (about 4 us per
+// item, during which a lone twelve-warp CTA leaves the SM's memory pipeline idle) overlap the other's
+// streaming: 2.68 -> 2.49 ms per step at batch 64 / context 1024, 2.12 -> 1.90 at context 500.  The items of
+// the full rounds get one CTA each and those of the last, partly empty round are split so that they
+// fill it (384 items on 296 slots: 296 whole, 88 in three parts).  Splitting ALL items was measured slower
+// (3.02 vs 2.68 ms per step with twelve-warp halves), four- and three-warp CTAs (three and four per SM)
+// too (2.58, 2.55).  Depends on the batch size only, so a captured graph stays valid.
 struct BdShape { int warps, n_full, p_tail; };
 static BdShape bd_shape(int items, int sms, bool can_split) {
-    if (items <= 2 * sms) {
-        int p = can_split ? (2 * sms) / items : 1;
-        p = p < 1 ? 1 : (p > BD_MAX_PARTS ? BD_MAX_PARTS : p);
-        return p == 1 ? BdShape{6, items, 1} : BdShape{6, 0, p};
+    if (items <= sms) {
+        int p = can_split ? sms / items : 1;
+        p = p > BD_MAX_PARTS ? BD_MAX_PARTS : p;
+        return p < 2 ? BdShape{12, items, 1} : BdShape{12, 0, p};
     }
-    const int rem = items % sms;
-    if (!can_split || rem == 0) return {12, items, 1};
-    int p = sms / rem;                                           // parts that still fit the last round
+    const int slots = 2 * sms, rem = items % slots;
+    if (!can_split || rem == 0) return {6, items, 1};
+    int p = slots / rem;                                         // parts that still fit the last round
     p = p > BD_MAX_PARTS ? BD_MAX_PARTS : p;
-    return p < 2 ? BdShape{12, items, 1} : BdShape{12, items - rem, p};
+    return p < 2 ? BdShape{6, items, 1} : BdShape{6, items - rem, p};
 }
 
 template <bool FP8, int WARPS>

@@ -47,7 +47,11 @@ def run_batch(bd, prompts, forced, steps):
 
 
 def check_against_batch1(dec, prompts, first, fed, logits, which, what):
-    """Sequence b of the batch against the batch-1 decoder fed the same tokens."""
+    """Sequence b of the batch against the batch-1 decoder fed the same tokens.
+
+    Both sides are bf16 implementations of the same arithmetic with different summation orders (packed
+    mma.sync prefill and split-K GEMMs here, tcgen05 prefill and GEMV kernels there), each within
+    8e-3 mean of the oracle; two such results differ from each other by up to sqrt(2) times that."""
     worst = {"max": 0.0, "mean": 0.0}
     for b in which:
         dec.reset()
@@ -59,7 +63,7 @@ def check_against_batch1(dec, prompts, first, fed, logits, which, what):
         for i in range(len(fed)):
             _, lg = dec.decode_step_logits(int(fed[i][b]))
             r = logit_report(logits[i, b], lg.cpu())
-            assert r["max"] <= 6e-2 and r["mean"] <= 8e-3, (what, b, i, r)
+            assert r["max"] <= 6.25e-2 and r["mean"] <= 1.13e-2, (what, b, i, r)
             worst = {k: max(worst[k], r[k]) for k in worst}
     return worst
 
