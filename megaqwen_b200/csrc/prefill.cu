@@ -402,9 +402,11 @@ k_gemm_skinny(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ 
     constexpr int TM_COLS = MPAD < 32 ? 32 : MPAD;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* xs = smem + SK_MAXKB * W_BYTES;                               // X tiles, each 1024-byte aligned
+    // the launch sizes the dynamic shared memory for kb_per_cta k-blocks (not the maximum), so that CTAs with short K
+    // slices fit two to an SM and a grid of up to 2 x SMs CTAs runs in one round
+    uint8_t* xs = smem + kb_per_cta * W_BYTES;                             // X tiles, each 1024-byte aligned
     constexpr int X_STRIDE = (X_BYTES + 1023) & ~1023;
-    uint64_t* full = reinterpret_cast<uint64_t*>(xs + SK_MAXKB * X_STRIDE);
+    uint64_t* full = reinterpret_cast<uint64_t*>(xs + kb_per_cta * X_STRIDE);
     uint64_t* accum = full + SK_MAXKB;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1264,11 +1266,14 @@ static int launch_skinny_t(const bf16* const* W, const int* rowsW, int nW, const
     constexpr int X_STRIDE = ((MPAD * GM_BK * 2) + 1023) & ~1023;
     const size_t smem = (size_t)SK_MAXKB * (128 * GM_BK * 2 + X_STRIDE) + 1024 + 256;
     static bool attr_set[64] = {false};
+    static int sms[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev < 0 || dev >= 64) return MQ_ERR_UNSUPPORTED;
+    if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_gemm_skinny<MPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
         attr_set[dev] = true;
     }
     const int kb = K / GM_BK;
@@ -1285,7 +1290,11 @@ static int launch_skinny_t(const bf16* const* W, const int* rowsW, int nW, const
     int rc = get_map(X, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, MPAD, &mx);
     if (rc != MQ_OK) return rc;
     dim3 grid(tiles[0] + tiles[1] + tiles[2], ksplit);
-    launch_pdl(k_gemm_skinny<MPAD>, dim3(grid), dim3(GM_THREADS), smem, stream, mw[0], mw[1], mw[2], tiles[0], tiles[1], mx, part, M, ldp, kb / ksplit, status);
+    // A grid of at most one CTA per SM asks for the full ring, so that no two of its CTAs share an SM; a larger
+    // one (gate|up: 48 tiles x 4 K slices = 192 CTAs) asks for what its k-blocks need and runs in one round.
+    const size_t smem_exact = (size_t)(kb / ksplit) * (128 * GM_BK * 2 + X_STRIDE) + 1024 + 256;
+    const size_t smem_used = (int)(grid.x * grid.y) > sms[dev] ? smem_exact : smem;
+    launch_pdl(k_gemm_skinny<MPAD>, dim3(grid), dim3(GM_THREADS), smem_used, stream, mw[0], mw[1], mw[2], tiles[0], tiles[1], mx, part, M, ldp, kb / ksplit, status);
     return (int)cudaGetLastError();
 }
 static int launch_skinny(const bf16* const* W, const int* rowsW, int nW, const bf16* X, int ldx, float* part, int M, int K, int ksplit,
