@@ -5,7 +5,7 @@ import torch
 
 from helpers import logit_report
 from megaqwen_b200.spec import QWEN3_TINY
-from megaqwen_b200.synthetic import random_prompt, random_weights
+from megaqwen_b200.synthetic import random_lengths, random_prompt, random_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -231,4 +231,32 @@ def test_small_batch_splits_keys_over_ctas():
         rep = logit_report(lg2[b].cpu(), r.forward([nxt[b]]))
         assert rep["max"] <= 6e-2 and rep["mean"] <= 8e-3, (b, rep)
     assert int(bd._attn_tickets.abs().sum()) == 0
+    bd.check_status()
+
+
+@pytest.mark.parametrize("B", [3, 20, 40])
+def test_decode_ignores_cache_rows_beyond_each_sequence(B):
+    """Cache rows past a sequence's position belong to nobody; with NaN there (K and V) a decode step must
+    give the logits it gives over a zeroed cache, bit for bit.  B = 3 splits the keys of an item over CTAs,
+    20 runs twelve-warp CTAs, 40 six-warp CTAs two to an SM."""
+    from megaqwen_b200.batch import MegakernelBatchDecoder
+    lens = random_lengths(B, 1, 300, seed=77 + B)
+    w = random_weights(QWEN3_TINY, 512)
+    lw = [t.cuda() for t in w["layer_weights"]]
+    e = w["embed_weight"].cuda()
+    bd = MegakernelBatchDecoder(e, lw, w["final_norm_weight"].cuda(), e, w["cos_table"].cuda(), w["sin_table"].cuda(),
+                                QWEN3_TINY.num_layers, 512, B)
+    prompts = [random_prompt(QWEN3_TINY, n, 9, i) for i, n in enumerate(lens)]
+    out = []
+    for poison in (False, True):
+        bd.reset()
+        first = bd.prefill_batch(prompts)
+        if poison:
+            for b, n in enumerate(lens):
+                bd.get_k_cache()[b, :, :, n + 1:] = float("nan")
+                bd.get_v_cache()[b, :, :, n + 1:] = float("nan")
+        _, lg = bd.decode_batch(first, return_logits=True)
+        out.append(lg.clone())
+    assert not bool(torch.isnan(out[1]).any())
+    assert torch.equal(out[0], out[1])
     bd.check_status()

@@ -133,6 +133,26 @@ def test_single_steps_chain_and_graph_agree(tiny):
     assert dec.position() == len(prompt) - 1 + 40
 
 
+@pytest.mark.parametrize("plen", [5, 200, 700])
+def test_decode_ignores_cache_rows_beyond_the_position(tiny, plen):
+    """NaN in the K and V rows past the current position (the tail of a split's last 16-position tile, and
+    everything behind it) must not reach the logits: bit-identical to the step over a zeroed cache."""
+    dec, _ = tiny
+    prompt = random_prompt(QWEN3_TINY, plen, 21, plen)
+    out = []
+    for poison in (False, True):
+        dec.reset()
+        tok = dec.prefill_step(prompt)
+        if poison:
+            dec.get_k_cache()[:, :, plen + 1:] = float("nan")
+            dec.get_v_cache()[:, :, plen + 1:] = float("nan")
+        _, lg = dec.decode_step_logits(int(tok))
+        out.append(lg.clone())
+    dec.reset()
+    assert not bool(torch.isnan(out[1]).any())
+    assert torch.equal(out[0], out[1])
+
+
 def test_long_context_split_kv(tiny):
     """Contexts that need several KV splits, against the restatement."""
     from oracle.qwen3_restatement import RestatedQwen3
