@@ -140,7 +140,10 @@ constexpr int GM_THREADS = 192;    // skinny GEMM: warp 0 TMA, warp 1 MMA + TMEM
 // epilogue of a 256 x 256 tile (65 536 silu + products on 128 threads) took as long as its main loop.
 constexpr int GM_EPI_WARPS = 8;
 constexpr int GM_TILE_THREADS = 64 + 32 * GM_EPI_WARPS;
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };   // PARTIAL: fp32 plane blockIdx.z of a K split
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_STORE_2CTA = 4 };   // PARTIAL: fp32 plane blockIdx.z of a K split
+// EPI_STORE_2CTA: EPI_STORE with a three-stage ring (97 KB), so that two CTAs share an SM.  For a GEMM of many short
+// CTAs that stream weights (the batched LM head: 1187 column tiles of a 64-row matrix), where a lone CTA's start-up and
+// epilogue leave the SM's memory pipeline idle.
 
 // Every kernel of the prefill and batched-decode chains is launched with programmatic
 // stream serialisation and begins with griddepcontrol.wait + launch_dependents: the next
@@ -174,7 +177,7 @@ struct GemmCfg {
     static constexpr int NB = (EPI == EPI_SWIGLU) ? 2 : 1;                       // B operands per stage
     static constexpr int A_BYTES = MT * GM_BM * GM_BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + NB * BN * GM_BK * 2;
-    static constexpr int STAGES = (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES > 6 ? 6 : (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = EPI == EPI_STORE_2CTA ? 3 : (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES > 6 ? 6 : (MQ_GEMM_BUDGET_KB * 1024) / STAGE_BYTES;
     static constexpr int ACC_COLS = MT * NB * BN;                                // accumulator columns in use
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;   // allocations are powers of two
     static_assert(ACC_COLS <= 512 && BN % 32 == 0, "tensor memory holds 512 columns; the epilogue reads 32 at a time");
@@ -1924,7 +1927,7 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
     // last row of every sequence -> final norm -> LM head -> arg-max (advances positions[b] to len_b)
     launch_pdl(k_pf_gather_last, dim3(B), dim3(H / 8), 0, stream, h, seq_row0, seq_len, attn);
     launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, attn, (const bf16*)model->final_norm, x, B);
-    rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
+    rc = launch_gemm<128, EPI_STORE_2CTA>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
                                      model->vocab_size, status, stream);
     if (rc) return rc;
     launch_pdl(k_bd_argmax_advance, dim3(B), dim3(1024), 0, stream, (const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, (float*)nullptr);
@@ -2082,7 +2085,7 @@ static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, con
     }
     launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)model->final_norm, x, B);
     }
-    rc = launch_gemm<128, EPI_STORE>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
+    rc = launch_gemm<128, EPI_STORE_2CTA>(x, H, (const bf16*)model->lm_head, nullptr, (bf16*)bb->logits, nullptr, B, model->vocab_size, H,
                                      model->vocab_size, status, stream);
     if (rc) return rc;
     launch_pdl(k_bd_argmax_advance, dim3(B), dim3(1024), 0, stream, (const bf16*)bb->logits, model->vocab_size, out_tokens, bb->positions, logits_f32);
