@@ -303,7 +303,7 @@ int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffers* bb, con
 int mq_launch_decode_batch_kv8(const MqModel* model, const MqBatchBuffers* bb, const MqKvFp8* kv8,
                                const int* in_tokens, int* out_tokens, float* logits_f32, void* stream);
 
-/* Kernels one step launches on the tile-GEMM path (batch > 64); at most one fewer per layer otherwise. */
+/* Kernels one step launches on the tile-GEMM path (batch > 64); two fewer per layer on the split-K path. */
 int mq_decode_batch_launch_count(int num_layers);
 
 /* Number of kernels one mq_launch_prefill call launches. */

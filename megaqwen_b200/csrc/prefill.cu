@@ -1402,16 +1402,26 @@ __device__ __forceinline__ void bd_expand_tile_fp8(const uint8_t* raw, bf16* til
 // decode attention with KV_FP8, csrc/megakernel/split_decode_gemm.cu:950-1310).  The row of
 // the new position was written to the bf16 cache by the preceding kernel; this CTA quantises
 // it into the shadow cache first (split_decode_gemm.cu:487-493).
+// qk.part != nullptr: the step's q|k|v rows are still the fp32 planes of the K-split projection; the CTA sums
+// its item's four heads itself (two query heads, and in the part that holds the new position the K and V
+// head), applies QK-norm + RoPE with the arithmetic of k_pf_qknorm_rope and writes the new K / V row into
+// the cache, so that kernel is not launched.
 // One-dimensional grid: CTAs 0 .. n_full - 1 take one (sequence, kv head) item each; the remaining items
 // are split over p_tail CTAs each (CTA n_full + r: item n_full + r / p_tail, part r % p_tail).  The CTAs
 // of a split item write their (m, l, acc) to `parts` and take a ticket, and the one that takes the last
 // merges them (no CTA waits for another).  tickets: one zero-initialised counter per item, reset by the merger.
+struct BdQkFuse {
+    const float* part;        // [ksplit][M][QKV] fp32 planes of the q|k|v projection, or nullptr
+    int ksplit, M;
+    const bf16* wq; const bf16* wk; const bf16* cos; const bf16* sin;
+};
 template <bool FP8, int WARPS>
 __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                                                   bf16* __restrict__ out, const int* __restrict__ positions, int layer, int max_seq,
                                                   size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
                                                   const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride,
-                                                  float* __restrict__ parts, unsigned int* __restrict__ tickets, int n_full, int p_tail) {
+                                                  float* __restrict__ parts, unsigned int* __restrict__ tickets, int n_full, int p_tail,
+                                                  const BdQkFuse& qk) {
     constexpr int BD_THREADS = WARPS * 32;
     const int cta = (int)blockIdx.x;
     const int item_i = cta < n_full ? cta : n_full + (cta - n_full) / p_tail;
@@ -1447,20 +1457,70 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
     const uint8_t* k8b = FP8 ? k8 + head_off : nullptr;
     const uint8_t* v8b = FP8 ? v8 + head_off : nullptr;
 
-    // The first tile of this warp is requested before anything else.  FP8: the tile that holds the
-    // new position is requested only after the block barrier below, which orders it after the
-    // quantised row written by threads 0..63.
+    // The first tile of this warp is requested before anything else.  The tile that holds the new position
+    // waits for the block barrier below where this CTA writes that row itself (FP8: the quantised row written
+    // by threads 0..63; fused QK-norm: the bf16 row written by warps 2 and 3).
+    const bool fused = qk.part != nullptr;
+    const bool defer_new = has_new && (FP8 || fused);
 #pragma unroll
     for (int s = 0; s < BD_STAGES - 1; ++s) {
         const int t = tile_lo + warp + s * (BD_THREADS / 32);
-        if (t < ntiles) {
-            if constexpr (FP8) {
-                if (!(has_new && t == ntiles - 1)) bd_load_tile_fp8(wraw + s * BD8_RAW, k8b, v8b, t, len, lane);
-            } else {
-                bd_load_tile(wring + s * BD_STAGE_ELEMS, kb, vb, t, len, lane);
-            }
+        if (t < ntiles && !(defer_new && t == ntiles - 1)) {
+            if constexpr (FP8) bd_load_tile_fp8(wraw + s * BD8_RAW, k8b, v8b, t, len, lane);
+            else bd_load_tile(wring + s * BD_STAGE_ELEMS, kb, vb, t, len, lane);
         }
         cp_async_commit();
+    }
+    if (fused) {
+        // warp 0, 1: query heads 2 g, 2 g + 1 -> qs; warp 2: the new K row; warp 3: the new V row (both into the cache)
+        if (warp < 2 || (warp < 4 && has_new)) {
+            const size_t plane = (size_t)qk.M * QKV;
+            const int col0 = warp < 2 ? (2 * g + warp) * D : warp == 2 ? QSZ + g * D : QSZ + KVSZ + g * D;
+            const size_t i0 = (size_t)b * QKV + col0;
+            if (warp == 3) {
+                float f[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) f[e] = sum_splits(qk.part, qk.ksplit, plane, i0 + 4 * lane + e);
+                *reinterpret_cast<uint2*>(const_cast<bf16*>(vb) + (size_t)pos * D + 4 * lane) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+            } else {
+                float xl[2], xh[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    xl[e] = rbf(sum_splits(qk.part, qk.ksplit, plane, i0 + 2 * lane + e));
+                    xh[e] = rbf(sum_splits(qk.part, qk.ksplit, plane, i0 + 64 + 2 * lane + e));
+                }
+                float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
+                ss = warp_sum(ss);
+                const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
+                const bf16* wn = warp < 2 ? qk.wq : qk.wk;
+                const bf16* cosr = qk.cos + (size_t)pos * D;
+                const bf16* sinr = qk.sin + (size_t)pos * D;
+                const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
+                const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
+                const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
+                const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
+                const float clo[2] = {bf_lo(cl), bf_hi(cl)}, chi[2] = {bf_lo(chh), bf_hi(chh)};
+                const float slo[2] = {bf_lo(sl), bf_hi(sl)}, shi[2] = {bf_lo(sh), bf_hi(sh)};
+                float lo[2], hi[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float nl = rbf(wlo[e] * rbf(xl[e] * r));
+                    const float nh = rbf(whi[e] * rbf(xh[e] * r));
+                    lo[e] = rbf(rbf(nl * clo[e]) + rbf(-nh * slo[e]));
+                    hi[e] = rbf(rbf(nh * chi[e]) + rbf(nl * shi[e]));
+                }
+                if (warp < 2) {
+                    bf16* qd = qs + warp * D;
+                    *reinterpret_cast<uint32_t*>(qd + 2 * lane) = FP8 ? pack_f16x2(lo[0], lo[1]) : pack_bf16x2(lo[0], lo[1]);
+                    *reinterpret_cast<uint32_t*>(qd + 64 + 2 * lane) = FP8 ? pack_f16x2(hi[0], hi[1]) : pack_bf16x2(hi[0], hi[1]);
+                } else {
+                    bf16* kd = const_cast<bf16*>(kb) + (size_t)pos * D;
+                    *reinterpret_cast<uint32_t*>(kd + 2 * lane) = pack_bf16x2(lo[0], lo[1]);
+                    *reinterpret_cast<uint32_t*>(kd + 64 + 2 * lane) = pack_bf16x2(hi[0], hi[1]);
+                }
+            }
+        }
+        if constexpr (FP8) __syncthreads();   // the bf16 row is complete before threads 0..63 quantise it
     }
     if constexpr (FP8) {
         if (tid < 64 && has_new) {
@@ -1473,7 +1533,7 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
             __threadfence_block();
         }
     }
-    if (tid >= 64 && tid < 96) {
+    if (!fused && tid >= 64 && tid < 96) {
         const int t8 = tid - 64;
         uint4 q = *reinterpret_cast<const uint4*>(qkv + (size_t)b * QKV + 2 * g * D + t8 * 8);
         if constexpr (FP8) {   // f16 tiles are multiplied with an f16 query
@@ -1483,10 +1543,12 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
         *reinterpret_cast<uint4*>(qs + t8 * 8) = q;
     }
     __syncthreads();
-    if constexpr (FP8) {
+    if (FP8 || fused) {
         const int tl = ntiles - 1 - tile_lo;                  // the deferred tile, counted from this part's first
-        if (has_new && tl >= 0 && tl < (BD_STAGES - 1) * (BD_THREADS / 32) && warp == tl % (BD_THREADS / 32))
-            bd_load_tile_fp8(wraw + (tl / (BD_THREADS / 32)) * BD8_RAW, k8b, v8b, ntiles - 1, len, lane);
+        if (defer_new && tl >= 0 && tl < (BD_STAGES - 1) * (BD_THREADS / 32) && warp == tl % (BD_THREADS / 32)) {
+            if constexpr (FP8) bd_load_tile_fp8(wraw + (tl / (BD_THREADS / 32)) * BD8_RAW, k8b, v8b, ntiles - 1, len, lane);
+            else bd_load_tile(wring + (tl / (BD_THREADS / 32)) * BD_STAGE_ELEMS, kb, vb, ntiles - 1, len, lane);
+        }
         cp_async_commit();
     }
 
@@ -1662,9 +1724,9 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 6 ? 2 : 1)
 k_bd_attention(const bf16* __restrict__ qkv, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
                const int* __restrict__ positions, int layer, int max_seq, size_t seq_stride, uint8_t* __restrict__ k8, uint8_t* __restrict__ v8,
                const float* __restrict__ k_scale, const float* __restrict__ v_scale, int scale_stride, float* __restrict__ parts,
-               unsigned int* __restrict__ tickets, int n_full, int p_tail) {
+               unsigned int* __restrict__ tickets, int n_full, int p_tail, const BdQkFuse qk) {
     bd_attention_body<FP8, WARPS>(qkv, k_cache, v_cache, out, positions, layer, max_seq, seq_stride, k8, v8, k_scale, v_scale, scale_stride, parts,
-                                  tickets, n_full, p_tail);
+                                  tickets, n_full, p_tail, qk);
 }
 
 // out_tokens[b] = lowest index of the maximum bf16 logit of row b; positions[b] += 1.
@@ -1934,7 +1996,7 @@ extern "C" int mq_launch_prefill_packed(const MqModel* model, const MqBatchBuffe
     return (int)cudaGetLastError();
 }
 
-// kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches one fewer per layer
+// kernels of one step on the tile-GEMM path (batch > 64); the split-K path for smaller batches launches two fewer per layer
 extern "C" int mq_decode_batch_launch_count(int num_layers) { return 1 + num_layers * 10 + 3; }
 
 // How a batched attention launch is shaped for `items` = 8 x batch (sequence, kv head) pairs.  Up to one
@@ -1977,21 +2039,21 @@ static int bd_set_smem() {
 // attention of one layer of a batched decode step, from the bf16 caches or from the e4m3 shadow caches
 template <bool FP8, int WARPS>
 static void launch_bd_attention_t(int B, BdShape sh, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn,
-                                  int l, const MqModel* model, size_t seq_stride) {
+                                  int l, const MqModel* model, size_t seq_stride, const BdQkFuse& qk) {
     const int ctas = sh.n_full + (B * NKV - sh.n_full) * sh.p_tail;
     launch_pdl(k_bd_attention<FP8, WARPS>, dim3(ctas), dim3(WARPS * 32), bd_smem_bytes(WARPS), stream, qkv, (const bf16*)bb->k_cache,
                (const bf16*)bb->v_cache, attn, (const int*)bb->positions, l, model->max_seq_len, seq_stride,
                (uint8_t*)(kv8 ? kv8->k_fp8 : nullptr), (uint8_t*)(kv8 ? kv8->v_fp8 : nullptr), (const float*)(kv8 ? kv8->k_scale : nullptr),
-               (const float*)(kv8 ? kv8->v_scale : nullptr), model->num_layers * NKV, bb->attn_parts, bb->attn_tickets, sh.n_full, sh.p_tail);
+               (const float*)(kv8 ? kv8->v_scale : nullptr), model->num_layers * NKV, bb->attn_parts, bb->attn_tickets, sh.n_full, sh.p_tail, qk);
 }
 static void launch_bd_attention(int B, BdShape sh, cudaStream_t stream, const bf16* qkv, const MqBatchBuffers* bb, const MqKvFp8* kv8, bf16* attn, int l,
-                                const MqModel* model, size_t seq_stride) {
+                                const MqModel* model, size_t seq_stride, const BdQkFuse& qk) {
     if (kv8) {
-        if (sh.warps == 6) launch_bd_attention_t<true, 6>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
-        else launch_bd_attention_t<true, 12>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        if (sh.warps == 6) launch_bd_attention_t<true, 6>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride, qk);
+        else launch_bd_attention_t<true, 12>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride, qk);
     } else {
-        if (sh.warps == 6) launch_bd_attention_t<false, 6>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
-        else launch_bd_attention_t<false, 12>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        if (sh.warps == 6) launch_bd_attention_t<false, 6>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride, qk);
+        else launch_bd_attention_t<false, 12>(B, sh, stream, qkv, bb, kv8, attn, l, model, seq_stride, qk);
     }
 }
 
@@ -2040,11 +2102,10 @@ static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, con
             const int rqkv[3] = {QSZ, KVSZ, KVSZ};
             rc = launch_skinny(wqkv, rqkv, 3, x, H, part, B, H, 4, status, stream);
             if (rc) return rc;
-            // sums the four K-split planes, applies QK-norm + RoPE, writes q to qkv and k, v to the caches
-            launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
-                                                             (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
-                                                             model->max_seq_len, bb->positions, seq_stride, (const float*)part, 4, B, nullptr);
-            launch_bd_attention(B, shape, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+            // the attention CTAs sum the four K-split planes of their heads, apply QK-norm + RoPE and write the new K / V rows
+            const BdQkFuse qk{(const float*)part, 4, B, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
+                              (const bf16*)model->sin_table};
+            launch_bd_attention(B, shape, stream, qkv, bb, kv8, attn, l, model, seq_stride, qk);
             const bf16* wo[1] = {(const bf16*)w.o_proj};
             const int ro[1] = {H};
             rc = launch_skinny(wo, ro, 1, attn, QSZ, part, B, QSZ, 8, status, stream);
@@ -2074,7 +2135,7 @@ static int decode_batch_impl(const MqModel* model, const MqBatchBuffers* bb, con
         launch_pdl(k_pf_qknorm_rope, dim3(dim3(B, 4)), dim3(256), 0, stream, qkv, (const bf16*)w.q_norm, (const bf16*)w.k_norm, (const bf16*)model->cos_table,
                                                          (const bf16*)model->sin_table, (bf16*)bb->k_cache, (bf16*)bb->v_cache, l, 0,
                                                          model->max_seq_len, bb->positions, seq_stride, nullptr, 0, 0, nullptr);
-        launch_bd_attention(B, shape, stream, qkv, bb, kv8, attn, l, model, seq_stride);
+        launch_bd_attention(B, shape, stream, qkv, bb, kv8, attn, l, model, seq_stride, BdQkFuse{});
         rc = launch_gemm<128, EPI_RESID>(attn, QSZ, (const bf16*)w.o_proj, nullptr, h, h, B, H, QSZ, H, status, stream);
         if (rc) return rc;
         launch_pdl(k_pf_rmsnorm, dim3((B + 7) / 8), dim3(256), 0, stream, h, (const bf16*)w.post_attn_layernorm, x, B);
