@@ -480,10 +480,38 @@ k_gemm_skinny(const __grid_constant__ CUtensorMap tmW0, const __grid_constant__ 
 }
 
 // consumers of the fp32 K-split partials part[ks][row][col] (ks summed in index order)
+template <int KS>
+__device__ __forceinline__ float sum_planes(const float* part, size_t plane, size_t idx) {
+    float v[KS];
+#pragma unroll
+    for (int k = 0; k < KS; ++k) v[k] = part[(size_t)k * plane + idx];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < KS; ++k) s += v[k];
+    return s;
+}
 __device__ __forceinline__ float sum_splits(const float* part, int ksplit, size_t plane, size_t idx) {
+    // every plane is requested before the first is used (a loop of unknown length would wait for one L2 round trip
+    // per plane); the sum runs in plane order whatever the count, so the result does not depend on this dispatch
+    switch (ksplit) {
+    case 2: return sum_planes<2>(part, plane, idx);
+    case 4: return sum_planes<4>(part, plane, idx);
+    case 8: return sum_planes<8>(part, plane, idx);
+    default: break;
+    }
     float s = 0.f;
     for (int k = 0; k < ksplit; ++k) s += part[(size_t)k * plane + idx];
     return s;
+}
+template <int KS>
+__device__ __forceinline__ float4 sum_planes4(const float* part, size_t plane, size_t idx) {
+    float4 v[KS];
+#pragma unroll
+    for (int k = 0; k < KS; ++k) v[k] = *reinterpret_cast<const float4*>(part + (size_t)k * plane + idx);
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < KS; ++k) { a.x += v[k].x; a.y += v[k].y; a.z += v[k].z; a.w += v[k].w; }
+    return a;
 }
 
 
@@ -495,12 +523,16 @@ __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__
     __shared__ float s_red[8];
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t base = (size_t)row * H + 4 * tid, plane = (size_t)M * H;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int k = 0; k < ksplit; ++k) {
-        const float4 p = *reinterpret_cast<const float4*>(part + (size_t)k * plane + base);
-        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-    }
     const uint2 hu = *reinterpret_cast<const uint2*>(h + base);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ksplit == 8) acc = sum_planes4<8>(part, plane, base);
+    else if (ksplit == 2) acc = sum_planes4<2>(part, plane, base);
+    else if (ksplit == 4) acc = sum_planes4<4>(part, plane, base);
+    else
+        for (int k = 0; k < ksplit; ++k) {
+            const float4 p = *reinterpret_cast<const float4*>(part + (size_t)k * plane + base);
+            acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        }
     float v[4] = {rbf(bf_lo(hu.x) + rbf(acc.x)), rbf(bf_hi(hu.x) + rbf(acc.y)), rbf(bf_lo(hu.y) + rbf(acc.z)), rbf(bf_hi(hu.y) + rbf(acc.w))};
     *reinterpret_cast<uint2*>(h + base) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
     if (!w) return;   // residual stream only (after the last layer nothing is normalised here)
