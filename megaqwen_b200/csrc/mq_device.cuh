@@ -275,6 +275,9 @@ __device__ __forceinline__ float dot_slice(const bf16* wrow_smem, const float (&
 // RMSNorm of a 1024-wide bf16 vector held as a register slice per lane (every
 // warp holds the whole vector): x <- bf16(w * bf16(x * rsqrt(mean(x^2) + eps))).
 __device__ __forceinline__ void rmsnorm_slice(float (&x)[32], const bf16* w, int lane) {
+    uint4 wu[4];   // requested before the row sum, used after it
+#pragma unroll
+    for (int j = 0; j < 4; ++j) wu[j] = *reinterpret_cast<const uint4*>(w + j * 256 + lane * 8);
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) ss = fmaf(x[i], x[i], ss);
@@ -282,7 +285,7 @@ __device__ __forceinline__ void rmsnorm_slice(float (&x)[32], const bf16* w, int
     const float r = 1.0f / sqrtf(ss * (1.0f / H) + RMS_EPS);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        uint4 u = *reinterpret_cast<const uint4*>(w + j * 256 + lane * 8);
+        const uint4 u = wu[j];
         const float wv[8] = {bf_lo(u.x), bf_hi(u.x), bf_lo(u.y), bf_hi(u.y), bf_lo(u.z), bf_hi(u.z), bf_lo(u.w), bf_hi(u.w)};
 #pragma unroll
         for (int e = 0; e < 8; ++e) x[j * 8 + e] = rbf(wv[e] * rbf(x[j * 8 + e] * r));

@@ -524,6 +524,7 @@ __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const size_t base = (size_t)row * H + 4 * tid, plane = (size_t)M * H;
     const uint2 hu = *reinterpret_cast<const uint2*>(h + base);
+    const uint2 wu = w ? *reinterpret_cast<const uint2*>(w + 4 * tid) : make_uint2(0u, 0u);   // requested with the planes, used after the row sum
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (ksplit == 8) acc = sum_planes4<8>(part, plane, base);
     else if (ksplit == 2) acc = sum_planes4<2>(part, plane, base);
@@ -543,7 +544,6 @@ __global__ void __launch_bounds__(256) k_sk_resid_norm(const float* __restrict__
 #pragma unroll
     for (int i = 0; i < 8; ++i) tot += s_red[i];
     const float r = 1.0f / sqrtf(tot * (1.0f / H) + RMS_EPS);
-    const uint2 wu = *reinterpret_cast<const uint2*>(w + 4 * tid);
     const uint2 o = make_uint2(pack_bf16x2(rbf(bf_lo(wu.x) * rbf(v[0] * r)), rbf(bf_hi(wu.x) * rbf(v[1] * r))),
                                pack_bf16x2(rbf(bf_lo(wu.y) * rbf(v[2] * r)), rbf(bf_hi(wu.y) * rbf(v[3] * r))));
     *reinterpret_cast<uint2*>(x + base) = o;
@@ -676,10 +676,10 @@ __global__ void __launch_bounds__(256) k_pf_qknorm_rope(bf16* __restrict__ qkv, 
             const uint32_t ulo = *reinterpret_cast<const uint32_t*>(head + 2 * lane), uhi = *reinterpret_cast<const uint32_t*>(head + 64 + 2 * lane);
             xl[0] = bf_lo(ulo); xl[1] = bf_hi(ulo); xh[0] = bf_lo(uhi); xh[1] = bf_hi(uhi);
         }
+        const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
         float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
         ss = warp_sum(ss);
         const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
-        const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
         const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
         float lo[2], hi[2];
 #pragma unroll
@@ -1515,6 +1515,13 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
                 for (int e = 0; e < 4; ++e) f[e] = sum_splits(qk.part, qk.ksplit, plane, i0 + 4 * lane + e);
                 *reinterpret_cast<uint2*>(const_cast<bf16*>(vb) + (size_t)pos * D + 4 * lane) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
             } else {
+                // the norm weights and the position's cos / sin rows are requested together with the planes
+                const bf16* wn = warp < 2 ? qk.wq : qk.wk;
+                const bf16* cosr = qk.cos + (size_t)pos * D;
+                const bf16* sinr = qk.sin + (size_t)pos * D;
+                const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
+                const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
+                const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
                 float xl[2], xh[2];
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
@@ -1524,12 +1531,6 @@ __device__ __forceinline__ void bd_attention_body(const bf16* __restrict__ qkv, 
                 float ss = xl[0] * xl[0] + xl[1] * xl[1] + xh[0] * xh[0] + xh[1] * xh[1];
                 ss = warp_sum(ss);
                 const float r = 1.0f / sqrtf(ss * (1.0f / D) + RMS_EPS);
-                const bf16* wn = warp < 2 ? qk.wq : qk.wk;
-                const bf16* cosr = qk.cos + (size_t)pos * D;
-                const bf16* sinr = qk.sin + (size_t)pos * D;
-                const uint32_t wl = *reinterpret_cast<const uint32_t*>(wn + 2 * lane), wh = *reinterpret_cast<const uint32_t*>(wn + 64 + 2 * lane);
-                const uint32_t cl = *reinterpret_cast<const uint32_t*>(cosr + 2 * lane), chh = *reinterpret_cast<const uint32_t*>(cosr + 64 + 2 * lane);
-                const uint32_t sl = *reinterpret_cast<const uint32_t*>(sinr + 2 * lane), sh = *reinterpret_cast<const uint32_t*>(sinr + 64 + 2 * lane);
                 const float wlo[2] = {bf_lo(wl), bf_hi(wl)}, whi[2] = {bf_lo(wh), bf_hi(wh)};
                 const float clo[2] = {bf_lo(cl), bf_hi(cl)}, chi[2] = {bf_lo(chh), bf_hi(chh)};
                 const float slo[2] = {bf_lo(sl), bf_hi(sl)}, shi[2] = {bf_lo(sh), bf_hi(sh)};
