@@ -39,6 +39,34 @@ def test_tcgen05_gemm_matches_torch(M, N, K, resid):
     assert float(d.max()) <= 2 ** -5 * max(1.0, float(ref.float().abs().max()))
 
 
+def test_gemm_operand_written_by_the_preceding_launch():
+    """The library's own chains request weight tiles before the dependency wait; the public GEMM must not: its
+    B operand may be what the launch just before it on the stream has written.  Twenty back-to-back pairs
+    C1 = A1 B1^T, C2 = A2 C1^T with C1 overwritten by a different product each time."""
+    from megaqwen_b200 import _lib
+    lib = _lib.lib()
+    g = torch.Generator(device="cpu").manual_seed(11)
+    M1, K1, N2 = 256, 512, 384                      # C1 [M1, 1024] is GEMM 2's B: N = M1, K = 1024
+    a2 = (torch.randn((N2, 1024), generator=g) * 0.1).to(torch.bfloat16).cuda()
+    c1 = torch.zeros((M1, 1024), dtype=torch.bfloat16, device="cuda")
+    c2 = torch.zeros((N2, M1), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for it in range(20):
+        a1 = (torch.randn((M1, K1), generator=g) * 0.5).to(torch.bfloat16).cuda()
+        b1 = (torch.randn((1024, K1), generator=g) * 0.05).to(torch.bfloat16).cuda()
+        torch.cuda.synchronize()
+        assert lib.mq_launch_gemm_bf16(a1.data_ptr(), K1, b1.data_ptr(), c1.data_ptr(), None, M1, 1024, K1, 1024, status.data_ptr(), stream) == 0
+        assert lib.mq_launch_gemm_bf16(a2.data_ptr(), 1024, c1.data_ptr(), c2.data_ptr(), None, N2, M1, 1024, M1, status.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        ref1 = (a1.float() @ b1.float().t()).to(torch.bfloat16)
+        assert float((c1.float() - ref1.float()).abs().max()) <= 2 ** -5 * max(1.0, float(ref1.float().abs().max()))
+        ref2 = (a2.float() @ c1.float().t()).to(torch.bfloat16)          # against the C1 actually produced
+        d = (c2.float() - ref2.float()).abs()
+        assert float(d.max()) <= 2 ** -5 * max(1.0, float(ref2.float().abs().max())), (it, float(d.max()))
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("drop_kb", [0, 9])
 def test_expired_wait_sets_status_and_leaves_the_device_usable(drop_kb):
     """The error path every bounded device wait shares, made to run out on the host's terms: the GEMM's
