@@ -53,6 +53,14 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the same with the A operand in tensor memory (row i of A in lane i, two consecutive K elements per 32-bit column)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // arrive on `bar` once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -938,7 +946,9 @@ __global__ void __launch_bounds__(FA_THREADS, 1) k_pf_attention(const bf16* __re
 // One CTA per (query head, 128-query tile); key tiles of 128 positions.  Both contractions run
 // on the 5th-generation tensor cores with their accumulators in tensor memory:
 //     S = Q K^T     A = Q tile [128 q x 128 d], B = K tile [128 keys x 128 d] straight from the KV cache
-//     O_j = P V     A = P tile [128 q x 128 keys] (bf16, written by the softmax warps),
+//     O_j = P V     A = P tile [128 q x 128 keys] (bf16) IN TENSOR MEMORY: the softmax warps write the probabilities
+//                   over the scores they came from (tcgen05.st; 64 packed columns of S's 128), so the product
+//                   reads only V from shared memory and nothing crosses the generic / async proxy boundary,
 //                   B = V tile [128 keys x 128 d] straight from the KV cache, read as an MN-major operand
 //                   (the cache rows are contiguous along d, the product contracts over the keys)
 // (128-byte swizzle, fetched by TMA; the V map ends at the last key of the prompt, so the rows of the
@@ -953,11 +963,10 @@ constexpr int TA_BQ = 128, TA_BK = 128;
 constexpr int TA_THREADS = 320;                             // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 constexpr int TA_TILE_BYTES = 128 * 128 * 2;               // two 64-column halves of [128 rows x 128 bytes]
 constexpr int TA_HALF_BYTES = TA_TILE_BYTES / 2;
-constexpr size_t TA_SMEM = (size_t)7 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + TA_BQ * 8 /*row exchange*/;   // Q, 2 K, 2 V, 2 P
+constexpr size_t TA_SMEM = (size_t)5 * TA_TILE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + TA_BQ * 8 /*row exchange*/;   // Q, 2 K, 2 V
 static_assert(TA_SMEM <= 232448, "shared memory of one CTA");
 constexpr uint32_t TA_TMEM_COLS = 512;                      // S0 | S1 | O (128 columns each)
 
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __global__ void __launch_bounds__(TA_THREADS, 1)
 k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -969,8 +978,7 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + TA_TILE_BYTES;            // [2]
     uint8_t* sV = sK + 2 * TA_TILE_BYTES;        // [2]
-    uint8_t* sP = sV + 2 * TA_TILE_BYTES;        // [2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TA_TILE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * TA_TILE_BYTES);
     uint64_t* q_full = bars;                     // 1
     uint64_t* k_full = bars + 1;                 // 2
     uint64_t* k_empty = bars + 3;                // 2
@@ -979,7 +987,6 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint64_t* s_full = bars + 9;                 // 2
     uint64_t* s_free = bars + 11;                // 2 (256 arrivals)
     uint64_t* p_full = bars + 13;                // 2 (256 arrivals)
-    uint64_t* p_free = bars + 15;                // 2
     uint64_t* o_full = bars + 17;                // 1
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
     float (*xm)[2] = reinterpret_cast<float(*)[2]>(bars + 20);   // [128][2]: the two half-row maxima (at the end: sums) of a query row
@@ -994,7 +1001,7 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 256); mbar_init(&p_full[i], 256); mbar_init(&p_free[i], 1);
+            mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 256); mbar_init(&p_full[i], 256);
         }
         mbar_init(o_full, 1);
         mbar_fence_init();
@@ -1057,14 +1064,14 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (ok) {
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk) {
-                        const uint64_t da = smem_desc_sw128(sP + st * TA_TILE_BYTES + (kk >> 2) * TA_HALF_BYTES) + 2 * (kk & 3);
-                        // 16 keys per step = two 1024-byte groups of the [keys][64 d] panels (d 0-63 | d 64-127)
+                        // A = the probabilities, written by the softmax threads over the scores they came from: 16 keys
+                        // of a row are eight 32-bit columns.  B: 16 keys per step = two 1024-byte groups of the
+                        // [keys][64 d] panels (d 0-63 | d 64-127)
                         const uint64_t db = smem_desc_mn_sw128(sV + st * TA_TILE_BYTES, TA_HALF_BYTES) + (uint64_t)(kk * (2048 >> 4));
-                        umma_bf16(tmem_o, da, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates over all key tiles
+                        umma_bf16_ts(tmem_o, tmem_base + st * 128 + kk * 8, db, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);   // O accumulates over all key tiles
                     }
                 }
                 umma_commit(&v_empty[st]);
-                umma_commit(&p_free[st]);
                 umma_commit(o_full);
             }
         }
@@ -1144,26 +1151,24 @@ k_pf_attention_tc(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 if (grow) m = mx;
             }
             const float mc = m * c;
-            if (j >= 2) ok = ok && mbar_wait(&p_free[st], (uint32_t)((j >> 1) - 1) & 1u, status);
-            // probabilities -> bf16 -> A operand of the P V product (K-major, 128-byte swizzle); this thread's
-            // 64 keys are the 64-column half `half` of the tile
+            // (S[st] last held the probabilities of tile j - 2; their product was issued before the Q K^T of this tile)
+            // probabilities -> bf16 pairs -> A operand of the P V product in tensor memory; this thread's 64 keys
+            // are 32 packed columns
             float rs = 0.f;
-            uint8_t* prow = sP + st * TA_TILE_BYTES + half * TA_HALF_BYTES + r * 128;
+            uint32_t pk[32];
 #pragma unroll
-            for (int c16 = 0; c16 < 8; ++c16) {               // 16-byte chunk = 8 keys
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c16 * 8 + 2 * e]), c, -mc));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c16 * 8 + 2 * e + 1]), c, -mc));
-                    rs += p0 + p1;
-                    pk[e] = pack_bf16x2(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(prow + ((c16 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), c, -mc));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), c, -mc));
+                rs += p0 + p1;
+                pk[i] = pack_bf16x2(p0, p1);
             }
+            // into the columns the scores of keys 0-63 came from (both threads of the row have read theirs: the
+            // exchange above lies in between); 64 keys of the row are 32 columns
+            tmem_st32(tmem_base + st * 128 + lane_off + half * 32, pk);
             l += rs;
             if (!seen_prev) ok = ok && mbar_wait(o_full, (uint32_t)(j - 1) & 1u, status);   // P V of tile j - 1 (precedes this tile's anyway)
-            fence_async_smem();                               // the tensor core reads P through the async proxy
+            tc_fence_before();
             mbar_arrive(&p_full[st]);
         }
         // the last P V product, then out = O / l (l = the sum of the two half-row sums)
